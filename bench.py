@@ -1,0 +1,313 @@
+#!/usr/bin/env python
+"""Benchmark of the fused AllReduce optimizer step.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 2): mixed-precision Adam on one flattened buffer of
+334,000,000 parameters -- fp16 Local gradients (loss scale 1024, removed in the
+kernel), fp32 master weights, fp32 Sliced m/v, fp16 Replicated weight copy that
+is all-gathered -- at world size N.  Synthetic seeded inputs.
+
+A "step" is one fused call per rank: reduce-scatter of the gradients, the Adam
+update of the rank's slice, all-gather of the updated weights; one kernel.
+`value` counts gradient elements reduced and applied per second over the whole
+job (N ranks x count / step time), inputs resident in HBM.  `e2e` is the same
+with the gradients arriving from pinned host memory and the updated fp16
+weights read back to the host every step.
+
+For N > 1 launch with torchrun (one rank per GPU); rank 0 prints ONE JSON line.
+`--impl reference` times the reference's CPU path (single-threaded host loops)
+on a bounded sample instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+COUNT = 334_000_000
+LOSS_SCALE = 1024.0
+HYPER = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-6)
+NVLINK_PEER_GBS = 770.0  # measured peer copy per direction on this pool (900 nominal)
+METRIC = "fused_allreduce_adam_grad_elems_per_s"
+UNIT = "Gelem/s"
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self._stop = index, [], threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                if len(f) >= 9:
+                    self.samples.append(f)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def start(self):
+        self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        self._t.join(timeout=6)
+        sm = sorted(float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit())
+        mx = [float(s[2]) for s in self.samples if s[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[5:9]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def cpu_baseline(count_sample, world, reps=2):
+    """The reference's CPU path (host sum of `world` gradient arrays + the
+    per-element passes) on a bounded sample, single-threaded."""
+    import numpy as np
+    import oracle_lib as O
+    so = os.path.join(ROOT, "oracle", "liboracle.so")
+    if not os.path.exists(so):
+        subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "-s"])
+    n = count_sample
+    rng = np.random.default_rng(0)
+    grads = [(rng.standard_normal(n, dtype=np.float32) * 1e-3 * LOSS_SCALE).astype(np.float16)
+             for _ in range(world)]
+    w = (rng.standard_normal(n, dtype=np.float32) * 0.02).astype(np.float32)
+    m, v = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    wl = np.zeros(n, np.float16)
+    best = None
+    for step in range(reps):
+        t0 = time.perf_counter()
+        O.cpu_step_adam(grads, w, m, v, HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"],
+                        step, inv_scale=1.0 / LOSS_SCALE, w_lp=wl)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": world * n / best / 1e9, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"{n} of {COUNT} elements x {world} gradient arrays, best of {reps}, "
+                      f"{best * 1e3:.1f} ms per step; host has {os.cpu_count()} cores"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    n = 1 << 24
+    steps = max(1, min(args.steps, 3))
+    cb = cpu_baseline(n, world, reps=steps + min(args.warmup, 1))
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT,
+            "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 1),
+            "ms_per_step": world * n / (cb["value"] * 1e9) * 1e3 * (COUNT / n),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "mixed_adam_334M", "count": COUNT, "world": world,
+                       "note": "CPU loops timed on a sample and reported as a rate; ms_per_step "
+                               "is that rate scaled to the full count"},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--count", type=int, default=COUNT, help="elements (default: the 334M workload)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the stock NCCL comparison (N > 1)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1 and args.gpus > 1:
+        print(f"bench.py --gpus {args.gpus} must be launched with torchrun (one rank per GPU)",
+              file=sys.stderr)
+        sys.exit(2)
+
+    if args.impl == "reference":
+        run_reference(args, rank, max(world, args.gpus))
+        return
+
+    import torch
+    import torch.distributed as dist
+    import coconet_b200 as coco
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        comm = coco.Communicator.from_torch_distributed()
+    else:
+        comm = coco.Communicator.init_all(1, [local_rank])[0]
+
+    N, R = args.count, world
+    lo, hi = coco.slice_bounds(N, R, rank)
+    S = (N + R - 1) // R
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    # two gradient buffers, alternated, each far larger than L2 (126 MB)
+    g = []
+    for _ in range(2):
+        t = torch.empty(N, dtype=torch.float16, device=dev)
+        chunk = 1 << 26
+        for a in range(0, N, chunk):
+            b = min(N, a + chunk)
+            t[a:b] = (torch.randn(b - a, device=dev, generator=gen) * (1e-3 * LOSS_SCALE)).half()
+        g.append(t)
+    wgen = torch.Generator(device=dev).manual_seed(7)
+    w = torch.randn(N, device=dev, generator=wgen) * 0.02
+    w_lp = w.half()
+    m = torch.zeros(S, device=dev)
+    v = torch.zeros(S, device=dev)
+    for t in g:
+        comm.register(t)
+    comm.register(w_lp)
+
+    step_no = [0]
+
+    def fused_step(gbuf):
+        comm.fused_adam(gbuf, w, m, v, HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"],
+                        step_no[0], w_lp=w_lp, grad_scale=1.0 / LOSS_SCALE)
+        step_no[0] += 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        """ms per step, max over ranks (CUDA events on the launching stream)."""
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        barrier()
+        return float(ms.item())
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    l0 = comm.launch_count()
+    ms = timed(lambda i: fused_step(g[i & 1]), args.steps, args.warmup)
+    launches = comm.launch_count() - l0 - args.warmup
+    clocks = sampler.stop() if sampler else None
+    st = comm.status()
+    if st["code"] != 0:
+        raise SystemExit(f"device-side failure during the benchmark: {st}")
+
+    # ---- end to end: host gradients in, host fp16 weights out ------------------
+    e2e = None
+    if not args.no_e2e:
+        hg = torch.empty(N, dtype=torch.float16).pin_memory()
+        hg.copy_(g[0])
+        hout = torch.empty(N, dtype=torch.float16).pin_memory()
+
+        def e2e_step(i):
+            g[i & 1].copy_(hg, non_blocking=True)
+            fused_step(g[i & 1])
+            hout.copy_(w_lp, non_blocking=True)
+
+        k = max(3, min(args.steps, 10))
+        ems = timed(e2e_step, k, 2)
+        e2e = {"value": R * N / (ems * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ems,
+               "h2d_bytes_per_step": N * 2, "d2h_bytes_per_step": N * 2}
+        del hg, hout
+
+    # ---- stock NCCL all-reduce + separate update kernel (the AR_C schedule) ---
+    nccl = None
+    if world > 1 and not args.no_baseline:
+        local = coco.Communicator.init_all(1, [local_rank])[0]
+        mf = torch.zeros(N, device=dev)
+        vf = torch.zeros(N, device=dev)
+        gb = g[0].clone()
+        bstep = [0]
+
+        def nccl_step(i):
+            dist.all_reduce(gb)
+            local.fused_adam(gb, w, mf, vf, HYPER["lr"], HYPER["beta1"], HYPER["beta2"],
+                             HYPER["eps"], bstep[0], w_lp=w_lp, grad_scale=1.0 / LOSS_SCALE)
+            bstep[0] += 1
+
+        k = max(3, min(args.steps, 10))
+        bms = timed(nccl_step, k, 3)
+        nccl = {"what": "torch.distributed.all_reduce (NCCL) on fp16 gradients + one update "
+                        "kernel over all elements", "ms_per_step": bms, "speedup": bms / ms}
+        local.destroy()
+        del mf, vf, gb
+
+    if rank == 0:
+        hbm_peak, peak_kind = measured_peaks()
+        s_g, s_o = 2, 2
+        # algorithmic bytes per launch (per GPU)
+        b_hbm = N * s_g + (hi - lo) * 24 + (hi - lo) * s_o + (R - 1) * S * s_o
+        b_nv = (R - 1) * S * (s_g + s_o)
+        t = ms * 1e-3
+        if R == 1:
+            roof = {"bound": "hbm", "achieved": b_hbm / t / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": b_hbm / t / 1e9 / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                    "algorithmic_bytes": b_hbm}
+        else:
+            t_roof = max(b_nv / (NVLINK_PEER_GBS * 1e9), b_hbm / (hbm_peak * 1e9))
+            roof = {"bound": "nvlink", "achieved": b_nv / t / 1e9, "peak": NVLINK_PEER_GBS,
+                    "unit": "GB/s", "frac": t_roof / t, "traffic": None,
+                    "peak_kind": "measured peer copy per direction (900 nominal)",
+                    "algorithmic_bytes": b_nv, "hbm_bytes": b_hbm,
+                    "frac_of_nominal_900": max(b_nv / 900e9, b_hbm / 8e12) / t}
+        line = {"metric": METRIC, "value": R * N / t / 1e9, "unit": UNIT, "n_gpus": R,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
+                "config": {"workload": "mixed_adam_334M" if N == COUNT else f"mixed_adam_{N}",
+                           "count": N, "world": R, "grad": "f16", "state": "f32", "gathered": "f16",
+                           "l2": "inputs larger than L2 (two 668 MB gradient buffers alternated)"},
+                "bus_gbs": b_nv / t / 1e9, "roofline": roof, "clocks": clocks,
+                "gpu_launches": int(launches), "e2e": e2e}
+        if nccl:
+            line["nccl_baseline"] = nccl
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(1 << 24, 1)
+        print(json.dumps(line), flush=True)
+
+    comm.destroy()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,821 @@
+// Host side of the C ABI declared in coconet_rt.h: communicators, peer
+// mapping of caller buffers, the flag page, launch configuration.
+//
+// Replaces, for the fused optimizer step only, what the reference gets from
+// its NCCL 2.6.4 fork (parasailteam/coconet): communicator set-up
+// (nccl/src/init.cc), the P2P transport's IPC mapping
+// (nccl/src/transport/p2p.cc:118-238), argument marshalling and launch
+// (nccl/src/enqueue.cc:200-343) and async error reporting
+// (nccl/src/init.cc:972-1021).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <cmath>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "bootstrap.h"
+#include "coconet_rt.h"
+#include "fused_step.cuh"
+
+using namespace coco;
+
+namespace {
+
+int env_int(const char *name, int dflt) {
+  const char *e = getenv(name);
+  if (!e || !e[0]) return dflt;
+  return atoi(e);
+}
+
+int debug_level() {
+  static int lvl = [] {
+    const char *e = getenv("COCO_DEBUG");
+    if (!e) return 0;
+    if (!strcmp(e, "INFO")) return 2;
+    if (!strcmp(e, "WARN")) return 1;
+    return atoi(e);
+  }();
+  return lvl;
+}
+
+#define COCO_WARN(...)                      \
+  do {                                      \
+    if (debug_level() >= 1) {               \
+      fprintf(stderr, "[coconet_rt] WARN ");\
+      fprintf(stderr, __VA_ARGS__);         \
+      fprintf(stderr, "\n");                \
+    }                                       \
+  } while (0)
+#define COCO_INFO(...)                      \
+  do {                                      \
+    if (debug_level() >= 2) {               \
+      fprintf(stderr, "[coconet_rt] INFO ");\
+      fprintf(stderr, __VA_ARGS__);         \
+      fprintf(stderr, "\n");                \
+    }                                       \
+  } while (0)
+
+#define CUDA_TRY(expr)                                                            \
+  do {                                                                            \
+    cudaError_t e_ = (expr);                                                      \
+    if (e_ != cudaSuccess) {                                                      \
+      COCO_WARN("%s:%d %s -> %s", __FILE__, __LINE__, #expr, cudaGetErrorString(e_)); \
+      (void)cudaGetLastError();                                                   \
+      return cocoCudaError;                                                       \
+    }                                                                             \
+  } while (0)
+
+#define COCO_TRY(expr)             \
+  do {                             \
+    int r_ = (expr);               \
+    if (r_ != cocoSuccess) return r_; \
+  } while (0)
+
+size_t dtype_size(cocoDataType_t t) {
+  switch (t) {
+    case cocoFloat32: return 4;
+    case cocoFloat16:
+    case cocoBfloat16: return 2;
+  }
+  return 0;
+}
+
+// A caller buffer that peers can address.  peer[r] is this rank's view of
+// rank r's buffer start (peer[rank] == base).
+struct Region {
+  char *base = nullptr;
+  size_t bytes = 0;
+  char *peer[kMaxRanks] = {};
+};
+
+struct IpcBlob {
+  cudaIpcMemHandle_t handle;
+  unsigned long long offset;  // of the registered pointer inside its allocation
+  unsigned long long bytes;
+  int valid;
+  int pad;
+};
+
+// One fused call waiting for its launch (single-process groups).
+struct PendingCall {
+  int opt = 0;
+  cocoDataType_t g_type = cocoFloat32, lp_type = cocoFloat16;
+  const void *g = nullptr;
+  float *w = nullptr;
+  void *w_lp = nullptr;
+  float *m = nullptr, *v = nullptr;
+  StepArgs sa = {};
+  cudaStream_t stream = nullptr;
+};
+
+struct LocalGroup;  // ranks that live in one process
+
+}  // namespace
+
+struct cocoComm {
+  int world = 1, rank = 0, device = 0;
+  int sm_count = 0;
+  bool coop_supported = false;
+  // process mode
+  std::unique_ptr<Bootstrap> boot;
+  std::vector<Region> regions;
+  std::map<std::string, void *> ipc_open;  // "<peer>:<handle bytes>" -> mapped base
+  // single-process mode
+  std::shared_ptr<LocalGroup> group;
+  bool has_pending = false;
+  PendingCall pending;
+  // both
+  FlagPage *flags = nullptr;
+  FlagPage *peer_flags[kMaxRanks] = {};
+  unsigned long long seq = 0;
+  unsigned long long launches = 0;
+  int ctas_per_sm = 0;  // 0 = automatic
+  int threads = 512;
+  int timeout_ms = 10000;
+};
+
+namespace {
+
+struct LocalGroup {
+  std::vector<cocoComm *> comms;         // index = rank
+  std::map<int, RankArgs *> table_dev;   // device -> table for virtual ranks
+  std::mutex mu;
+};
+
+thread_local int g_group_depth = 0;
+thread_local std::vector<cocoComm *> g_group_touched;
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) ok = false;
+    if (ok && prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+int init_common(cocoComm *c) {
+  cudaDeviceProp prop;
+  CUDA_TRY(cudaGetDeviceProperties(&prop, c->device));
+  c->sm_count = prop.multiProcessorCount;
+  c->coop_supported = prop.cooperativeLaunch != 0;
+  c->ctas_per_sm = env_int("COCO_CTAS_PER_SM", 0);
+  c->threads = env_int("COCO_THREADS", 512);
+  if (c->threads < 32 || c->threads > 512 || (c->threads % 32) != 0) c->threads = 512;
+  c->timeout_ms = env_int("COCO_TIMEOUT_MS", 10000);
+  if (c->timeout_ms <= 0) c->timeout_ms = 10000;
+  CUDA_TRY(cudaMalloc((void **)&c->flags, sizeof(FlagPage)));
+  CUDA_TRY(cudaMemset(c->flags, 0, sizeof(FlagPage)));
+  CUDA_TRY(cudaDeviceSynchronize());
+  c->peer_flags[c->rank] = c->flags;
+  return cocoSuccess;
+}
+
+// ---- process mode: CUDA IPC ------------------------------------------------
+int alloc_range(const void *ptr, char **base, size_t *size) {
+  // The driver entry point is looked up at run time so that the library has
+  // no link-time dependency on libcuda (it must load on machines without a
+  // driver, e.g. to list its symbols).
+  typedef CUresult (*GetRangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+  static GetRangeFn fn = [] {
+    void *f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &q) != cudaSuccess)
+      f = nullptr;
+    return (GetRangeFn)f;
+  }();
+  if (!fn) return cocoCudaError;
+  CUdeviceptr b = 0;
+  size_t s = 0;
+  CUresult r = fn(&b, &s, (CUdeviceptr)ptr);
+  if (r != CUDA_SUCCESS) return cocoInvalidArgument;
+  *base = (char *)b;
+  *size = s;
+  return cocoSuccess;
+}
+
+int map_region_ipc(cocoComm *c, void *ptr, size_t bytes, Region *out) {
+  IpcBlob mine;
+  memset(&mine, 0, sizeof(mine));
+  char *abase = nullptr;
+  size_t asize = 0;
+  int rc = alloc_range(ptr, &abase, &asize);
+  if (rc == cocoSuccess) {
+    cudaError_t e = cudaIpcGetMemHandle(&mine.handle, abase);
+    if (e == cudaSuccess) {
+      mine.offset = (unsigned long long)((char *)ptr - abase);
+      mine.bytes = bytes;
+      mine.valid = 1;
+    } else {
+      COCO_WARN("cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+      (void)cudaGetLastError();
+    }
+  }
+  // Always take part in the exchange so that a local failure cannot leave
+  // the peers blocked in the collective.
+  std::vector<IpcBlob> all(c->world);
+  COCO_TRY(c->boot->all_gather(&mine, all.data(), sizeof(IpcBlob)));
+  for (int r = 0; r < c->world; ++r)
+    if (!all[r].valid) return cocoCudaError;
+
+  out->base = (char *)ptr;
+  out->bytes = bytes;
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) {
+      out->peer[r] = (char *)ptr;
+      continue;
+    }
+    if (all[r].bytes < bytes) return cocoInvalidUsage;  // ranks disagree on the size
+    std::string key = std::to_string(r) + ":" +
+                      std::string((const char *)&all[r].handle, sizeof(cudaIpcMemHandle_t));
+    void *mapped = nullptr;
+    auto it = c->ipc_open.find(key);
+    if (it != c->ipc_open.end()) {
+      mapped = it->second;
+    } else {
+      cudaError_t e = cudaIpcOpenMemHandle(&mapped, all[r].handle, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        COCO_WARN("cudaIpcOpenMemHandle(rank %d): %s", r, cudaGetErrorString(e));
+        (void)cudaGetLastError();
+        return cocoPeerError;
+      }
+      c->ipc_open[key] = mapped;
+    }
+    out->peer[r] = (char *)mapped + all[r].offset;
+  }
+  return cocoSuccess;
+}
+
+const Region *find_region(const cocoComm *c, const void *ptr, size_t bytes) {
+  const char *p = (const char *)ptr;
+  for (const Region &r : c->regions)
+    if (p >= r.base && p + bytes <= r.base + r.bytes) return &r;
+  return nullptr;
+}
+
+// Peer views of [ptr, ptr+bytes); registers the buffer on first use.
+int peer_views(cocoComm *c, const void *ptr, size_t bytes, char *views[kMaxRanks]) {
+  if (c->world == 1) {
+    views[0] = (char *)ptr;
+    return cocoSuccess;
+  }
+  const Region *r = find_region(c, ptr, bytes);
+  if (!r) {
+    Region fresh;
+    COCO_TRY(map_region_ipc(c, (void *)ptr, bytes, &fresh));
+    c->regions.push_back(fresh);
+    r = &c->regions.back();
+    COCO_INFO("rank %d registered %p (+%zu bytes)", c->rank, ptr, bytes);
+  }
+  const size_t off = (const char *)ptr - r->base;
+  for (int p = 0; p < c->world; ++p) views[p] = r->peer[p] + off;
+  return cocoSuccess;
+}
+
+// ---- launch configuration ---------------------------------------------------
+bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
+
+int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
+                cocoDataType_t lp_type, size_t count, int world, int nvirt, LaunchConfig *cfg) {
+  int occ = 0;
+  CUDA_TRY(fused_step_occupancy(opt, g_type, has_lp, lp_type, c->threads, &occ));
+  if (occ < 1) return cocoInternalError;
+  const bool coop = (opt == kLAMB) || nvirt > 1;
+  if (coop && !c->coop_supported) return cocoInvalidUsage;
+  int per_sm = c->ctas_per_sm > 0 ? std::min(c->ctas_per_sm, occ) : std::min(occ, 2);
+  long ctas = (long)per_sm * c->sm_count;
+  if (nvirt > 1) ctas = std::max(1L, ((long)occ * c->sm_count) / nvirt);
+  // no more CTAs than there are 16-byte units in the slice
+  const size_t slice = (count + world - 1) / world;
+  const size_t vec = g_type == cocoFloat32 ? 4 : 8;
+  const size_t units = std::max<size_t>(1, (slice + vec - 1) / vec);
+  const long need = (long)((units + c->threads - 1) / c->threads);
+  ctas = std::max(1L, std::min(ctas, need));
+  ctas = std::min<long>(ctas, kMaxCtasPerRank);
+  cfg->ctas = (int)ctas;
+  cfg->threads = c->threads;
+  cfg->nvirt = nvirt;
+  cfg->cooperative = coop;
+  return cocoSuccess;
+}
+
+int validate(const cocoComm *c, const PendingCall &pc) {
+  if (!c || !pc.g || !pc.w) return cocoInvalidArgument;
+  if (dtype_size(pc.g_type) == 0) return cocoInvalidArgument;
+  if (pc.w_lp && pc.lp_type != cocoFloat16 && pc.lp_type != cocoBfloat16)
+    return cocoInvalidArgument;
+  if (pc.opt != kSGD && (!pc.m || !pc.v)) return cocoInvalidArgument;
+  if (pc.sa.variant < cocoVariantOverlap || pc.sa.variant > cocoVariantNccl)
+    return cocoInvalidArgument;
+  if (pc.sa.variant == cocoVariantNccl) {
+    // the forked-NCCL formulation is defined for fp16 gradients + fp16 copy only
+    if (pc.opt != kAdam || pc.g_type != cocoFloat16 || !pc.w_lp || pc.lp_type != cocoFloat16)
+      return cocoInvalidArgument;
+  }
+  if (pc.sa.variant == cocoVariantDsl && pc.opt == kAdam && !(pc.sa.beta1 != 0.f && pc.sa.beta2 != 0.f))
+    return cocoInvalidArgument;
+  return cocoSuccess;
+}
+
+void fill_rank_args(RankArgs *ra, int rank, int world, char *const g_views[], char *const out_views[],
+                    FlagPage *const flags[], const PendingCall &pc) {
+  memset(ra, 0, sizeof(*ra));
+  bool ok16 = aligned16(pc.w) && (pc.opt == kSGD || (aligned16(pc.m) && aligned16(pc.v)));
+  for (int p = 0; p < world; ++p) {
+    ra->g[p] = g_views[p];
+    ra->out[p] = out_views[p];
+    ra->flags[p] = flags[p];
+    ok16 = ok16 && aligned16(g_views[p]) && aligned16(out_views[p]);
+  }
+  ra->w = pc.w;
+  ra->m = pc.m;
+  ra->v = pc.v;
+  ra->rank = rank;
+  const size_t S = (pc.sa.count + world - 1) / world;
+  const size_t vec = pc.g_type == cocoFloat32 ? 4 : 8;
+  size_t lo = (size_t)rank * S;
+  if (lo > pc.sa.count) lo = pc.sa.count;
+  ra->pad = (ok16 && (lo % vec) == 0) ? 1 : 0;
+}
+
+// Launch of one rank that owns its device alone (process mode, or a
+// single-process rank with a device of its own).
+int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
+                  char *const out_views[]) {
+  RankArgs ra;
+  fill_rank_args(&ra, c->rank, c->world, g_views, out_views, c->peer_flags, pc);
+  LaunchConfig cfg;
+  COCO_TRY(pick_launch(c, pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, pc.sa.count,
+                       c->world, 1, &cfg));
+  CUDA_TRY(launch_fused_step(pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, pc.sa, ra, nullptr,
+                             cfg, pc.stream));
+  c->launches++;
+  return cocoSuccess;
+}
+
+// Launch every queued call of a single-process group: one launch per device;
+// ranks that share a device become virtual ranks of one cooperative launch.
+int flush_group(LocalGroup *grp) {
+  std::lock_guard<std::mutex> lock(grp->mu);
+  const int R = (int)grp->comms.size();
+  for (cocoComm *c : grp->comms)
+    if (!c->has_pending) return cocoInvalidUsage;  // every rank must have called
+  const PendingCall &first = grp->comms[0]->pending;
+  char *g_views[kMaxRanks], *out_views[kMaxRanks];
+  FlagPage *flags[kMaxRanks];
+  for (int r = 0; r < R; ++r) {
+    const PendingCall &pc = grp->comms[r]->pending;
+    if (pc.opt != first.opt || pc.g_type != first.g_type || pc.sa.count != first.sa.count ||
+        (pc.w_lp != nullptr) != (first.w_lp != nullptr) || pc.lp_type != first.lp_type ||
+        pc.sa.seq != first.sa.seq) {
+      for (cocoComm *c : grp->comms) c->has_pending = false;
+      return cocoInvalidUsage;  // ranks disagree on the operation
+    }
+    g_views[r] = (char *)pc.g;
+    out_views[r] = pc.w_lp ? (char *)pc.w_lp : (char *)pc.w;
+    flags[r] = grp->comms[r]->flags;
+  }
+  std::map<int, std::vector<int>> by_dev;
+  for (int r = 0; r < R; ++r) by_dev[grp->comms[r]->device].push_back(r);
+  int result = cocoSuccess;
+  for (auto &kv : by_dev) {
+    const std::vector<int> &ranks = kv.second;
+    cocoComm *lead = grp->comms[ranks[0]];
+    DeviceGuard guard(kv.first);
+    if (!guard.ok) {
+      result = cocoCudaError;
+      break;
+    }
+    const PendingCall &pc0 = lead->pending;
+    std::vector<RankArgs> host(ranks.size());
+    for (size_t k = 0; k < ranks.size(); ++k)
+      fill_rank_args(&host[k], ranks[k], R, g_views, out_views, flags,
+                     grp->comms[ranks[k]]->pending);
+    LaunchConfig cfg;
+    int rc = pick_launch(lead, pc0.opt, pc0.g_type, pc0.w_lp != nullptr, pc0.lp_type,
+                         pc0.sa.count, R, (int)ranks.size(), &cfg);
+    if (rc != cocoSuccess) {
+      result = rc;
+      break;
+    }
+    RankArgs *table = nullptr;
+    if (ranks.size() > 1) {
+      RankArgs *&slot = grp->table_dev[kv.first];
+      if (!slot && cudaMalloc((void **)&slot, sizeof(RankArgs) * kMaxRanks) != cudaSuccess) {
+        result = cocoCudaError;
+        break;
+      }
+      table = slot;
+      // pageable source: the copy is staged before this call returns
+      if (cudaMemcpyAsync(table, host.data(), sizeof(RankArgs) * ranks.size(),
+                          cudaMemcpyHostToDevice, pc0.stream) != cudaSuccess) {
+        result = cocoCudaError;
+        break;
+      }
+    }
+    cudaError_t e = launch_fused_step(pc0.opt, pc0.g_type, pc0.w_lp != nullptr, pc0.lp_type,
+                                      pc0.sa, host[0], table, cfg, pc0.stream);
+    if (e != cudaSuccess) {
+      COCO_WARN("launch failed: %s", cudaGetErrorString(e));
+      (void)cudaGetLastError();
+      result = cocoCudaError;
+      break;
+    }
+    lead->launches++;
+  }
+  for (cocoComm *c : grp->comms) c->has_pending = false;
+  return result;
+}
+
+int enqueue(cocoComm *c, PendingCall &pc) {
+  COCO_TRY(validate(c, pc));
+  if (pc.sa.count == 0) return cocoSuccess;
+  pc.sa.world = c->world;
+  pc.sa.seq = ++c->seq;
+  pc.sa.timeout_ns = (unsigned long long)c->timeout_ms * 1000000ull;
+
+  if (c->group) {  // single-process: wait until every rank of the group has called
+    if (c->has_pending) return cocoInvalidUsage;
+    c->pending = pc;
+    c->has_pending = true;
+    if (g_group_depth > 0) {
+      if (std::find(g_group_touched.begin(), g_group_touched.end(), c) == g_group_touched.end())
+        g_group_touched.push_back(c);
+      return cocoSuccess;
+    }
+    for (cocoComm *o : c->group->comms)
+      if (!o->has_pending) return cocoSuccess;  // more ranks to come
+    return flush_group(c->group.get());
+  }
+
+  DeviceGuard guard(c->device);
+  if (!guard.ok) return cocoCudaError;
+  char *g_views[kMaxRanks] = {}, *out_views[kMaxRanks] = {};
+  COCO_TRY(peer_views(c, pc.g, pc.sa.count * dtype_size(pc.g_type), g_views));
+  if (pc.w_lp)
+    COCO_TRY(peer_views(c, pc.w_lp, pc.sa.count * dtype_size(pc.lp_type), out_views));
+  else
+    COCO_TRY(peer_views(c, pc.w, pc.sa.count * sizeof(float), out_views));
+  return launch_single(c, pc, g_views, out_views);
+}
+
+void set_denominators(StepArgs *sa, int opt, int step) {
+  // m^ = m/d1, v^ = v/d2.  overlap: 1 - beta^t evaluated in double as the
+  // reference's host check does (multi-process-adam-scattered.cpp:118-119);
+  // dsl Adam / nccl: beta (adam.cpp:68-69, reduce_kernel.h:33-47);
+  // dsl LAMB: 1 - beta (lamb.cpp:82-83).
+  sa->d1d = sa->d2d = 1.0;
+  if (sa->variant == cocoVariantOverlap) {
+    sa->d1d = 1.0 - std::pow((double)sa->beta1, (double)(step + 1));
+    sa->d2d = 1.0 - std::pow((double)sa->beta2, (double)(step + 1));
+    sa->d1 = (float)sa->d1d;
+    sa->d2 = (float)sa->d2d;
+  } else if (opt == kLAMB) {
+    sa->d1 = 1.0f - sa->beta1;
+    sa->d2 = 1.0f - sa->beta2;
+  } else {
+    sa->d1 = sa->beta1;
+    sa->d2 = sa->beta2;
+  }
+}
+
+}  // namespace
+
+// ============================================================================
+// C ABI
+// ============================================================================
+extern "C" {
+
+int cocoGetVersion(int *version) {
+  if (!version) return cocoInvalidArgument;
+  *version = COCO_VERSION;
+  return cocoSuccess;
+}
+
+const char *cocoErrorString(int result) {
+  switch (result) {
+    case cocoSuccess: return "success";
+    case cocoInvalidArgument: return "invalid argument";
+    case cocoInvalidUsage: return "invalid usage";
+    case cocoCudaError: return "CUDA error";
+    case cocoSystemError: return "system error (bootstrap)";
+    case cocoTimeout: return "timed out waiting for a peer";
+    case cocoPeerError: return "no peer access";
+    case cocoInternalError: return "internal error";
+  }
+  return "unknown result code";
+}
+
+int cocoSliceBounds(size_t count, int world, int rank, size_t *begin, size_t *end) {
+  if (world < 1 || rank < 0 || rank >= world || !begin || !end) return cocoInvalidArgument;
+  const size_t S = (count + world - 1) / world;
+  size_t lo = (size_t)rank * S;
+  if (lo > count) lo = count;
+  size_t hi = lo + S;
+  if (hi > count) hi = count;
+  *begin = lo;
+  *end = hi;
+  return cocoSuccess;
+}
+
+int cocoCommInitRank(cocoComm_t *comm, int world, int rank, const char *bootstrap) {
+  if (!comm || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return cocoInvalidArgument;
+  std::unique_ptr<cocoComm> c(new cocoComm);
+  c->world = world;
+  c->rank = rank;
+  CUDA_TRY(cudaGetDevice(&c->device));
+  CUDA_TRY(cudaFree(0));
+  c->boot.reset(new Bootstrap);
+  const int boot_timeout = env_int("COCO_BOOTSTRAP_TIMEOUT_MS", 120000);
+  COCO_TRY(c->boot->init(world, rank, resolve_bootstrap_addr(bootstrap), boot_timeout));
+  int rc = init_common(c.get());
+  // agree on success before anyone maps anything
+  std::vector<int> rcs(world);
+  COCO_TRY(c->boot->all_gather(&rc, rcs.data(), sizeof(int)));
+  for (int r : rcs)
+    if (r != cocoSuccess) return r;
+  if (world > 1) {
+    Region reg;
+    COCO_TRY(map_region_ipc(c.get(), c->flags, sizeof(FlagPage), &reg));
+    for (int p = 0; p < world; ++p) c->peer_flags[p] = (FlagPage *)reg.peer[p];
+    COCO_TRY(c->boot->barrier());
+  }
+  COCO_INFO("rank %d/%d on device %d (%d SMs) ready", rank, world, c->device, c->sm_count);
+  *comm = c.release();
+  return cocoSuccess;
+}
+
+int cocoCommInitAll(cocoComm_t *comms, int n, const int *devices) {
+  if (!comms || n < 1 || n > kMaxRanks) return cocoInvalidArgument;
+  int ndev = 0;
+  CUDA_TRY(cudaGetDeviceCount(&ndev));
+  std::vector<int> devs(n);
+  for (int r = 0; r < n; ++r) {
+    devs[r] = devices ? devices[r] : r;
+    if (devs[r] < 0 || devs[r] >= ndev) return cocoInvalidArgument;
+  }
+  int prev = 0;
+  CUDA_TRY(cudaGetDevice(&prev));
+  auto grp = std::make_shared<LocalGroup>();
+  std::vector<std::unique_ptr<cocoComm>> made;
+  int rc = cocoSuccess;
+  for (int r = 0; r < n && rc == cocoSuccess; ++r) {
+    std::unique_ptr<cocoComm> c(new cocoComm);
+    c->world = n;
+    c->rank = r;
+    c->device = devs[r];
+    if (cudaSetDevice(devs[r]) != cudaSuccess) {
+      rc = cocoCudaError;
+      break;
+    }
+    rc = init_common(c.get());
+    made.push_back(std::move(c));
+  }
+  // peer access between distinct devices
+  for (int a = 0; a < n && rc == cocoSuccess; ++a)
+    for (int b = 0; b < n && rc == cocoSuccess; ++b) {
+      if (devs[a] == devs[b]) continue;
+      int can = 0;
+      if (cudaDeviceCanAccessPeer(&can, devs[a], devs[b]) != cudaSuccess || !can) {
+        rc = cocoPeerError;
+        break;
+      }
+      cudaSetDevice(devs[a]);
+      cudaError_t e = cudaDeviceEnablePeerAccess(devs[b], 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+      } else if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        rc = cocoPeerError;
+      }
+    }
+  cudaSetDevice(prev);
+  if (rc != cocoSuccess) {
+    for (auto &c : made)
+      if (c->flags) cudaFree(c->flags);
+    return rc;
+  }
+  for (int r = 0; r < n; ++r) {
+    made[r]->group = n > 1 ? grp : nullptr;
+    for (int p = 0; p < n; ++p) made[r]->peer_flags[p] = made[p]->flags;
+  }
+  for (int r = 0; r < n; ++r) {
+    grp->comms.push_back(made[r].get());
+    comms[r] = made[r].release();
+  }
+  return cocoSuccess;
+}
+
+int cocoCommDestroy(cocoComm_t comm) {
+  if (!comm) return cocoInvalidArgument;
+  DeviceGuard guard(comm->device);
+  cudaDeviceSynchronize();
+  for (auto &kv : comm->ipc_open) cudaIpcCloseMemHandle(kv.second);
+  if (comm->group) {
+    std::lock_guard<std::mutex> lock(comm->group->mu);
+    auto &v = comm->group->comms;
+    // the last member frees what the group owns
+    bool last = true;
+    for (cocoComm *&o : v) {
+      if (o == comm) o = nullptr;
+      if (o) last = false;
+    }
+    if (last)
+      for (auto &kv : comm->group->table_dev) {
+        DeviceGuard g2(kv.first);
+        cudaFree(kv.second);
+      }
+  }
+  if (comm->flags) cudaFree(comm->flags);
+  (void)cudaGetLastError();
+  delete comm;
+  return cocoSuccess;
+}
+
+int cocoCommCount(cocoComm_t comm, int *world) {
+  if (!comm || !world) return cocoInvalidArgument;
+  *world = comm->world;
+  return cocoSuccess;
+}
+int cocoCommUserRank(cocoComm_t comm, int *rank) {
+  if (!comm || !rank) return cocoInvalidArgument;
+  *rank = comm->rank;
+  return cocoSuccess;
+}
+int cocoCommCuDevice(cocoComm_t comm, int *device) {
+  if (!comm || !device) return cocoInvalidArgument;
+  *device = comm->device;
+  return cocoSuccess;
+}
+
+int cocoBarrier(cocoComm_t comm) {
+  if (!comm) return cocoInvalidArgument;
+  if (comm->boot) return comm->boot->barrier();
+  return cocoSuccess;  // single-process groups share one host thread of control
+}
+
+int cocoAllGatherHost(cocoComm_t comm, const void *send, void *recv, size_t bytes_per_rank) {
+  if (!comm || !send || !recv) return cocoInvalidArgument;
+  if (comm->boot) return comm->boot->all_gather(send, recv, bytes_per_rank);
+  if (comm->world == 1) {
+    if (send != recv) memcpy(recv, send, bytes_per_rank);
+    return cocoSuccess;
+  }
+  return cocoInvalidUsage;
+}
+
+int cocoGroupStart(void) {
+  ++g_group_depth;
+  return cocoSuccess;
+}
+
+int cocoGroupEnd(void) {
+  if (g_group_depth <= 0) return cocoInvalidUsage;
+  if (--g_group_depth > 0) return cocoSuccess;
+  std::vector<cocoComm *> touched;
+  touched.swap(g_group_touched);
+  int result = cocoSuccess;
+  std::vector<LocalGroup *> done;
+  for (cocoComm *c : touched) {
+    if (!c->group) continue;
+    LocalGroup *g = c->group.get();
+    if (std::find(done.begin(), done.end(), g) != done.end()) continue;
+    done.push_back(g);
+    int rc = flush_group(g);
+    if (rc != cocoSuccess && result == cocoSuccess) result = rc;
+  }
+  return result;
+}
+
+int cocoRegister(cocoComm_t comm, void *ptr, size_t bytes) {
+  if (!comm || !ptr || bytes == 0) return cocoInvalidArgument;
+  if (comm->world == 1 || comm->group) return cocoSuccess;  // one address space: nothing to map
+  if (find_region(comm, ptr, bytes)) return cocoSuccess;
+  DeviceGuard guard(comm->device);
+  Region reg;
+  COCO_TRY(map_region_ipc(comm, ptr, bytes, &reg));
+  comm->regions.push_back(reg);
+  return cocoSuccess;
+}
+
+int cocoDeregister(cocoComm_t comm, void *ptr) {
+  if (!comm || !ptr) return cocoInvalidArgument;
+  auto &v = comm->regions;
+  for (size_t k = 0; k < v.size(); ++k)
+    if (v[k].base == (char *)ptr) {
+      v.erase(v.begin() + k);
+      return cocoSuccess;
+    }
+  return (comm->world == 1 || comm->group) ? cocoSuccess : cocoInvalidArgument;
+}
+
+int cocoFusedSGD(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w, void *w_lp,
+                 cocoDataType_t lp_type, size_t count, float lr, float grad_scale,
+                 cocoStream_t stream) {
+  if (!comm) return cocoInvalidArgument;
+  PendingCall pc;
+  pc.opt = kSGD;
+  pc.g = g, pc.g_type = g_type, pc.w = w, pc.w_lp = w_lp, pc.lp_type = lp_type;
+  pc.sa.count = count;
+  pc.sa.lr = lr;
+  pc.sa.grad_scale = grad_scale;
+  pc.sa.variant = cocoVariantOverlap;
+  pc.sa.d1 = pc.sa.d2 = 1.f;
+  pc.sa.d1d = pc.sa.d2d = 1.0;
+  pc.stream = (cudaStream_t)stream;
+  return enqueue(comm, pc);
+}
+
+int cocoFusedAdam(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w, void *w_lp,
+                  cocoDataType_t lp_type, float *m, float *v, size_t count, float lr,
+                  float beta1, float beta2, float eps, int step, float grad_scale,
+                  cocoVariant_t variant, cocoStream_t stream) {
+  if (!comm || step < 0) return cocoInvalidArgument;
+  PendingCall pc;
+  pc.opt = kAdam;
+  pc.g = g, pc.g_type = g_type, pc.w = w, pc.w_lp = w_lp, pc.lp_type = lp_type;
+  pc.m = m, pc.v = v;
+  pc.sa.count = count;
+  pc.sa.lr = lr, pc.sa.beta1 = beta1, pc.sa.beta2 = beta2;
+  // only the bias-corrected form has an epsilon (reduce_kernel.h:243 of
+  // nccl-overlap); the other two divide by v^ / sqrt(v^) directly
+  pc.sa.eps = variant == cocoVariantOverlap ? eps : 0.f;
+  pc.sa.grad_scale = grad_scale;
+  pc.sa.variant = (int)variant;
+  set_denominators(&pc.sa, kAdam, step);
+  pc.stream = (cudaStream_t)stream;
+  return enqueue(comm, pc);
+}
+
+int cocoFusedLAMB(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w, void *w_lp,
+                  cocoDataType_t lp_type, float *m, float *v, size_t count, float lr,
+                  float beta1, float beta2, float eps, float weight_decay, int step,
+                  float grad_scale, cocoVariant_t variant, unsigned flags, cocoStream_t stream) {
+  if (!comm || step < 0 || variant == cocoVariantNccl) return cocoInvalidArgument;
+  PendingCall pc;
+  pc.opt = kLAMB;
+  pc.g = g, pc.g_type = g_type, pc.w = w, pc.w_lp = w_lp, pc.lp_type = lp_type;
+  pc.m = m, pc.v = v;
+  pc.sa.count = count;
+  pc.sa.lr = lr, pc.sa.beta1 = beta1, pc.sa.beta2 = beta2;
+  pc.sa.eps = variant == cocoVariantOverlap ? eps : 0.f;  // lamb.cpp:72,84: epsilon unused
+  pc.sa.weight_decay = weight_decay;
+  pc.sa.grad_scale = grad_scale;
+  pc.sa.variant = (int)variant;
+  pc.sa.flags = flags;
+  set_denominators(&pc.sa, kLAMB, step);
+  pc.stream = (cudaStream_t)stream;
+  return enqueue(comm, pc);
+}
+
+int cocoLastLambNorms(cocoComm_t comm, double out[2]) {
+  if (!comm || !out) return cocoInvalidArgument;
+  DeviceGuard guard(comm->device);
+  CUDA_TRY(cudaMemcpy(out, comm->flags->last_norms, 2 * sizeof(double), cudaMemcpyDeviceToHost));
+  return cocoSuccess;
+}
+
+int cocoGetStatus(cocoComm_t comm, cocoStatus_t *status) {
+  if (!comm || !status) return cocoInvalidArgument;
+  DeviceGuard guard(comm->device);
+  int raw[8];
+  CUDA_TRY(cudaMemcpy(raw, comm->flags->status, sizeof(raw), cudaMemcpyDeviceToHost));
+  status->code = raw[0];
+  status->rank = raw[1];
+  status->phase = raw[2];
+  status->peer = raw[3];
+  status->seq = ((uint64_t)(unsigned)raw[5] << 32) | (unsigned)raw[4];
+  if (raw[0] != 0) CUDA_TRY(cudaMemset(comm->flags->status, 0, sizeof(raw)));
+  return cocoSuccess;
+}
+
+int cocoSetTunables(cocoComm_t comm, int ctas_per_sm, int threads, int timeout_ms) {
+  if (!comm) return cocoInvalidArgument;
+  if (ctas_per_sm > 0) comm->ctas_per_sm = ctas_per_sm;
+  if (threads > 0) {
+    if (threads < 32 || threads > 512 || (threads % 32) != 0) return cocoInvalidArgument;
+    comm->threads = threads;
+  }
+  if (timeout_ms > 0) comm->timeout_ms = timeout_ms;
+  return cocoSuccess;
+}
+
+int cocoLaunchCount(cocoComm_t comm, uint64_t *launches) {
+  if (!comm || !launches) return cocoInvalidArgument;
+  *launches = comm->launches;
+  return cocoSuccess;
+}
+
+}  // extern "C"

@@ -1,0 +1,223 @@
+"""ctypes host layer over libcoconet_rt.so (see include/coconet_rt.h).
+
+Tensors are torch CUDA tensors; only their device pointers cross the C ABI.
+"""
+import contextlib
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+VARIANT_OVERLAP, VARIANT_DSL, VARIANT_NCCL = 0, 1, 2
+LAMB_REF_QUIRK = 0x1
+_F16, _F32, _BF16 = 6, 7, 9
+
+
+class CocoError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        super().__init__(f"{what}: {error_string(code)} ({code})")
+
+
+class _Status(C.Structure):
+    _fields_ = [("code", C.c_int), ("rank", C.c_int), ("phase", C.c_int), ("peer", C.c_int),
+                ("seq", C.c_uint64)]
+
+
+def library_path():
+    return os.path.join(HERE, "libcoconet_rt.so")
+
+
+_lib = None
+
+# name -> (restype, argtypes); also the list the symbol-export test checks.
+_SIGNATURES = {
+    "cocoGetVersion": (C.c_int, [C.POINTER(C.c_int)]),
+    "cocoErrorString": (C.c_char_p, [C.c_int]),
+    "cocoCommInitRank": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_char_p]),
+    "cocoCommInitAll": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_int)]),
+    "cocoCommDestroy": (C.c_int, [C.c_void_p]),
+    "cocoCommCount": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "cocoCommUserRank": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "cocoCommCuDevice": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "cocoBarrier": (C.c_int, [C.c_void_p]),
+    "cocoAllGatherHost": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "cocoGroupStart": (C.c_int, []),
+    "cocoGroupEnd": (C.c_int, []),
+    "cocoRegister": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "cocoDeregister": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "cocoFusedSGD": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                               C.c_size_t, C.c_float, C.c_float, C.c_void_p]),
+    "cocoFusedAdam": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
+                                C.c_float, C.c_float, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "cocoFusedLAMB": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
+                                C.c_float, C.c_float, C.c_float, C.c_int, C.c_float, C.c_int,
+                                C.c_uint, C.c_void_p]),
+    "cocoLastLambNorms": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
+    "cocoGetStatus": (C.c_int, [C.c_void_p, C.POINTER(_Status)]),
+    "cocoSliceBounds": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_size_t),
+                                  C.POINTER(C.c_size_t)]),
+    "cocoSetTunables": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "cocoLaunchCount": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
+}
+
+
+def lib():
+    """The loaded C-ABI library.  Raises if it has not been built: there is no
+    fallback path."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise ImportError(
+                f"{path} is missing: build it with `python -m coconet_b200.build` "
+                "(or __graft_entry__.build()); coconet_b200 has no fallback path")
+        L = C.CDLL(path)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def error_string(code):
+    return lib().cocoErrorString(code).decode()
+
+
+def _check(code, what):
+    if code != 0:
+        raise CocoError(code, what)
+
+
+def slice_bounds(count, world, rank):
+    lo, hi = C.c_size_t(), C.c_size_t()
+    _check(lib().cocoSliceBounds(count, world, rank, C.byref(lo), C.byref(hi)), "cocoSliceBounds")
+    return lo.value, hi.value
+
+
+@contextlib.contextmanager
+def group():
+    """Fused calls issued inside are launched together on exit (needed when
+    several ranks of a single-process communicator share one GPU)."""
+    _check(lib().cocoGroupStart(), "cocoGroupStart")
+    try:
+        yield
+    finally:
+        _check(lib().cocoGroupEnd(), "cocoGroupEnd")
+
+
+def _dtype_code(t):
+    import torch
+    return {torch.float32: _F32, torch.float16: _F16, torch.bfloat16: _BF16}[t.dtype]
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(stream):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+class Communicator:
+    """One rank of a fused-step communicator (wraps cocoComm_t)."""
+
+    def __init__(self, handle, world, rank):
+        self._h = C.c_void_p(handle)
+        self.world = world
+        self.rank = rank
+
+    # ---- construction ----
+    @classmethod
+    def init_rank(cls, world, rank, bootstrap=None):
+        """One process per GPU; the current CUDA device becomes the rank's."""
+        h = C.c_void_p()
+        addr = bootstrap.encode() if bootstrap else None
+        _check(lib().cocoCommInitRank(C.byref(h), world, rank, addr), "cocoCommInitRank")
+        return cls(h.value, world, rank)
+
+    @classmethod
+    def init_all(cls, n, devices=None):
+        """All ranks in this process; a device listed twice hosts virtual ranks."""
+        hs = (C.c_void_p * n)()
+        devs = (C.c_int * n)(*devices) if devices is not None else None
+        _check(lib().cocoCommInitAll(hs, n, devs), "cocoCommInitAll")
+        return [cls(hs[r], n, r) for r in range(n)]
+
+    @classmethod
+    def from_torch_distributed(cls, pg=None):
+        """Rendezvous through an initialised torch.distributed group: rank 0
+        picks a free port and broadcasts it."""
+        import socket
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(pg), dist.get_rank(pg)
+        box = [None]
+        if rank == 0:
+            s = socket.socket()
+            s.bind(("127.0.0.1", 0))
+            box[0] = s.getsockname()[1]
+            s.close()
+        dist.broadcast_object_list(box, src=0, group=pg)
+        host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+        return cls.init_rank(world, rank, f"{host}:{box[0]}")
+
+    def destroy(self):
+        if self._h:
+            lib().cocoCommDestroy(self._h)
+            self._h = None
+
+    # ---- host-side collectives ----
+    def barrier(self):
+        _check(lib().cocoBarrier(self._h), "cocoBarrier")
+
+    def register(self, t):
+        _check(lib().cocoRegister(self._h, _ptr(t), t.numel() * t.element_size()), "cocoRegister")
+
+    def set_tunables(self, ctas_per_sm=0, threads=0, timeout_ms=0):
+        _check(lib().cocoSetTunables(self._h, ctas_per_sm, threads, timeout_ms), "cocoSetTunables")
+
+    # ---- the fused step ----
+    def _lp(self, w_lp):
+        return (_ptr(w_lp), _dtype_code(w_lp)) if w_lp is not None else (None, _F16)
+
+    def fused_sgd(self, g, w, lr, w_lp=None, grad_scale=1.0, stream=None):
+        lp, lpt = self._lp(w_lp)
+        _check(lib().cocoFusedSGD(self._h, _ptr(g), _dtype_code(g), _ptr(w), lp, lpt, w.numel(),
+                                  lr, grad_scale, _stream(stream)), "cocoFusedSGD")
+
+    def fused_adam(self, g, w, m, v, lr, beta1, beta2, eps, step, w_lp=None, grad_scale=1.0,
+                   variant=VARIANT_OVERLAP, stream=None):
+        lp, lpt = self._lp(w_lp)
+        _check(lib().cocoFusedAdam(self._h, _ptr(g), _dtype_code(g), _ptr(w), lp, lpt, _ptr(m),
+                                   _ptr(v), w.numel(), lr, beta1, beta2, eps, step, grad_scale,
+                                   variant, _stream(stream)), "cocoFusedAdam")
+
+    def fused_lamb(self, g, w, m, v, lr, beta1, beta2, eps, weight_decay, step, w_lp=None,
+                   grad_scale=1.0, variant=VARIANT_OVERLAP, flags=0, stream=None):
+        lp, lpt = self._lp(w_lp)
+        _check(lib().cocoFusedLAMB(self._h, _ptr(g), _dtype_code(g), _ptr(w), lp, lpt, _ptr(m),
+                                   _ptr(v), w.numel(), lr, beta1, beta2, eps, weight_decay, step,
+                                   grad_scale, variant, flags, _stream(stream)), "cocoFusedLAMB")
+
+    # ---- introspection ----
+    def status(self):
+        """First device-side failure since the last call, as a dict (code 0 =
+        none).  Synchronise the stream first."""
+        s = _Status()
+        _check(lib().cocoGetStatus(self._h, C.byref(s)), "cocoGetStatus")
+        return {"code": s.code, "rank": s.rank, "phase": s.phase, "peer": s.peer, "seq": s.seq}
+
+    def last_lamb_norms(self):
+        out = (C.c_double * 2)()
+        _check(lib().cocoLastLambNorms(self._h, out), "cocoLastLambNorms")
+        return out[0], out[1]
+
+    def launch_count(self):
+        n = C.c_uint64()
+        _check(lib().cocoLaunchCount(self._h, C.byref(n)), "cocoLaunchCount")
+        return n.value

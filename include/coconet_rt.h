@@ -1,0 +1,189 @@
+/*
+ * coconet_rt — C ABI of the B200 runtime for CoCoNet's fused AllReduce
+ * optimizer step:  ReduceScatter(sum) of Local gradients  ->  sliced
+ * SGD / Adam / LAMB update  ->  AllGather of the Replicated weights, as ONE
+ * kernel per step per GPU over NVLink peer memory.
+ *
+ * It replaces, for this one call, the reference's patched NCCL 2.6.4 fork.
+ * Reference interfaces are cited as file:line inside parasailteam/coconet.
+ *
+ * Conventions
+ *  - plain C: pointers and sizes only; every entry point returns an int
+ *    (cocoSuccess == 0), never throws, never terminates the process.
+ *  - one communicator per GPU per process (or several per process through
+ *    cocoCommInitAll); all ranks call the collective entry points in the same
+ *    order, like NCCL.  One fused operation in flight per communicator.
+ *  - data layout: N elements, world size R, S = ceil(N/R); rank r owns the
+ *    contiguous slice [r*S, min(N,(r+1)*S)) — the element count the reference
+ *    gives a `Sliced` tensor (src/codegen.cpp:139-165).
+ *      g      Local       N elements per rank (fp32 | fp16 | bf16), read-only
+ *      w      Replicated  N fp32.  Without w_lp it is gathered to all ranks;
+ *                         with w_lp only the own slice (the fp32 master) is
+ *                         updated, indexed by global element like the
+ *                         reference (all_reduce_computation.h:110)
+ *      w_lp   Replicated  N fp16/bf16 copy of w, gathered to all ranks; or NULL
+ *      m, v   Sliced      S fp32 per rank, indexed from the slice start
+ *                         (examples/adam/adam.cpp:62-63)
+ *  - buffers read or written by peers (g, and w or w_lp) are peer-mapped on
+ *    first use (a collective host-side exchange) unless registered before
+ *    with cocoRegister.
+ *  - every device-side wait is bounded (COCO_TIMEOUT_MS, default 10000); on
+ *    expiry the kernel records {code, rank, phase, peer} in a host-visible
+ *    status word and returns.  Read it with cocoGetStatus after synchronising
+ *    the stream.
+ */
+#ifndef COCONET_RT_H_
+#define COCONET_RT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COCO_VERSION 100
+#define COCO_MAX_RANKS 8
+
+typedef struct cocoComm *cocoComm_t;
+
+/* CUDA stream handle (cudaStream_t) passed as an opaque pointer so that this
+ * header needs no CUDA include. */
+typedef void *cocoStream_t;
+
+typedef enum {
+  cocoSuccess = 0,
+  cocoInvalidArgument = 1,
+  cocoInvalidUsage = 2,
+  cocoCudaError = 3,
+  cocoSystemError = 4,   /* sockets / bootstrap */
+  cocoTimeout = 5,       /* a bounded device- or host-side wait expired */
+  cocoPeerError = 6,     /* no peer access between two ranks */
+  cocoInternalError = 7,
+  cocoNumResults = 8
+} cocoResult_t;
+
+/* Element types; values of the first three match ncclDataType_t's
+ * ncclFloat32 = 7, ncclFloat16 = 6, ncclBfloat16 = 9 so that emitted
+ * programs can pass either (nccl/src/nccl.h.in:104-118). */
+typedef enum { cocoFloat16 = 6, cocoFloat32 = 7, cocoBfloat16 = 9 } cocoDataType_t;
+
+/* Which of the reference's three formulations the update evaluates. */
+typedef enum {
+  /* bias-corrected, eps in the denominator:  nccl-overlap/src/collectives/
+   * device/reduce_kernel.h:143-246; host check nccl-overlap/samples/
+   * multi-process-adam-scattered.cpp:112-123 (Adam), 402-435 (LAMB). */
+  cocoVariantOverlap = 0,
+  /* the DSL programs as written: examples/adam/adam.cpp:65-71 and its frozen
+   * check examples/test-adam.cu:14-38; examples/lamb/lamb.cpp:79-88. */
+  cocoVariantDsl = 1,
+  /* the forked-NCCL functors, fp16 gradient sum in ring order included:
+   * nccl/src/collectives/device/reduce_kernel.h:27-62,
+   * common_kernel.h:853-923.  Needs fp16 gradients and w_lp. */
+  cocoVariantNccl = 2
+} cocoVariant_t;
+
+/* flags */
+#define COCO_LAMB_REF_QUIRK 0x1u /* scale = trust/||r||, norms of the mean
+                                    square (multi-process-adam-scattered.cpp:
+                                    415-433); for known-answer tests only */
+
+typedef struct {
+  int code;        /* cocoResult_t of the first device-side failure, 0 if none */
+  int rank;        /* rank that recorded it */
+  int phase;       /* 1 start barrier, 2 norm exchange, 3 end barrier */
+  int peer;        /* peer rank that was waited for, -1 if n/a */
+  uint64_t seq;    /* sequence number of the fused call */
+} cocoStatus_t;
+
+int cocoGetVersion(int *version);
+const char *cocoErrorString(int result);
+
+/* ---- communicators ------------------------------------------------------
+ * Replaces ncclGetUniqueId + MPI_Bcast + ncclCommInitRank in the emitted
+ * main() (src/codegen.cpp:4587-4601).  `bootstrap` is "host:port" of a TCP
+ * rendezvous that rank 0 listens on; NULL reads COCO_BOOTSTRAP, else
+ * MASTER_ADDR:MASTER_PORT+1.  The calling thread's current CUDA device
+ * becomes the communicator's device. */
+int cocoCommInitRank(cocoComm_t *comm, int world, int rank, const char *bootstrap);
+
+/* Single-process variant (counterpart of ncclCommInitAll, used by
+ * nccl-overlap/samples/single-process-adam-scattered.cu:179-281).  devices[i]
+ * is the CUDA device of rank i; NULL means 0..n-1.  The same device may be
+ * listed several times: those ranks become virtual ranks whose fused calls,
+ * issued between cocoGroupStart/cocoGroupEnd, run as ONE cooperative launch
+ * (kernels that wait for one another must never be separate launches on one
+ * GPU). */
+int cocoCommInitAll(cocoComm_t *comms, int n, const int *devices);
+
+int cocoCommDestroy(cocoComm_t comm);
+int cocoCommCount(cocoComm_t comm, int *world);
+int cocoCommUserRank(cocoComm_t comm, int *rank);
+int cocoCommCuDevice(cocoComm_t comm, int *device);
+
+/* Host-side barrier and all-gather of small blobs over the bootstrap (what
+ * the emitted programs used MPI_Barrier / MPI_Bcast for). */
+int cocoBarrier(cocoComm_t comm);
+int cocoAllGatherHost(cocoComm_t comm, const void *send, void *recv, size_t bytes_per_rank);
+
+/* Like ncclGroupStart/End: fused calls issued in between are launched at
+ * cocoGroupEnd.  Required when several ranks share one device. */
+int cocoGroupStart(void);
+int cocoGroupEnd(void);
+
+/* Collective.  Peer-maps [ptr, ptr+bytes) for the other ranks (CUDA IPC
+ * between processes; peer access inside one process), the counterpart of the
+ * reference's P2P transport set-up (nccl/src/transport/p2p.cc:118-238). */
+int cocoRegister(cocoComm_t comm, void *ptr, size_t bytes);
+int cocoDeregister(cocoComm_t comm, void *ptr);
+
+/* ---- the fused step -----------------------------------------------------
+ * All three enqueue one kernel on `stream` and return.  grad_scale multiplies
+ * the reduced gradient (1/loss_scale for mixed precision; pass 1.0f else).
+ * step counts from 0 (the reference's `epoch`; t = step + 1). */
+
+/* w' = w - lr * sum_r g_r   (examples/sgd/sgd.cpp:45-47, test-sgd.cu:17-23) */
+int cocoFusedSGD(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w, void *w_lp,
+                 cocoDataType_t lp_type, size_t count, float lr, float grad_scale,
+                 cocoStream_t stream);
+
+/* Replaces AllReduce_pipe(lr,beta1,beta2,g,w,halfw,m,v,count,...)
+ * (nccl/src/nccl.h.in:211-212, nccl/src/collectives/all_reduce.cc:41-48). */
+int cocoFusedAdam(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w, void *w_lp,
+                  cocoDataType_t lp_type, float *m, float *v, size_t count, float lr,
+                  float beta1, float beta2, float eps, int step, float grad_scale,
+                  cocoVariant_t variant, cocoStream_t stream);
+
+/* Replaces the LAMB form AllReduce_pipe(...,m,v,r,count,...)
+ * (nccl/src/nccl.h.in:214-215, all_reduce.cc:50-58).  No `r` buffer is
+ * needed: r is recomputed from m, v, w in the second phase, as the
+ * reference's host checker does (multi-process-adam-scattered.cpp:427-431). */
+int cocoFusedLAMB(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w, void *w_lp,
+                  cocoDataType_t lp_type, float *m, float *v, size_t count, float lr,
+                  float beta1, float beta2, float eps, float weight_decay, int step,
+                  float grad_scale, cocoVariant_t variant, unsigned flags, cocoStream_t stream);
+
+/* Norms of the last LAMB step on this communicator: out[0] = ||w||,
+ * out[1] = ||r|| as used for the trust ratio.  Synchronise the stream first. */
+int cocoLastLambNorms(cocoComm_t comm, double out[2]);
+
+/* First device-side failure since the last call (then cleared); the
+ * counterpart of ncclCommGetAsyncError (nccl/src/init.cc:996-1021). */
+int cocoGetStatus(cocoComm_t comm, cocoStatus_t *status);
+
+/* Slice bounds of `rank` for `count` elements over `world` ranks. */
+int cocoSliceBounds(size_t count, int world, int rank, size_t *begin, size_t *end);
+
+/* Per-launch tunables (also COCO_CTAS_PER_SM / COCO_THREADS / COCO_TIMEOUT_MS
+ * in the environment, in the style of NCCL_PARAM, nccl/src/include/param.h:
+ * 48-64).  Values <= 0 keep the current setting. */
+int cocoSetTunables(cocoComm_t comm, int ctas_per_sm, int threads, int timeout_ms);
+
+/* Number of kernels this communicator has launched (for accounting). */
+int cocoLaunchCount(cocoComm_t comm, uint64_t *launches);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* COCONET_RT_H_ */
