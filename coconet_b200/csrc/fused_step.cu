@@ -62,6 +62,11 @@ __device__ __forceinline__ uint4 ld_sys_16(const void *p) {
                : "l"(p));
   return v;
 }
+__device__ __forceinline__ uint2 ld_sys_8(const void *p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ unsigned ld_sys_4(const void *p) {
   unsigned v;
   asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p));
@@ -151,7 +156,7 @@ template <> struct Bits16<__nv_bfloat16> {
 };
 
 template <typename GT> struct GradTraits {
-  static constexpr int kVec = 8;  // 16 bytes of 16-bit elements
+  static constexpr int kVec = 4;  // direct path: 4 elements per thread and pass
   static constexpr bool kIs16 = true;
 };
 template <> struct GradTraits<float> {
@@ -179,13 +184,13 @@ template <> struct RawUnit<float, 1> {
   __device__ __forceinline__ float get(int) const { return __uint_as_float(q); }
   __device__ __forceinline__ unsigned short bits(int) const { return 0; }
 };
-template <typename GT> struct RawUnit<GT, 8> {
-  uint4 q;
+template <typename GT> struct RawUnit<GT, 4> {
+  uint2 q;
   __device__ __forceinline__ void load(const void *base, size_t i) {
-    q = ld_sys_16((const unsigned short *)base + i);
+    q = ld_sys_8((const unsigned short *)base + i);
   }
   __device__ __forceinline__ unsigned short bits(int k) const {
-    const unsigned wd = (k >> 1) == 0 ? q.x : (k >> 1) == 1 ? q.y : (k >> 1) == 2 ? q.z : q.w;
+    const unsigned wd = (k >> 1) == 0 ? q.x : q.y;
     return (unsigned short)((k & 1) ? (wd >> 16) : (wd & 0xffffu));
   }
   __device__ __forceinline__ float get(int k) const { return Bits16<GT>::to_f32(bits(k)); }
@@ -200,48 +205,87 @@ template <typename GT> struct RawUnit<GT, 1> {
 };
 
 // ---------------------------------------------------------------------------
-// reduce-scatter of one unit: pull from every rank, sum in fp32 in rank order
+// reduce-scatter of one unit: pull from every rank, sum in fp32 in rank order.
+//
+// RB is a compile-time bound on the world size (the kernel dispatches once on
+// it): RB = 1 or 2 means R == RB exactly, RB = 4 / 8 covers R <= RB with a
+// predicate per slot.  All RB loads are issued before the first use, so a
+// thread has up to RB remote requests in flight.  RB = 0 is a plain loop over
+// the R ranks (cold scalar path).
 // ---------------------------------------------------------------------------
-template <typename GT, int VEC>
+template <typename GT, int VEC, int RB>
 __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &sa, size_t i,
                                             float (&g)[VEC], float (&gg)[VEC]) {
-  RawUnit<GT, VEC> raw[kMaxRanks];
   const int R = sa.world;
   const bool ring = GradTraits<GT>::kIs16 && sa.variant == cocoVariantNccl;
   // The forked-NCCL variant reproduces the ring: the chunk owned by `rank`
   // starts at rank+1 and is accumulated hop by hop in fp16 (__hadd2,
   // common_kernel.h:795-807).  Everything else sums 0..R-1 in fp32.
   const int first = ring ? (ra.rank + 1) % R : 0;
-#pragma unroll
-  for (int k = 0; k < kMaxRanks; ++k) {
-    if (k < R) {
+  if constexpr (RB == 0) {
+    RawUnit<GT, VEC> raw;
+    __half hacc[VEC];
+    for (int k = 0; k < R; ++k) {
       int p = first + k;
       if (p >= R) p -= R;
-      raw[k].load(ra.g[p], i);
-    }
-  }
-  if (ring) {
-    if constexpr (std::is_same<GT, __half>::value) {
+      raw.load(ra.g[p], i);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        __half acc = __ushort_as_half(raw[0].bits(e));
-#pragma unroll
-        for (int k = 1; k < kMaxRanks; ++k)
-          if (k < R) acc = __hadd(acc, __ushort_as_half(raw[k].bits(e)));
-        g[e] = __half2float(acc);
-        gg[e] = __half2float(__hmul(acc, acc));  // (float)(S0 * S0), reduce_kernel.h:29
+        if (ring) {
+          if constexpr (std::is_same<GT, __half>::value)
+            hacc[e] = k == 0 ? __ushort_as_half(raw.bits(e))
+                             : __hadd(hacc[e], __ushort_as_half(raw.bits(e)));
+        } else {
+          g[e] = k == 0 ? raw.get(e) : __fadd_rn(g[e], raw.get(e));
+        }
       }
     }
-    return;
-  }
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) {
-    float acc = raw[0].get(e);
+    for (int e = 0; e < VEC; ++e) {
+      if (ring) {
+        if constexpr (std::is_same<GT, __half>::value) {
+          g[e] = __half2float(hacc[e]);
+          gg[e] = __half2float(__hmul(hacc[e], hacc[e]));
+        }
+      } else {
+        g[e] = __fmul_rn(g[e], sa.grad_scale);
+        gg[e] = 0.f;
+      }
+    }
+  } else {
+    constexpr bool kExact = RB <= 2;  // R == RB: no per-slot predicate
+    RawUnit<GT, VEC> raw[RB];
 #pragma unroll
-    for (int k = 1; k < kMaxRanks; ++k)
-      if (k < R) acc = __fadd_rn(acc, raw[k].get(e));
-    g[e] = __fmul_rn(acc, sa.grad_scale);
-    gg[e] = 0.f;
+    for (int k = 0; k < RB; ++k) {
+      if (kExact || k < R) {
+        int p = first + k;
+        if (p >= R) p -= R;
+        raw[k].load(ra.g[p], i);
+      }
+    }
+    if (ring) {
+      if constexpr (std::is_same<GT, __half>::value) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          __half acc = __ushort_as_half(raw[0].bits(e));
+#pragma unroll
+          for (int k = 1; k < RB; ++k)
+            if (kExact || k < R) acc = __hadd(acc, __ushort_as_half(raw[k].bits(e)));
+          g[e] = __half2float(acc);
+          gg[e] = __half2float(__hmul(acc, acc));  // (float)(S0 * S0), reduce_kernel.h:29
+        }
+      }
+      return;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float acc = raw[0].get(e);
+#pragma unroll
+      for (int k = 1; k < RB; ++k)
+        if (kExact || k < R) acc = __fadd_rn(acc, raw[k].get(e));
+      g[e] = __fmul_rn(acc, sa.grad_scale);
+      gg[e] = 0.f;
+    }
   }
 }
 
@@ -251,6 +295,9 @@ __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &
 template <int VEC> __device__ __forceinline__ void load_f32(const float *p, float (&x)[VEC]) {
   if constexpr (VEC == 1) {
     x[0] = *p;
+  } else if constexpr (VEC == 2) {
+    const float2 t = __ldcs(reinterpret_cast<const float2 *>(p));
+    x[0] = t.x, x[1] = t.y;
   } else {
 #pragma unroll
     for (int q = 0; q < VEC / 4; ++q) {
@@ -262,6 +309,8 @@ template <int VEC> __device__ __forceinline__ void load_f32(const float *p, floa
 template <int VEC> __device__ __forceinline__ void store_f32(float *p, const float (&x)[VEC]) {
   if constexpr (VEC == 1) {
     *p = x[0];
+  } else if constexpr (VEC == 2) {
+    __stcs(reinterpret_cast<float2 *>(p), make_float2(x[0], x[1]));
   } else {
 #pragma unroll
     for (int q = 0; q < VEC / 4; ++q)
@@ -271,43 +320,58 @@ template <int VEC> __device__ __forceinline__ void store_f32(float *p, const flo
 }
 
 // Store VEC updated weights at element i of every rank's gathered buffer.
-template <typename LPT, int VEC>
+// RB as in reduce_unit.
+template <int VEC> struct Packed;  // VEC output elements as one store
+template <typename LPT, int VEC, int RB>
 __device__ __forceinline__ void gather_unit(const RankArgs &ra, int R, size_t i,
                                             const float (&x)[VEC]) {
+  constexpr bool kExact = RB == 1 || RB == 2;
+  constexpr int kSlots = RB == 0 ? 1 : RB;
   if constexpr (std::is_same<LPT, NoLp>::value) {
-    if constexpr (VEC == 1) {
-      const unsigned b = __float_as_uint(x[0]);
-      for (int p = 0; p < R; ++p) st_sys_4((float *)ra.out[p] + i, b);
+    auto put = [&](int p) {
+      float *dst = (float *)ra.out[p] + i;
+      if constexpr (VEC == 1) {
+        st_sys_4(dst, __float_as_uint(x[0]));
+      } else if constexpr (VEC == 2) {
+        st_sys_8(dst, make_uint2(__float_as_uint(x[0]), __float_as_uint(x[1])));
+      } else {
+#pragma unroll
+        for (int j = 0; j < VEC / 4; ++j)
+          st_sys_16(dst + 4 * j,
+                    make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
+                               __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3])));
+      }
+    };
+    if constexpr (RB == 0) {
+      for (int p = 0; p < R; ++p) put(p);
     } else {
-      uint4 q[VEC / 4];
 #pragma unroll
-      for (int j = 0; j < VEC / 4; ++j)
-        q[j] = make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
-                          __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3]));
-#pragma unroll
-      for (int p = 0; p < kMaxRanks; ++p)
-        if (p < R) {
-#pragma unroll
-          for (int j = 0; j < VEC / 4; ++j) st_sys_16((float *)ra.out[p] + i + 4 * j, q[j]);
-        }
+      for (int p = 0; p < kSlots; ++p)
+        if (kExact || p < R) put(p);
     }
   } else {
     unsigned short h[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) h[e] = Bits16<LPT>::from_f32(x[e]);
-    if constexpr (VEC == 1) {
-      for (int p = 0; p < R; ++p) st_sys_2((unsigned short *)ra.out[p] + i, h[0]);
-    } else if constexpr (VEC == 4) {
-      const uint2 q = make_uint2(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16));
-#pragma unroll
-      for (int p = 0; p < kMaxRanks; ++p)
-        if (p < R) st_sys_8((unsigned short *)ra.out[p] + i, q);
+    auto put = [&](int p) {
+      unsigned short *dst = (unsigned short *)ra.out[p] + i;
+      if constexpr (VEC == 1) {
+        st_sys_2(dst, h[0]);
+      } else if constexpr (VEC == 2) {
+        st_sys_4(dst, h[0] | ((unsigned)h[1] << 16));
+      } else if constexpr (VEC == 4) {
+        st_sys_8(dst, make_uint2(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16)));
+      } else {
+        st_sys_16(dst, make_uint4(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16),
+                                  h[4] | ((unsigned)h[5] << 16), h[6] | ((unsigned)h[7] << 16)));
+      }
+    };
+    if constexpr (RB == 0) {
+      for (int p = 0; p < R; ++p) put(p);
     } else {
-      const uint4 q = make_uint4(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16),
-                                 h[4] | ((unsigned)h[5] << 16), h[6] | ((unsigned)h[7] << 16));
 #pragma unroll
-      for (int p = 0; p < kMaxRanks; ++p)
-        if (p < R) st_sys_16((unsigned short *)ra.out[p] + i, q);
+      for (int p = 0; p < kSlots; ++p)
+        if (kExact || p < R) put(p);
     }
   }
 }
@@ -319,17 +383,21 @@ __device__ __forceinline__ void gather_unit(const RankArgs &ra, int R, size_t i,
 // ---------------------------------------------------------------------------
 struct Hyper {
   float lr, b1, b2, omb1, omb2, eps, wd, d1, d2;
-  double d1d, d2d;
+  double d1d, d2d, r1d, r2d;
   int variant;
+  bool square_first;  // (1-b2)*(g*g) instead of ((1-b2)*g)*g
 };
 
-__device__ __forceinline__ Hyper make_hyper(const StepArgs &sa) {
+template <int OPT> __device__ __forceinline__ Hyper make_hyper(const StepArgs &sa) {
   Hyper h;
   h.lr = sa.lr, h.b1 = sa.beta1, h.b2 = sa.beta2;
   h.omb1 = __fsub_rn(1.f, sa.beta1), h.omb2 = __fsub_rn(1.f, sa.beta2);
   h.eps = sa.eps, h.wd = sa.weight_decay, h.d1 = sa.d1, h.d2 = sa.d2;
   h.d1d = sa.d1d, h.d2d = sa.d2d;
+  h.r1d = 1.0 / sa.d1d, h.r2d = 1.0 / sa.d2d;
   h.variant = sa.variant;
+  // test-adam.cu:16 squares first; lamb.cpp:81 multiplies left to right
+  h.square_first = OPT == kAdam && sa.variant == cocoVariantDsl;
   return h;
 }
 
@@ -347,7 +415,7 @@ __device__ __forceinline__ void moments_elem(const Hyper &h, float g, float gg, 
   if (h.variant == cocoVariantNccl) {
     v = __fadd_rn(__fmul_rn(v, h.b2), __fmul_rn(gg, h.omb2));
     m = __fadd_rn(__fmul_rn(m, h.b2), __fmul_rn(g, h.omb2));
-  } else if (h.variant == cocoVariantDsl) {
+  } else if (h.square_first) {
     v = __fadd_rn(__fmul_rn(h.b2, v), __fmul_rn(h.omb2, __fmul_rn(g, g)));
     m = __fadd_rn(__fmul_rn(h.b1, m), __fmul_rn(h.omb1, g));
   } else {
@@ -356,25 +424,57 @@ __device__ __forceinline__ void moments_elem(const Hyper &h, float g, float gg, 
   }
 }
 
-// m^ = m/d1, v^ = v/d2.  The bias-corrected form divides by the DOUBLE
-// 1 - beta^t and narrows, exactly as the reference's host check does
-// (multi-process-adam-scattered.cpp:118-119: pow() promotes to double), so the
-// result can match a CPU evaluation bit for bit; the other forms divide by a
-// float (test-adam.cu:21,29; reduce_kernel.h:33-47).
-__device__ __forceinline__ void corrected_moments(const Hyper &h, float m, float v, float &m_,
-                                                  float &v_) {
+// float(double(x) / d), exactly, at the price of one double multiply in the
+// common case.  q = x * (1/d) is within a few units in the last place of the
+// true quotient; narrowing q to float gives the same result as narrowing the
+// true quotient unless a rounding boundary of the float format (the midpoint
+// between two floats: dropped 29 bits == 0x10000000) lies within that error,
+// or the result leaves the normal float range.  `risky` collects those rare
+// cases so that ONE branch per batch of elements redoes them with the IEEE
+// division (a branch per element would serialise the elements' dependency
+// chains, and this kernel is latency-bound on them).
+__device__ __forceinline__ float div_narrow_fast(float x, double rcp_d, bool &risky) {
+  const double q = __dmul_rn((double)x, rcp_d);
+  const unsigned lo = (unsigned)__double2loint(q);
+  const unsigned ex = ((unsigned)__double2hiint(q) >> 20) & 0x7ffu;
+  risky = risky || ((lo & 0x1fffffffu) - 0x0ffffff0u) <= 0x20u || ex <= 1023u - 126u ||
+          ex >= 1023u + 127u;
+  return __double2float_rn(q);
+}
+
+// m^ = m/d1, v^ = v/d2 for a batch of elements.  The bias-corrected form
+// divides by the DOUBLE 1 - beta^t and narrows, exactly as the reference's
+// host check does (multi-process-adam-scattered.cpp:118-119: pow() promotes to
+// double), so the result matches a CPU evaluation bit for bit; the other
+// forms divide by a float (test-adam.cu:21,29; reduce_kernel.h:33-47).
+template <int V>
+__device__ __forceinline__ void corrected_moments(const Hyper &h, const float (&m)[V],
+                                                  const float (&v)[V], float (&m_)[V],
+                                                  float (&v_)[V]) {
   if (h.variant == cocoVariantOverlap) {
-    m_ = __double2float_rn(__ddiv_rn((double)m, h.d1d));
-    v_ = __double2float_rn(__ddiv_rn((double)v, h.d2d));
+    bool risky = false;
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      m_[e] = div_narrow_fast(m[e], h.r1d, risky);
+      v_[e] = div_narrow_fast(v[e], h.r2d, risky);
+    }
+    if (risky) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        m_[e] = __double2float_rn(__ddiv_rn((double)m[e], h.d1d));
+        v_[e] = __double2float_rn(__ddiv_rn((double)v[e], h.d2d));
+      }
+    }
   } else {
-    m_ = __fdiv_rn(m, h.d1);
-    v_ = __fdiv_rn(v, h.d2);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      m_[e] = __fdiv_rn(m[e], h.d1);
+      v_[e] = __fdiv_rn(v[e], h.d2);
+    }
   }
 }
 
-__device__ __forceinline__ float adam_elem(const Hyper &h, float w, float m, float v) {
-  float m_, v_;
-  corrected_moments(h, m, v, m_, v_);
+__device__ __forceinline__ float adam_elem(const Hyper &h, float w, float m_, float v_) {
   if (h.variant == cocoVariantDsl)  // test-adam.cu:38:  w - (lr*m_)/v_
     return __fsub_rn(w, __fdiv_rn(__fmul_rn(h.lr, m_), v_));
   // overlap (sample :121): lr*m_/(sqrt(v_)+eps); nccl (reduce_kernel.h:48-62) is
@@ -383,9 +483,7 @@ __device__ __forceinline__ float adam_elem(const Hyper &h, float w, float m, flo
 }
 
 // r = m^/(sqrt(v^)+eps) + lambda*w  (sample :416; lamb.cpp:84 with eps == 0)
-__device__ __forceinline__ float lamb_r_elem(const Hyper &h, float w, float m, float v) {
-  float m_, v_;
-  corrected_moments(h, m, v, m_, v_);
+__device__ __forceinline__ float lamb_r_elem(const Hyper &h, float w, float m_, float v_) {
   return __fadd_rn(__fdiv_rn(m_, __fadd_rn(__fsqrt_rn(v_), h.eps)), __fmul_rn(h.wd, w));
 }
 
@@ -393,11 +491,11 @@ __device__ __forceinline__ float lamb_r_elem(const Hyper &h, float w, float m, f
 // one unit of the data phase
 // ---------------------------------------------------------------------------
 // SGD and Adam: whole step.  LAMB phase 1: moments + norm partials only.
-template <int OPT, typename GT, typename LPT, int VEC>
+template <int OPT, typename GT, typename LPT, int VEC, int RB>
 __device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
                                           size_t lo, size_t i, double &sum_w2, double &sum_r2) {
   float g[VEC], gg[VEC], w[VEC];
-  reduce_unit<GT, VEC>(ra, sa, i, g, gg);
+  reduce_unit<GT, VEC, RB>(ra, sa, i, g, gg);
   load_f32<VEC>(ra.w + i, w);
   if constexpr (OPT == kSGD) {
 #pragma unroll
@@ -406,13 +504,16 @@ __device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa
     float m[VEC], v[VEC];
     load_f32<VEC>(ra.m + (i - lo), m);
     load_f32<VEC>(ra.v + (i - lo), v);
+    float m_[VEC], v_[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) moments_elem(h, g[e], gg[e], m[e], v[e]);
+    corrected_moments<VEC>(h, m, v, m_, v_);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
-      moments_elem(h, g[e], gg[e], m[e], v[e]);
       if constexpr (OPT == kAdam) {
-        w[e] = adam_elem(h, w[e], m[e], v[e]);
+        w[e] = adam_elem(h, w[e], m_[e], v_[e]);
       } else {
-        const float r = lamb_r_elem(h, w[e], m[e], v[e]);
+        const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
         if (sa.flags & COCO_LAMB_REF_QUIRK) {
           sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), (float)sa.count);
           sum_w2 += (double)__fmul_rn(w[e], w[e]);
@@ -427,12 +528,12 @@ __device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa
   }
   if constexpr (OPT != kLAMB) {
     if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<VEC>(ra.w + i, w);
-    gather_unit<LPT, VEC>(ra, sa.world, i, w);
+    gather_unit<LPT, VEC, RB>(ra, sa.world, i, w);
   }
 }
 
 // LAMB phase 2: recompute r from the stored moments, apply the scaled step.
-template <typename LPT, int VEC>
+template <typename LPT, int VEC, int RB>
 __device__ __forceinline__ void lamb_apply_unit(const RankArgs &ra, const StepArgs &sa,
                                                 const Hyper &h, size_t lo, size_t i,
                                                 float lr_scale) {
@@ -440,13 +541,35 @@ __device__ __forceinline__ void lamb_apply_unit(const RankArgs &ra, const StepAr
   load_f32<VEC>(ra.w + i, w);
   load_f32<VEC>(ra.m + (i - lo), m);
   load_f32<VEC>(ra.v + (i - lo), v);
+  float m_[VEC], v_[VEC];
+  corrected_moments<VEC>(h, m, v, m_, v_);
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
-    const float r = lamb_r_elem(h, w[e], m[e], v[e]);
+    const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
     w[e] = __fsub_rn(w[e], __fmul_rn(lr_scale, r));  // sample :434-435
   }
   if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<VEC>(ra.w + i, w);
-  gather_unit<LPT, VEC>(ra, sa.world, i, w);
+  gather_unit<LPT, VEC, RB>(ra, sa.world, i, w);
+}
+
+// Grid-stride loops of the direct (register-staged) path over `nunits`
+// 4-element units starting at element `first`.
+template <int OPT, typename GT, typename LPT, int RB>
+__device__ __forceinline__ void direct_step(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
+                                            size_t lo, size_t first, size_t nunits, size_t tid,
+                                            size_t nth, double &sum_w2, double &sum_r2) {
+  constexpr int VEC = GradTraits<GT>::kVec;
+  for (size_t u = tid; u < nunits; u += nth)
+    step_unit<OPT, GT, LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, sum_w2, sum_r2);
+}
+template <typename GT, typename LPT, int RB>
+__device__ __forceinline__ void direct_apply(const RankArgs &ra, const StepArgs &sa,
+                                             const Hyper &h, size_t lo, size_t first,
+                                             size_t nunits, size_t tid, size_t nth,
+                                             float lr_scale) {
+  constexpr int VEC = GradTraits<GT>::kVec;
+  for (size_t u = tid; u < nunits; u += nth)
+    lamb_apply_unit<LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, lr_scale);
 }
 
 __device__ __forceinline__ double warp_sum(double x) {
@@ -456,16 +579,260 @@ __device__ __forceinline__ double warp_sum(double x) {
 }
 
 // ---------------------------------------------------------------------------
+// tile pipeline: bulk asynchronous copies (the TMA engine, 1-D form) stage
+// whole tiles of every input in shared memory a few tiles ahead of the math,
+// so that HBM / NVLink latency is covered by bytes in flight rather than by
+// registers.  One elected thread issues the copies; every thread consumes.
+// No cluster, no multicast: each CTA fetches its own tiles, local or remote.
+// ---------------------------------------------------------------------------
+constexpr int kTileElemsPerThread = 2;
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded: gives up after timeout_ns (checked every 256 probes) or 2^26 probes.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity,
+                                          unsigned long long timeout_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (unsigned spin = 1; spin < (1u << 26); ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 0u && globaltimer_ns() - t0 > timeout_ns) return false;
+  }
+  return false;
+}
+// global -> shared bulk copy; src, dst and bytes are multiples of 16.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes,
+                                          unsigned long long *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+struct TilePlan {
+  int stages;            // 0: pipeline off
+  unsigned g_bytes;      // bytes of one rank's gradient tile
+  unsigned stage_bytes;  // all inputs of one tile
+  size_t ntiles;         // full tiles in this rank's slice
+};
+
+// Math of one tile: each thread owns kTileElemsPerThread consecutive elements.
+// PHASE 0: whole SGD / Adam step, or LAMB moments + norm partials.
+// PHASE 1: LAMB apply.
+template <int OPT, typename GT, typename LPT, int PHASE>
+__device__ __forceinline__ void tile_math(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
+                                          const unsigned char *st, const TilePlan &tp, size_t lo,
+                                          size_t e0, double &sum_w2, double &sum_r2,
+                                          float lr_scale) {
+  constexpr int V = kTileElemsPerThread;
+  const int R = sa.world;
+  const int t0 = V * threadIdx.x;
+  const size_t i = e0 + t0;
+  float g[V], gg[V], w[V], m[V], v[V];
+  const unsigned goff = PHASE == 0 ? R * tp.g_bytes : 0;
+  const int T = V * blockDim.x;
+  if constexpr (PHASE == 0) {
+    const bool ring = GradTraits<GT>::kIs16 && sa.variant == cocoVariantNccl;
+    if constexpr (GradTraits<GT>::kIs16) {
+      if (ring) {
+        if constexpr (std::is_same<GT, __half>::value) {
+          __half acc[V];
+          for (int k = 0; k < R; ++k) {
+            int p = ra.rank + 1 + k;
+            if (p >= R) p -= R;
+            const unsigned q = *reinterpret_cast<const unsigned *>(st + p * tp.g_bytes + t0 * 2);
+            const unsigned short b[V] = {(unsigned short)(q & 0xffffu), (unsigned short)(q >> 16)};
+#pragma unroll
+            for (int e = 0; e < V; ++e)
+              acc[e] = k == 0 ? __ushort_as_half(b[e]) : __hadd(acc[e], __ushort_as_half(b[e]));
+          }
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            g[e] = __half2float(acc[e]);
+            gg[e] = __half2float(__hmul(acc[e], acc[e]));
+          }
+        }
+      } else {
+        for (int p = 0; p < R; ++p) {
+          const unsigned q = *reinterpret_cast<const unsigned *>(st + p * tp.g_bytes + t0 * 2);
+          const float x[V] = {Bits16<GT>::to_f32((unsigned short)(q & 0xffffu)),
+                              Bits16<GT>::to_f32((unsigned short)(q >> 16))};
+#pragma unroll
+          for (int e = 0; e < V; ++e) g[e] = p == 0 ? x[e] : __fadd_rn(g[e], x[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) g[e] = __fmul_rn(g[e], sa.grad_scale), gg[e] = 0.f;
+      }
+    } else {
+      for (int p = 0; p < R; ++p) {
+        const float2 q = *reinterpret_cast<const float2 *>(st + p * tp.g_bytes + t0 * 4);
+        const float x[V] = {q.x, q.y};
+#pragma unroll
+        for (int e = 0; e < V; ++e) g[e] = p == 0 ? x[e] : __fadd_rn(g[e], x[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) g[e] = __fmul_rn(g[e], sa.grad_scale), gg[e] = 0.f;
+    }
+  }
+  {
+    const float2 q = *reinterpret_cast<const float2 *>(st + goff + t0 * 4);
+    w[0] = q.x, w[1] = q.y;
+  }
+  if constexpr (OPT != kSGD) {
+    const float2 a = *reinterpret_cast<const float2 *>(st + goff + T * 4 + t0 * 4);
+    const float2 b = *reinterpret_cast<const float2 *>(st + goff + 2 * T * 4 + t0 * 4);
+    m[0] = a.x, m[1] = a.y;
+    v[0] = b.x, v[1] = b.y;
+  }
+  if constexpr (PHASE == 0) {
+    if constexpr (OPT == kSGD) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) w[e] = sgd_elem(h, w[e], g[e]);
+    } else {
+      float m_[V], v_[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) moments_elem(h, g[e], gg[e], m[e], v[e]);
+      corrected_moments<V>(h, m, v, m_, v_);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        if constexpr (OPT == kAdam) {
+          w[e] = adam_elem(h, w[e], m_[e], v_[e]);
+        } else {
+          const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
+          if (sa.flags & COCO_LAMB_REF_QUIRK) {
+            sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), (float)sa.count);
+            sum_w2 += (double)__fmul_rn(w[e], w[e]);
+          } else {
+            sum_r2 += (double)r * (double)r;
+            sum_w2 += (double)w[e] * (double)w[e];
+          }
+        }
+      }
+      store_f32<V>(ra.m + (i - lo), m);
+      store_f32<V>(ra.v + (i - lo), v);
+    }
+    if constexpr (OPT != kLAMB) {
+      if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<V>(ra.w + i, w);
+      gather_unit<LPT, V, 0>(ra, R, i, w);
+    }
+  } else {
+    float m_[V], v_[V];
+    corrected_moments<V>(h, m, v, m_, v_);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
+      w[e] = __fsub_rn(w[e], __fmul_rn(lr_scale, r));
+    }
+    if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<V>(ra.w + i, w);
+    gather_unit<LPT, V, 0>(ra, R, i, w);
+  }
+}
+
+// Runs this CTA's share of the slice's full tiles through the pipeline.
+// `iter` counts tiles this CTA has consumed so far (it carries the barrier
+// phases across the two LAMB phases).  Returns false if a copy did not land
+// in time (s_fail is then set for the whole CTA).
+template <int OPT, typename GT, typename LPT, int PHASE>
+__device__ __forceinline__ bool run_tiles(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
+                                          const TilePlan &tp, unsigned char *smem,
+                                          unsigned long long *full, int *s_fail, size_t lo,
+                                          unsigned &iter, double &sum_w2, double &sum_r2,
+                                          float lr_scale) {
+  const int R = sa.world;
+  const int T = kTileElemsPerThread * blockDim.x;
+  const unsigned state_bytes = (OPT == kSGD ? 1u : 3u) * T * 4u;
+  const unsigned bytes = PHASE == 0 ? tp.stage_bytes : state_bytes;
+  const size_t mine =
+      tp.ntiles > blockIdx.x ? (tp.ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const unsigned base = iter;
+
+  auto issue = [&](size_t j) {  // thread 0 only
+    const unsigned s = (base + (unsigned)j) % (unsigned)tp.stages;
+    const size_t e0 = lo + (blockIdx.x + j * gridDim.x) * (size_t)T;
+    unsigned char *st = smem + (size_t)s * tp.stage_bytes;
+    mbar_expect_tx(&full[s], bytes);
+    unsigned off = 0;
+    if constexpr (PHASE == 0) {
+      for (int p = 0; p < R; ++p)
+        bulk_load(st + p * tp.g_bytes, (const GT *)ra.g[p] + e0, tp.g_bytes, &full[s]);
+      off = R * tp.g_bytes;
+    }
+    bulk_load(st + off, ra.w + e0, T * 4u, &full[s]);
+    if constexpr (OPT != kSGD) {
+      bulk_load(st + off + T * 4u, ra.m + (e0 - lo), T * 4u, &full[s]);
+      bulk_load(st + off + 2u * T * 4u, ra.v + (e0 - lo), T * 4u, &full[s]);
+    }
+  };
+
+  if (threadIdx.x == 0)
+    for (size_t j = 0; j < mine && j + 1 < (size_t)tp.stages; ++j) issue(j);
+
+  bool ok = true;
+  size_t j = 0;
+  for (; j < mine; ++j) {
+    // the stage refilled here was consumed one iteration ago (barrier below)
+    if (threadIdx.x == 0 && j + tp.stages - 1 < mine) issue(j + tp.stages - 1);
+    const unsigned it = base + (unsigned)j;
+    const unsigned s = it % (unsigned)tp.stages;
+    if (!mbar_wait(&full[s], (it / (unsigned)tp.stages) & 1u, sa.timeout_ns)) *s_fail = 1;
+    __syncthreads();
+    if (*s_fail) {
+      ok = false;
+      break;
+    }
+    const size_t e0 = lo + (blockIdx.x + j * gridDim.x) * (size_t)T;
+    tile_math<OPT, GT, LPT, PHASE>(ra, sa, h, smem + (size_t)s * tp.stage_bytes, tp, lo, e0,
+                                   sum_w2, sum_r2, lr_scale);
+    __syncthreads();  // everyone is done reading stage s
+  }
+  if (!ok && threadIdx.x == 0) {
+    // Copies may still be in flight into this CTA's shared memory: give each
+    // issued tile one more bounded wait before the CTA is allowed to retire.
+    const size_t issued = mine < j + tp.stages ? mine : j + tp.stages;
+    for (size_t k = j; k < issued; ++k) {
+      const unsigned it = base + (unsigned)k;
+      mbar_wait(&full[it % (unsigned)tp.stages], (it / (unsigned)tp.stages) & 1u, sa.timeout_ns);
+    }
+  }
+  iter = base + (unsigned)mine;
+  return ok;
+}
+
+// ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
 template <int OPT, typename GT, typename LPT>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, 2)
     fused_step_kernel(const __grid_constant__ StepArgs sa, const __grid_constant__ RankArgs one,
                       const RankArgs *__restrict__ table) {
+  extern __shared__ __align__(128) unsigned char tile_smem[];
   __shared__ RankArgs ra;
   __shared__ int s_ok;
+  __shared__ int s_fail;
   __shared__ float s_lr_scale;
   __shared__ double s_red[2][16];
+  __shared__ __align__(8) unsigned long long s_full[8];
 
   {  // this (virtual) rank's pointers -> shared memory
     const RankArgs *src = table ? table + blockIdx.y : &one;
@@ -473,7 +840,13 @@ __global__ void __launch_bounds__(512)
     int *d = reinterpret_cast<int *>(&ra);
     for (int k = threadIdx.x; k < (int)(sizeof(RankArgs) / sizeof(int)); k += blockDim.x)
       d[k] = s[k];
-    if (threadIdx.x == 0) s_ok = 1;
+    if (threadIdx.x == 0) {
+      s_ok = 1;
+      s_fail = 0;
+      for (int k = 0; k < sa.pipe_stages; ++k) mbar_init(&s_full[k], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
   }
   __syncthreads();
 
@@ -506,17 +879,44 @@ __global__ void __launch_bounds__(512)
   const size_t hi = lo + S < N ? lo + S : N;
   const size_t L = hi - lo;
   constexpr int VEC = GradTraits<GT>::kVec;
-  const size_t nvec = ra.pad ? L / VEC : 0;  // pad != 0: slice and pointers allow 16-byte units
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nth = (size_t)gridDim.x * blockDim.x;
-  const Hyper h = make_hyper(sa);
+  const Hyper h = make_hyper<OPT>(sa);
+
+  // Full tiles go through the bulk-copy pipeline; what is left of the slice
+  // (and everything, when the slice or a pointer is not 16-byte aligned) is
+  // done with direct loads.
+  TilePlan tp;
+  const size_t T = (size_t)kTileElemsPerThread * blockDim.x;
+  tp.stages = ra.pad ? sa.pipe_stages : 0;
+  tp.g_bytes = (unsigned)(T * sizeof(GT));
+  tp.stage_bytes = (unsigned)(R * tp.g_bytes + (OPT == kSGD ? 1 : 3) * T * 4);
+  tp.ntiles = tp.stages > 0 ? L / T : 0;
+  const size_t piped = tp.ntiles * T;  // elements covered by the pipeline
+  const size_t nvec_rest = ra.pad ? (L - piped) / VEC : 0;
+  unsigned iter = 0;
 
   double sum_w2 = 0.0, sum_r2 = 0.0;
   if (ok) {
-    for (size_t u = tid; u < nvec; u += nth)
-      step_unit<OPT, GT, LPT, VEC>(ra, sa, h, lo, lo + u * VEC, sum_w2, sum_r2);
-    for (size_t j = nvec * VEC + tid; j < L; j += nth)
-      step_unit<OPT, GT, LPT, 1>(ra, sa, h, lo, lo + j, sum_w2, sum_r2);
+    if (tp.ntiles > 0 &&
+        !run_tiles<OPT, GT, LPT, 0>(ra, sa, h, tp, tile_smem, s_full, &s_fail, lo, iter, sum_w2,
+                                    sum_r2, 0.f)) {
+      if (threadIdx.x == 0) record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
+      ok = false;
+    }
+  }
+  if (ok) {
+    const size_t first = lo + piped;
+    if (R == 1)
+      direct_step<OPT, GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
+    else if (R == 2)
+      direct_step<OPT, GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
+    else if (R <= 4)
+      direct_step<OPT, GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
+    else
+      direct_step<OPT, GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
+    for (size_t j = piped + nvec_rest * VEC + tid; j < L; j += nth)
+      step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, lo, lo + j, sum_w2, sum_r2);
   }
 
   if constexpr (OPT == kLAMB) {
@@ -583,10 +983,25 @@ __global__ void __launch_bounds__(512)
     ok = s_ok != 0;
     if (ok) {
       const float lr_scale = s_lr_scale;
-      for (size_t u = tid; u < nvec; u += nth)
-        lamb_apply_unit<LPT, VEC>(ra, sa, h, lo, lo + u * VEC, lr_scale);
-      for (size_t j = nvec * VEC + tid; j < L; j += nth)
-        lamb_apply_unit<LPT, 1>(ra, sa, h, lo, lo + j, lr_scale);
+      if (tp.ntiles > 0 &&
+          !run_tiles<OPT, GT, LPT, 1>(ra, sa, h, tp, tile_smem, s_full, &s_fail, lo, iter, sum_w2,
+                                      sum_r2, lr_scale)) {
+        if (threadIdx.x == 0) record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
+        ok = false;
+      }
+      if (ok) {
+        const size_t first = lo + piped;
+        if (R == 1)
+          direct_apply<GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
+        else if (R == 2)
+          direct_apply<GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
+        else if (R <= 4)
+          direct_apply<GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
+        else
+          direct_apply<GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
+        for (size_t j = piped + nvec_rest * VEC + tid; j < L; j += nth)
+          lamb_apply_unit<LPT, 1, 0>(ra, sa, h, lo, lo + j, lr_scale);
+      }
     }
   }
 
@@ -648,16 +1063,28 @@ cudaError_t launch_fused_step(int opt, cocoDataType_t g_type, bool has_lp, cocoD
   const dim3 block(cfg.threads, 1, 1);
   const RankArgs *tbl = cfg.nvirt > 1 ? table : nullptr;
   void *params[] = {(void *)&sa, (void *)&one, (void *)&tbl};
+  if (cfg.smem_bytes > 0) {  // static + dynamic may exceed the 48 KB default together
+    cudaError_t e = cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)cfg.smem_bytes);
+    if (e != cudaSuccess) return e;
+  }
   if (cfg.cooperative)
-    return cudaLaunchCooperativeKernel((const void *)k, grid, block, params, 0, stream);
-  return cudaLaunchKernel((const void *)k, grid, block, params, 0, stream);
+    return cudaLaunchCooperativeKernel((const void *)k, grid, block, params, cfg.smem_bytes, stream);
+  return cudaLaunchKernel((const void *)k, grid, block, params, cfg.smem_bytes, stream);
 }
 
 cudaError_t fused_step_occupancy(int opt, cocoDataType_t g_type, bool has_lp,
-                                 cocoDataType_t lp_type, int threads, int *ctas_per_sm) {
+                                 cocoDataType_t lp_type, int threads, size_t smem_bytes,
+                                 int *ctas_per_sm) {
   KernelPtr k = pick(opt, g_type, has_lp, lp_type);
   if (!k) return cudaErrorInvalidValue;
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctas_per_sm, (const void *)k, threads, 0);
+  if (smem_bytes > 0) {
+    cudaError_t e = cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem_bytes);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctas_per_sm, (const void *)k, threads,
+                                                       smem_bytes);
 }
 
 }  // namespace coco

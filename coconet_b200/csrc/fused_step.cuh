@@ -15,7 +15,7 @@ constexpr int kMaxCtasPerRank = 2048;  // rows of the per-CTA partial-norm table
 enum Opt : int { kSGD = 0, kAdam = 1, kLAMB = 2 };
 
 // Phases recorded in the status word when a bounded wait gives up.
-enum Phase : int { kPhaseStart = 1, kPhaseNorm = 2, kPhaseEnd = 3 };
+enum Phase : int { kPhaseStart = 1, kPhaseNorm = 2, kPhaseEnd = 3, kPhaseCopy = 4 };
 
 // One per rank, in device memory, mapped into every peer.  Zero at creation;
 // every flag only ever grows (it holds the sequence number of a fused call),
@@ -58,6 +58,8 @@ struct StepArgs {
   float lr, beta1, beta2, eps, weight_decay, grad_scale;
   float d1, d2;               // denominators of m^ = m/d1, v^ = v/d2 ...
   double d1d, d2d;            // ... in double for the bias-corrected form
+  int pipe_stages;            // stages of the bulk-copy tile pipeline, 0 = off
+  int pad;
 };
 
 struct LaunchConfig {
@@ -65,6 +67,7 @@ struct LaunchConfig {
   int threads;     // threads per CTA
   int nvirt;       // virtual ranks in this launch (grid.y)
   bool cooperative;
+  size_t smem_bytes;  // dynamic shared memory of the tile pipeline
 };
 
 // Host entry: enqueue the fused kernel.  `table` (device memory, nvirt
@@ -75,6 +78,7 @@ cudaError_t launch_fused_step(int opt, cocoDataType_t g_type, bool has_lp, cocoD
 
 // Largest number of co-resident CTAs per SM for the given kernel/threads.
 cudaError_t fused_step_occupancy(int opt, cocoDataType_t g_type, bool has_lp,
-                                 cocoDataType_t lp_type, int threads, int *ctas_per_sm);
+                                 cocoDataType_t lp_type, int threads, size_t smem_bytes,
+                                 int *ctas_per_sm);
 
 }  // namespace coco

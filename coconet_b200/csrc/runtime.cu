@@ -140,6 +140,8 @@ struct cocoComm {
   int ctas_per_sm = 0;  // 0 = automatic
   int threads = 512;
   int timeout_ms = 10000;
+  int smem_budget_kb = 200;  // shared memory the tile pipeline may use per SM
+  bool pipeline = true;      // COCO_PIPELINE=0 forces direct loads
 };
 
 namespace {
@@ -173,6 +175,8 @@ int init_common(cocoComm *c) {
   c->ctas_per_sm = env_int("COCO_CTAS_PER_SM", 0);
   c->threads = env_int("COCO_THREADS", 512);
   if (c->threads < 32 || c->threads > 512 || (c->threads % 32) != 0) c->threads = 512;
+  c->pipeline = env_int("COCO_PIPELINE", 1) != 0;
+  c->smem_budget_kb = std::max(16, std::min(220, env_int("COCO_SMEM_KB", 200)));
   c->timeout_ms = env_int("COCO_TIMEOUT_MS", 10000);
   if (c->timeout_ms <= 0) c->timeout_ms = 10000;
   CUDA_TRY(cudaMalloc((void **)&c->flags, sizeof(FlagPage)));
@@ -287,20 +291,34 @@ int peer_views(cocoComm *c, const void *ptr, size_t bytes, char *views[kMaxRanks
 bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
 
 int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
-                cocoDataType_t lp_type, size_t count, int world, int nvirt, LaunchConfig *cfg) {
-  int occ = 0;
-  CUDA_TRY(fused_step_occupancy(opt, g_type, has_lp, lp_type, c->threads, &occ));
-  if (occ < 1) return cocoInternalError;
+                cocoDataType_t lp_type, size_t count, int world, int nvirt, StepArgs *sa,
+                LaunchConfig *cfg) {
   const bool coop = (opt == kLAMB) || nvirt > 1;
   if (coop && !c->coop_supported) return cocoInvalidUsage;
-  int per_sm = c->ctas_per_sm > 0 ? std::min(c->ctas_per_sm, occ) : std::min(occ, 2);
+  const size_t slice = (count + world - 1) / world;
+
+  // Tile pipeline: as many stages (2..4) as fit the shared-memory budget of
+  // one CTA; off when the slice has no full tile.
+  const int want_per_sm = c->ctas_per_sm > 0 ? c->ctas_per_sm : 2;
+  const size_t tile = (size_t)2 * c->threads;
+  const size_t stage_bytes =
+      (size_t)world * tile * dtype_size(g_type) + (opt == kSGD ? 1 : 3) * tile * 4;
+  const size_t budget = (size_t)c->smem_budget_kb * 1024 / want_per_sm;
+  int stages = (int)std::min<size_t>(4, budget / stage_bytes);
+  if (stages < 2 || slice < tile || !c->pipeline) stages = 0;
+  sa->pipe_stages = stages;
+  cfg->smem_bytes = (size_t)stages * stage_bytes;
+
+  int occ = 0;
+  CUDA_TRY(fused_step_occupancy(opt, g_type, has_lp, lp_type, c->threads, cfg->smem_bytes, &occ));
+  if (occ < 1) return cocoInternalError;
+  int per_sm = std::min(want_per_sm, occ);
   long ctas = (long)per_sm * c->sm_count;
   if (nvirt > 1) ctas = std::max(1L, ((long)occ * c->sm_count) / nvirt);
-  // no more CTAs than there are 16-byte units in the slice
-  const size_t slice = (count + world - 1) / world;
-  const size_t vec = g_type == cocoFloat32 ? 4 : 8;
-  const size_t units = std::max<size_t>(1, (slice + vec - 1) / vec);
-  const long need = (long)((units + c->threads - 1) / c->threads);
+  // no more CTAs than there is work: one tile (or 16-byte unit) per thread pass
+  const size_t vec = 4;
+  const size_t per_cta = stages > 0 ? tile : vec * c->threads;
+  const long need = (long)std::max<size_t>(1, (slice + per_cta - 1) / per_cta);
   ctas = std::max(1L, std::min(ctas, need));
   ctas = std::min<long>(ctas, kMaxCtasPerRank);
   cfg->ctas = (int)ctas;
@@ -343,7 +361,7 @@ void fill_rank_args(RankArgs *ra, int rank, int world, char *const g_views[], ch
   ra->v = pc.v;
   ra->rank = rank;
   const size_t S = (pc.sa.count + world - 1) / world;
-  const size_t vec = pc.g_type == cocoFloat32 ? 4 : 8;
+  const size_t vec = 8;  // 16 bytes of the narrowest element type
   size_t lo = (size_t)rank * S;
   if (lo > pc.sa.count) lo = pc.sa.count;
   ra->pad = (ok16 && (lo % vec) == 0) ? 1 : 0;
@@ -356,9 +374,10 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
   RankArgs ra;
   fill_rank_args(&ra, c->rank, c->world, g_views, out_views, c->peer_flags, pc);
   LaunchConfig cfg;
+  StepArgs sa = pc.sa;
   COCO_TRY(pick_launch(c, pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, pc.sa.count,
-                       c->world, 1, &cfg));
-  CUDA_TRY(launch_fused_step(pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, pc.sa, ra, nullptr,
+                       c->world, 1, &sa, &cfg));
+  CUDA_TRY(launch_fused_step(pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, sa, ra, nullptr,
                              cfg, pc.stream));
   c->launches++;
   return cocoSuccess;
@@ -403,8 +422,9 @@ int flush_group(LocalGroup *grp) {
       fill_rank_args(&host[k], ranks[k], R, g_views, out_views, flags,
                      grp->comms[ranks[k]]->pending);
     LaunchConfig cfg;
+    StepArgs sa = pc0.sa;
     int rc = pick_launch(lead, pc0.opt, pc0.g_type, pc0.w_lp != nullptr, pc0.lp_type,
-                         pc0.sa.count, R, (int)ranks.size(), &cfg);
+                         pc0.sa.count, R, (int)ranks.size(), &sa, &cfg);
     if (rc != cocoSuccess) {
       result = rc;
       break;
@@ -425,7 +445,7 @@ int flush_group(LocalGroup *grp) {
       }
     }
     cudaError_t e = launch_fused_step(pc0.opt, pc0.g_type, pc0.w_lp != nullptr, pc0.lp_type,
-                                      pc0.sa, host[0], table, cfg, pc0.stream);
+                                      sa, host[0], table, cfg, pc0.stream);
     if (e != cudaSuccess) {
       COCO_WARN("launch failed: %s", cudaGetErrorString(e));
       (void)cudaGetLastError();

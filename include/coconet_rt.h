@@ -91,7 +91,7 @@ typedef enum {
 typedef struct {
   int code;        /* cocoResult_t of the first device-side failure, 0 if none */
   int rank;        /* rank that recorded it */
-  int phase;       /* 1 start barrier, 2 norm exchange, 3 end barrier */
+  int phase;       /* 1 start barrier, 2 norm exchange, 3 end barrier, 4 tile copy */
   int peer;        /* peer rank that was waited for, -1 if n/a */
   uint64_t seq;    /* sequence number of the fused call */
 } cocoStatus_t;

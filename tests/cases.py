@@ -70,9 +70,10 @@ def assert_close(actual, expect, rtol, what):
     """|a-b| <= rtol*max(|a|,|b|) + atol, atol = rtol * 1e-3 (weights are O(1e-2))."""
     a = np.asarray(actual, np.float64)
     b = np.asarray(expect, np.float64)
-    err = np.abs(a - b)
+    both_nan = np.isnan(a) & np.isnan(b)  # e.g. 0/0 in the DSL's LAMB when a gradient is 0
+    err = np.where(both_nan, 0.0, np.abs(a - b))
     tol = rtol * np.maximum(np.abs(a), np.abs(b)) + rtol * 1e-3
-    bad = err > tol
+    bad = ~(err <= tol) & ~both_nan
     if bad.any():
         i = int(np.argmax(err - tol))
         raise AssertionError(f"{what}: {int(bad.sum())} of {a.size} outside rtol {rtol}; "

@@ -88,9 +88,18 @@ def _check_against(ranks, ora, rtol=RTOL_FP32, exact_state=True, exact_w=False):
             lp = ranks.lp[r].float().cpu().numpy()
             # half(w') of weights that agree to 1e-5 may differ by one fp16 ulp
             K.assert_close(lp, ora.w_lp.astype(np.float32), 1e-3, f"w_lp on rank {r}")
-            assert torch.equal(ranks.lp[r], ranks.lp[0]), "low-precision replicas differ"
+            assert torch.equal(ranks.lp[r].view(torch.int16), ranks.lp[0].view(torch.int16)), \
+                "low-precision replicas differ"
             own = ranks.w[r][lo:hi].to(ranks.lp[r].dtype)
-            assert torch.equal(ranks.lp[r][lo:hi], own), "w_lp is not the rounding of the master"
+            got = ranks.lp[r][lo:hi]
+            same = (got == own) | (got.isnan() & own.isnan())
+            if not bool(same.all()):
+                bad = torch.nonzero(~same).flatten()
+                k = int(bad[0])
+                raise AssertionError(
+                    f"w_lp is not the rounding of the master on rank {r}: {bad.numel()} elements, "
+                    f"first at slice index {k}: lp={float(ranks.lp[r][lo + k])!r} "
+                    f"master={float(ranks.w[r][lo + k])!r} oracle={float(ora.w[lo + k])!r}")
         if ranks.opt != K.SGD:
             m = ranks.m[r].cpu().numpy()[: hi - lo]
             v = ranks.v[r].cpu().numpy()[: hi - lo]
@@ -142,7 +151,7 @@ def test_sgd_config0_reference_checker():
 
 
 @pytest.mark.parametrize("R", [1, 2, 4, 8])
-@pytest.mark.parametrize("n", [7, 4099, 65536, (1 << 20) + 3])
+@pytest.mark.parametrize("n", [7, 4099, 65536, 1 << 20, (1 << 20) + 3])
 def test_adam_fp32(R, n):
     ranks = Ranks(K.ADAM, R, n, seed=3)
     ora = K.OracleState(K.ADAM, n, seed=3)
@@ -180,7 +189,7 @@ def test_adam_fp32_ten_steps_reference_checker():
 
 
 @pytest.mark.parametrize("R", [1, 2, 8])
-@pytest.mark.parametrize("n", [9, 4099, (1 << 20) + 8])
+@pytest.mark.parametrize("n", [9, 4099, 1 << 20, (1 << 20) + 8])
 @pytest.mark.parametrize("lp", [torch.float16, torch.bfloat16])
 def test_adam_mixed_precision(R, n, lp):
     # fp16 gradients scaled by 1024, unscaled in the kernel; fp32 master slice;
@@ -302,7 +311,7 @@ def test_adam_nccl_variant_matches_oracle_ring_sum():
 
 
 @pytest.mark.parametrize("R", [1, 2, 8])
-@pytest.mark.parametrize("n", [11, 4099, (1 << 20) + 3])
+@pytest.mark.parametrize("n", [11, 4099, 1 << 20, (1 << 20) + 3])
 def test_lamb_fp32(R, n):
     ranks = Ranks(K.LAMB, R, n, seed=9)
     ora = K.OracleState(K.LAMB, n, seed=9)
