@@ -10,6 +10,7 @@ There is no CPU fallback: everything raises if the library is missing.
 from .runtime import (  # noqa: F401
     CocoError,
     Communicator,
+    HostBootstrap,
     VARIANT_DSL,
     VARIANT_NCCL,
     VARIANT_OVERLAP,
@@ -21,6 +22,6 @@ from .runtime import (  # noqa: F401
 )
 
 __all__ = [
-    "CocoError", "Communicator", "VARIANT_DSL", "VARIANT_NCCL", "VARIANT_OVERLAP",
+    "CocoError", "Communicator", "HostBootstrap", "VARIANT_DSL", "VARIANT_NCCL", "VARIANT_OVERLAP",
     "LAMB_REF_QUIRK", "group", "lib", "library_path", "slice_bounds",
 ]

@@ -696,6 +696,40 @@ int cocoAllGatherHost(cocoComm_t comm, const void *send, void *recv, size_t byte
   return cocoInvalidUsage;
 }
 
+struct cocoBootstrap {
+  Bootstrap impl;
+};
+
+int cocoBootstrapInit(cocoBootstrap_t *bs, int world, int rank, const char *addr, int timeout_ms) {
+  if (!bs) return cocoInvalidArgument;
+  std::unique_ptr<cocoBootstrap> b(new cocoBootstrap);
+  COCO_TRY(b->impl.init(world, rank, resolve_bootstrap_addr(addr),
+                        timeout_ms > 0 ? timeout_ms : 120000));
+  *bs = b.release();
+  return cocoSuccess;
+}
+int cocoBootstrapAllGather(cocoBootstrap_t bs, const void *send, void *recv,
+                           size_t bytes_per_rank) {
+  if (!bs || !send || !recv) return cocoInvalidArgument;
+  return bs->impl.all_gather(send, recv, bytes_per_rank);
+}
+int cocoBootstrapBarrier(cocoBootstrap_t bs) {
+  if (!bs) return cocoInvalidArgument;
+  return bs->impl.barrier();
+}
+int cocoBootstrapDestroy(cocoBootstrap_t bs) {
+  if (!bs) return cocoInvalidArgument;
+  delete bs;
+  return cocoSuccess;
+}
+int cocoEnvRank(int *rank, int *world, int *local_rank) {
+  if (!rank || !world || !local_rank) return cocoInvalidArgument;
+  *rank = env_int("RANK", 0);
+  *world = env_int("WORLD_SIZE", 1);
+  *local_rank = env_int("LOCAL_RANK", *rank);
+  return cocoSuccess;
+}
+
 int cocoGroupStart(void) {
   ++g_group_depth;
   return cocoSuccess;

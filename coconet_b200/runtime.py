@@ -42,6 +42,11 @@ _SIGNATURES = {
     "cocoCommCuDevice": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "cocoBarrier": (C.c_int, [C.c_void_p]),
     "cocoAllGatherHost": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "cocoBootstrapInit": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_char_p, C.c_int]),
+    "cocoBootstrapAllGather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "cocoBootstrapBarrier": (C.c_int, [C.c_void_p]),
+    "cocoBootstrapDestroy": (C.c_int, [C.c_void_p]),
+    "cocoEnvRank": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "cocoGroupStart": (C.c_int, []),
     "cocoGroupEnd": (C.c_int, []),
     "cocoRegister": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
@@ -122,6 +127,29 @@ def _stream(stream):
     import torch
     s = stream if stream is not None else torch.cuda.current_stream()
     return C.c_void_p(s.cuda_stream)
+
+
+class HostBootstrap:
+    """The runtime's TCP rendezvous on its own (no GPU needed)."""
+
+    def __init__(self, world, rank, addr=None, timeout_ms=0):
+        h = C.c_void_p()
+        _check(lib().cocoBootstrapInit(C.byref(h), world, rank, addr.encode() if addr else None,
+                                       timeout_ms), "cocoBootstrapInit")
+        self._h, self.world, self.rank = h, world, rank
+
+    def all_gather(self, blob: bytes):
+        recv = C.create_string_buffer(len(blob) * self.world)
+        _check(lib().cocoBootstrapAllGather(self._h, blob, recv, len(blob)), "cocoBootstrapAllGather")
+        return [recv.raw[i * len(blob):(i + 1) * len(blob)] for i in range(self.world)]
+
+    def barrier(self):
+        _check(lib().cocoBootstrapBarrier(self._h), "cocoBootstrapBarrier")
+
+    def close(self):
+        if self._h:
+            lib().cocoBootstrapDestroy(self._h)
+            self._h = None
 
 
 class Communicator:

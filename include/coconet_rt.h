@@ -126,6 +126,20 @@ int cocoCommCuDevice(cocoComm_t comm, int *device);
 int cocoBarrier(cocoComm_t comm);
 int cocoAllGatherHost(cocoComm_t comm, const void *send, void *recv, size_t bytes_per_rank);
 
+/* ---- host rendezvous, usable without a GPU ---------------------------------
+ * What the emitted main() did with MPI_Init / MPI_Comm_rank / MPI_Bcast /
+ * MPI_Barrier (src/codegen.cpp:4587-4601, 4471-4487): a star of TCP
+ * connections to rank 0.  `addr` as for cocoCommInitRank.  Every call is
+ * collective and bounded by timeout_ms (a missing rank yields cocoTimeout). */
+typedef struct cocoBootstrap *cocoBootstrap_t;
+int cocoBootstrapInit(cocoBootstrap_t *bs, int world, int rank, const char *addr, int timeout_ms);
+int cocoBootstrapAllGather(cocoBootstrap_t bs, const void *send, void *recv, size_t bytes_per_rank);
+int cocoBootstrapBarrier(cocoBootstrap_t bs);
+int cocoBootstrapDestroy(cocoBootstrap_t bs);
+/* RANK / WORLD_SIZE / LOCAL_RANK as set by torchrun-style launchers (0, 1, 0
+ * when unset): how an emitted program finds its place without MPI. */
+int cocoEnvRank(int *rank, int *world, int *local_rank);
+
 /* Like ncclGroupStart/End: fused calls issued in between are launched at
  * cocoGroupEnd.  Required when several ranks share one device. */
 int cocoGroupStart(void);

@@ -1,0 +1,124 @@
+"""CPU-only checks of the host side: the C-ABI library loads and exports every
+declared entry point, slice bounds, argument validation that needs no device,
+and the TCP rendezvous with 2-4 processes (including its failure modes)."""
+import multiprocessing as mp
+import os
+import re
+import socket
+import sys
+import time
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import coconet_b200 as coco  # noqa: E402
+from coconet_b200 import runtime as rt  # noqa: E402
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "coconet_rt.h")).read()
+    declared = set(re.findall(r"^(?:int|const char \*)\s*(coco[A-Za-z]+)\(", hdr, re.M))
+    assert len(declared) >= 25
+    L = coco.lib()
+    for name in sorted(declared):
+        assert hasattr(L, name), f"{name} declared in coconet_rt.h but not exported"
+    assert declared == set(rt._SIGNATURES), declared ^ set(rt._SIGNATURES)
+
+
+def test_version_and_error_strings():
+    import ctypes as C
+    v = C.c_int()
+    assert coco.lib().cocoGetVersion(C.byref(v)) == 0 and v.value == 100
+    assert rt.error_string(0) == "success"
+    assert "timed out" in rt.error_string(5)
+    assert "unknown" in rt.error_string(1234)
+
+
+@pytest.mark.parametrize("n,R", [(0, 1), (1, 8), (10, 4), (334_000_000, 8), (1 << 20, 2), (4099, 3)])
+def test_slice_bounds_partition(n, R):
+    S = -(-n // R) if n else 0
+    prev = 0
+    for r in range(R):
+        lo, hi = coco.slice_bounds(n, R, r)
+        assert lo == min(n, r * S) and hi == min(n, lo + S) and lo == prev
+        prev = hi
+    assert prev == n
+    with pytest.raises(coco.CocoError):
+        coco.slice_bounds(n, R, R)
+
+
+def test_null_handles_are_rejected_not_dereferenced():
+    import ctypes as C
+    L = coco.lib()
+    assert L.cocoCommDestroy(None) == 1
+    assert L.cocoBarrier(None) == 1
+    assert L.cocoFusedSGD(None, None, 7, None, None, 6, 16, 0.1, 1.0, None) == 1
+    assert L.cocoGroupEnd() == 2  # no matching cocoGroupStart
+    st = rt._Status()
+    assert L.cocoGetStatus(None, C.byref(st)) == 1
+    assert L.cocoCommInitRank(None, 2, 0, None) == 1
+    h = C.c_void_p()
+    assert L.cocoCommInitRank(C.byref(h), 9, 0, None) == 1  # more than COCO_MAX_RANKS
+    assert L.cocoCommInitRank(C.byref(h), 2, 2, None) == 1
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _bs_worker(world, rank, port, q, mode):
+    try:
+        if mode == "late" and rank == 1:
+            time.sleep(1.0)
+        if mode == "absent" and rank == world - 1:
+            q.put((rank, "skipped"))
+            return
+        bs = coco.HostBootstrap(world, rank, f"127.0.0.1:{port}", timeout_ms=1500 if mode == "absent" else 20000)
+        out = []
+        for rnd in range(3):
+            blob = bytes([rank, rnd]) * 50
+            got = bs.all_gather(blob)
+            out.append(all(got[r] == bytes([r, rnd]) * 50 for r in range(world)))
+            bs.barrier()
+        big = bytes([rank]) * (1 << 20)
+        got = bs.all_gather(big)
+        out.append(all(got[r] == bytes([r]) * (1 << 20) for r in range(world)))
+        bs.close()
+        q.put((rank, all(out)))
+    except coco.CocoError as e:
+        q.put((rank, f"error {e.code}"))
+
+
+def _run(world, mode):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_bs_worker, args=(world, r, port, q, mode)) for r in range(world)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=60) for _ in ps)
+    for p in ps:
+        p.join(timeout=30)
+    return res
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_bootstrap_all_gather_and_barrier(world):
+    assert _run(world, "normal") == {r: True for r in range(world)}
+
+
+def test_bootstrap_tolerates_a_late_rank():
+    assert _run(2, "late") == {0: True, 1: True}
+
+
+def test_bootstrap_times_out_when_a_rank_never_joins():
+    res = _run(3, "absent")
+    assert res[2] == "skipped"
+    assert res[0] == "error 5"  # rank 0 gives up in accept()
+    assert res[1].startswith("error")  # connected, then the root went away

@@ -1,0 +1,47 @@
+"""Multi-process parity: one process per GPU over CUDA IPC peer memory, the
+product path for R > 1.  Needs at least two GPUs; skipped otherwise (the same
+kernel code runs in tests/test_fused_gpu.py with virtual ranks on one GPU)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _launch(case, world, timeout=600):
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ)
+    # plain peer loads only; no NVLS anywhere in these child processes
+    env.update(NCCL_NVLS_ENABLE="0", COCO_TIMEOUT_MS=env.get("COCO_TIMEOUT_MS", "5000"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           os.path.join(HERE, "mp_worker.py"), case]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_parity_all_gpus():
+    world = min(_ngpu(), 8)
+    r = _launch("parity", world)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok ") >= 8, r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_absent_rank_times_out_cleanly():
+    r = _launch("timeout", 2)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "ok timeout" in r.stdout
