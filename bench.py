@@ -24,7 +24,6 @@ import json
 import os
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -48,39 +47,52 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region."""
+    """nvidia-smi clocks and throttle reasons, sampled every 50 ms by one
+    streaming nvidia-smi process while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.samples, self._stop = index, [], threading.Event()
-        self._t = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
-                f = [x.strip() for x in out.strip().split(",")]
-                if len(f) >= 9:
-                    self.samples.append(f)
-            except Exception:
-                pass
-            self._stop.wait(0.1)
+        self.index, self.proc = index, None
 
     def start(self):
-        self._t.start()
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
+                 str(self.index), "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+            time.sleep(0.3)  # let the first samples arrive before the region starts
+        except Exception:
+            self.proc = None
 
     def stop(self):
-        self._stop.set()
-        self._t.join(timeout=6)
-        sm = sorted(float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit())
-        mx = [float(s[2]) for s in self.samples if s[2].replace(".", "").isdigit()]
+        samples = []
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()  # our own child, by handle
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+            except Exception:
+                out = ""
+            for line in out.splitlines():
+                f = [x.strip() for x in line.split(",")]
+                if len(f) >= 9:
+                    samples.append(f)
+
+        def num(x):
+            try:
+                return float(x)
+            except ValueError:
+                return None
+        sm = sorted(v for v in (num(s[1]) for s in samples) if v is not None)
+        mx = [v for v in (num(s[2]) for s in samples) if v is not None]
+        pw = [v for v in (num(s[3]) for s in samples) if v is not None]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for s in self.samples for n, v in zip(names, s[5:9]) if v.lower().startswith("active")})
+        reasons = sorted({n for s in samples for n, v in zip(names, s[5:9])
+                          if v.lower().startswith("active")})
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+                "power_w_max": max(pw) if pw else None, "reasons": reasons, "samples": len(samples)}
 
 
 def cpu_baseline(count_sample, world, reps=2):

@@ -141,7 +141,7 @@ struct cocoComm {
   int threads = 512;
   int timeout_ms = 10000;
   int smem_budget_kb = 200;  // shared memory the tile pipeline may use per SM
-  bool pipeline = true;      // COCO_PIPELINE=0 forces direct loads
+  bool pipeline = false;     // COCO_PIPELINE=1: stage tiles in shared memory by bulk copies
 };
 
 namespace {
@@ -175,7 +175,7 @@ int init_common(cocoComm *c) {
   c->ctas_per_sm = env_int("COCO_CTAS_PER_SM", 0);
   c->threads = env_int("COCO_THREADS", 512);
   if (c->threads < 32 || c->threads > 512 || (c->threads % 32) != 0) c->threads = 512;
-  c->pipeline = env_int("COCO_PIPELINE", 1) != 0;
+  c->pipeline = env_int("COCO_PIPELINE", 0) != 0;
   c->smem_budget_kb = std::max(16, std::min(220, env_int("COCO_SMEM_KB", 200)));
   c->timeout_ms = env_int("COCO_TIMEOUT_MS", 10000);
   if (c->timeout_ms <= 0) c->timeout_ms = 10000;

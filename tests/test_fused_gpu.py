@@ -364,6 +364,29 @@ def test_lamb_dsl_variant_and_mixed():
         ranks.close()
 
 
+@pytest.mark.parametrize("opt,R,n", [(K.ADAM, 2, 1 << 20), (K.ADAM, 8, 1 << 20), (K.LAMB, 4, 1 << 20),
+                                     (K.SGD, 2, (1 << 18) + 5), (K.ADAM, 1, (1 << 20) + 3)])
+def test_bulk_copy_tile_pipeline(monkeypatch, opt, R, n):
+    # the optional shared-memory staging path (COCO_PIPELINE=1) must give the
+    # same results as the default register-staged path
+    monkeypatch.setenv("COCO_PIPELINE", "1")
+    ranks = Ranks(opt, R, n, seed=21, lp_dtype=torch.float16 if opt == K.ADAM else None)
+    ora = K.OracleState(opt, n, seed=21, lp=opt == K.ADAM)
+    try:
+        for step in range(2):
+            if opt == K.ADAM:
+                grads = K.make_grads(R, n, 21, step, dtype=np.float16, loss_scale=1024.0)
+                ranks.step(grads, step, grad_scale=1 / 1024.0)
+                ora.step(grads, step, inv_scale=1 / 1024.0)
+            else:
+                grads = K.make_grads(R, n, 21, step)
+                ranks.step(grads, step)
+                ora.step(grads, step)
+            _check_against(ranks, ora, exact_w=opt != K.LAMB)
+    finally:
+        ranks.close()
+
+
 def test_unaligned_views_take_the_scalar_path():
     # pointers that are not 16-byte aligned (views at odd offsets)
     R, n = 2, 5001
