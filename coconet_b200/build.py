@@ -6,7 +6,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcoconet_rt.so")
-SOURCES = ["fused_step.cu", "runtime.cu", "bootstrap.cpp"]
+SOURCES = ["fused_step.cu", "runtime.cu", "bootstrap.cpp", "no_alloc.cu"]
 HEADERS = ["fused_step.cuh", "bootstrap.h", os.path.join(ROOT, "include", "coconet_rt.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 

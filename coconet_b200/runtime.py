@@ -60,6 +60,10 @@ _SIGNATURES = {
                                 C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
                                 C.c_float, C.c_float, C.c_float, C.c_int, C.c_float, C.c_int,
                                 C.c_uint, C.c_void_p]),
+    "cocoLambStepNoAlloc": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                      C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
+                                      C.c_float, C.c_float, C.c_float, C.c_int, C.c_float,
+                                      C.c_void_p]),
     "cocoLastLambNorms": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "cocoGetStatus": (C.c_int, [C.c_void_p, C.POINTER(_Status)]),
     "cocoSliceBounds": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_size_t),

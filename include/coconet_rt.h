@@ -177,6 +177,30 @@ int cocoFusedLAMB(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *
                   float beta1, float beta2, float eps, float weight_decay, int step,
                   float grad_scale, cocoVariant_t variant, unsigned flags, cocoStream_t stream);
 
+/* One LAMB step on ONE GPU (world size 1, bias-corrected formulation, same
+ * arguments and arithmetic as cocoFusedLAMB) for callers that may not
+ * allocate device memory when they step the optimizer: inside a stream
+ * capture's begin/end bracket, with a frozen or fully reserved memory pool,
+ * near the device's memory limit, or in a loop that must stay clear of the
+ * driver's allocation locks.  It needs no communicator and calls no
+ * cudaMalloc/cudaFree nor any allocating library routine: the kernel's scratch
+ * (CTA counters, per-CTA partial norms, status; about 33 KB) lives in a fixed
+ * __device__ array inside the library image, held by every GPU that loads the
+ * library until the process exits.
+ *  - Limit: count <= COCO_NO_ALLOC_MAX_COUNT, else cocoInvalidArgument.
+ *  - The first call on a device looks up the array's device address (once per
+ *    device, with that device current); make that first call before any
+ *    stream capture begins.
+ *  - All calls on a device share the array: two calls whose kernels overlap
+ *    on the GPU race.  Serialise them (one stream, or events).
+ *  - The current device is used; m, v hold `count` elements.
+ * This entry point has no counterpart in the reference. */
+#define COCO_NO_ALLOC_MAX_COUNT (1ull << 31)
+int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *w, void *w_lp,
+                        cocoDataType_t lp_type, float *m, float *v, size_t count, float lr,
+                        float beta1, float beta2, float eps, float weight_decay, int step,
+                        float grad_scale, cocoStream_t stream);
+
 /* Norms of the last LAMB step on this communicator: out[0] = ||w||,
  * out[1] = ||r|| as used for the trust ratio.  Synchronise the stream first. */
 int cocoLastLambNorms(cocoComm_t comm, double out[2]);
