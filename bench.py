@@ -152,6 +152,9 @@ def main():
     ap.add_argument("--no-baseline", action="store_true", help="skip the stock NCCL comparison (N > 1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--algo", default=os.environ.get("COCO_BENCH_ALGO", "p2p"), choices=["p2p", "nvls"],
+                    help="nvls: gradients and fp16 weights in symmetric memory with an NVSwitch "
+                         "multicast mapping; reduce-scatter and all-gather go through the switch")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -185,9 +188,27 @@ def main():
     S = (N + R - 1) // R
     gen = torch.Generator(device=dev).manual_seed(1000 + rank)
     # two gradient buffers, alternated, each far larger than L2 (126 MB)
+    use_nvls = args.algo == "nvls" and world > 1
+    symm = []
+
+    def comm_buffer(numel):
+        """A buffer peers touch: plain device memory (peer-mapped by the runtime
+        over CUDA IPC), or torch symmetric memory with a multicast address."""
+        if not use_nvls:
+            return torch.empty(numel, dtype=torch.float16, device=dev)
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(numel, dtype=torch.float16, device=dev)
+        h = symm_mem.rendezvous(t, dist.group.WORLD)
+        mc = int(h.multicast_ptr)
+        if not mc:
+            raise SystemExit("--algo nvls: this node exposes no NVLS multicast")
+        comm.register_mapped(t, [int(p) for p in h.buffer_ptrs], mc)
+        symm.append(h)
+        return t
+
     g = []
     for _ in range(2):
-        t = torch.empty(N, dtype=torch.float16, device=dev)
+        t = comm_buffer(N)
         chunk = 1 << 26
         for a in range(0, N, chunk):
             b = min(N, a + chunk)
@@ -195,12 +216,16 @@ def main():
         g.append(t)
     wgen = torch.Generator(device=dev).manual_seed(7)
     w = torch.randn(N, device=dev, generator=wgen) * 0.02
-    w_lp = w.half()
+    w_lp = comm_buffer(N)
+    w_lp.copy_(w)
     m = torch.zeros(S, device=dev)
     v = torch.zeros(S, device=dev)
-    for t in g:
-        comm.register(t)
-    comm.register(w_lp)
+    if use_nvls:
+        comm.set_algo(True)
+    else:
+        for t in g:
+            comm.register(t)
+        comm.register(w_lp)
 
     step_no = [0]
 
@@ -240,6 +265,7 @@ def main():
     clocks = sampler.stop() if sampler else None
     st = comm.status()
     if st["code"] != 0:
+        time.sleep(3.0 if use_nvls else 0.0)  # let the peers finish with this rank's memory
         raise SystemExit(f"device-side failure during the benchmark: {st}")
 
     # ---- end to end: host gradients in, host fp16 weights out ------------------
@@ -288,12 +314,15 @@ def main():
         # algorithmic bytes per launch (per GPU)
         b_hbm = N * s_g + (hi - lo) * 24 + (hi - lo) * s_o + (R - 1) * S * s_o
         b_nv = (R - 1) * S * (s_g + s_o)
+        b_bus = b_nv  # bus GB/s always by the peer-to-peer formula, whatever the algorithm
         t = ms * 1e-3
         if R == 1:
             roof = {"bound": "hbm", "achieved": b_hbm / t / 1e9, "peak": hbm_peak, "unit": "GB/s",
                     "frac": b_hbm / t / 1e9 / hbm_peak, "traffic": None, "peak_kind": peak_kind,
                     "algorithmic_bytes": b_hbm}
         else:
+            if use_nvls:  # every slice leaves each GPU once; every updated slice arrives once
+                b_nv = N * s_g + (hi - lo) * s_o
             t_roof = max(b_nv / (NVLINK_PEER_GBS * 1e9), b_hbm / (hbm_peak * 1e9))
             roof = {"bound": "nvlink", "achieved": b_nv / t / 1e9, "peak": NVLINK_PEER_GBS,
                     "unit": "GB/s", "frac": t_roof / t, "traffic": None,
@@ -305,9 +334,9 @@ def main():
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic",
                 "config": {"workload": "mixed_adam_334M" if N == COUNT else f"mixed_adam_{N}",
-                           "count": N, "world": R, "grad": "f16", "state": "f32", "gathered": "f16",
+                           "count": N, "world": R, "algo": "nvls" if use_nvls else "p2p", "grad": "f16", "state": "f32", "gathered": "f16",
                            "l2": "inputs larger than L2 (two 668 MB gradient buffers alternated)"},
-                "bus_gbs": b_nv / t / 1e9, "roofline": roof, "clocks": clocks,
+                "bus_gbs": b_bus / t / 1e9, "roofline": roof, "clocks": clocks,
                 "gpu_launches": int(launches), "e2e": e2e}
         if nccl:
             line["nccl_baseline"] = nccl

@@ -552,6 +552,151 @@ __device__ __forceinline__ void lamb_apply_unit(const RankArgs &ra, const StepAr
   gather_unit<LPT, VEC, RB>(ra, sa.world, i, w);
 }
 
+// ---------------------------------------------------------------------------
+// NVLS path: the reduce-scatter is ONE multimem.ld_reduce per 16 bytes (the
+// NVSwitch fetches the unit from all R gradient buffers and adds them on the
+// way), the all-gather ONE multimem.st (the switch replicates it to all R
+// output buffers).  Per GPU and direction this moves (1 + 1/R) * N * s bytes
+// instead of 2 * (R-1)/R * N * s.  The order of the in-switch sum is not the
+// rank order of the P2P path, and 16-bit sums are accumulated in fp32 but
+// delivered rounded to 16 bits, so results agree with the P2P path only to
+// within the stated tolerances, not bit for bit.
+// ---------------------------------------------------------------------------
+template <typename GT> struct Multimem;
+template <> struct Multimem<float> {
+  static constexpr int kN = 4;
+  static __device__ __forceinline__ void ld_reduce(const void *p, float (&x)[4]) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(x[0]), "=f"(x[1]), "=f"(x[2]), "=f"(x[3])
+                 : "l"(p)
+                 : "memory");
+  }
+};
+template <> struct Multimem<__half> {
+  static constexpr int kN = 8;
+  static __device__ __forceinline__ void ld_reduce(const void *p, float (&x)[8]) {
+    unsigned q[4];
+    asm volatile(
+        "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
+        : "l"(p)
+        : "memory");
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      x[2 * k] = Bits16<__half>::to_f32((unsigned short)(q[k] & 0xffffu));
+      x[2 * k + 1] = Bits16<__half>::to_f32((unsigned short)(q[k] >> 16));
+    }
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  static constexpr int kN = 8;
+  static __device__ __forceinline__ void ld_reduce(const void *p, float (&x)[8]) {
+    unsigned q[4];
+    asm volatile(
+        "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
+        : "l"(p)
+        : "memory");
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      x[2 * k] = Bits16<__nv_bfloat16>::to_f32((unsigned short)(q[k] & 0xffffu));
+      x[2 * k + 1] = Bits16<__nv_bfloat16>::to_f32((unsigned short)(q[k] >> 16));
+    }
+  }
+};
+// 16 bytes to every rank's copy (typed .f32 only to name the register class;
+// a store performs no arithmetic on the bits).
+__device__ __forceinline__ void multimem_st_16(void *p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+template <typename LPT, int V>
+__device__ __forceinline__ void nvls_gather(const RankArgs &ra, int R, size_t i,
+                                            const float (&x)[V]) {
+  if constexpr (std::is_same<LPT, NoLp>::value) {
+#pragma unroll
+    for (int j = 0; j < V / 4; ++j)
+      multimem_st_16((float *)ra.mc_out + i + 4 * j,
+                     make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
+                                __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3])));
+  } else {
+    unsigned short h[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) h[e] = Bits16<LPT>::from_f32(x[e]);
+    if constexpr (V == 8) {
+      multimem_st_16((unsigned short *)ra.mc_out + i,
+                     make_uint4(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16),
+                                h[4] | ((unsigned)h[5] << 16), h[6] | ((unsigned)h[7] << 16)));
+    } else {
+      // 4 low-precision elements are only 8 bytes: plain peer stores
+      gather_unit<LPT, V, 0>(ra, R, i, x);
+    }
+  }
+}
+
+// PHASE 0: SGD / Adam step or LAMB moments; PHASE 1: LAMB apply.
+template <int OPT, typename GT, typename LPT, int PHASE>
+__device__ __forceinline__ void nvls_phase(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
+                                           size_t lo, size_t nunits, size_t tid, size_t nth,
+                                           double &sum_w2, double &sum_r2, float lr_scale) {
+  constexpr int V = Multimem<GT>::kN;
+  for (size_t u = tid; u < nunits; u += nth) {
+    const size_t i = lo + u * V;
+    float g[V], w[V], m[V], v[V], m_[V], v_[V];
+    if constexpr (PHASE == 0) {
+      Multimem<GT>::ld_reduce((const GT *)ra.mc_g + i, g);
+#pragma unroll
+      for (int e = 0; e < V; ++e) g[e] = __fmul_rn(g[e], sa.grad_scale);
+    }
+    load_f32<V>(ra.w + i, w);
+    if constexpr (OPT != kSGD) {
+      load_f32<V>(ra.m + (i - lo), m);
+      load_f32<V>(ra.v + (i - lo), v);
+    }
+    if constexpr (PHASE == 0) {
+      if constexpr (OPT == kSGD) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) w[e] = sgd_elem(h, w[e], g[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) moments_elem(h, g[e], 0.f, m[e], v[e]);
+        corrected_moments<V>(h, m, v, m_, v_);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          if constexpr (OPT == kAdam) {
+            w[e] = adam_elem(h, w[e], m_[e], v_[e]);
+          } else {
+            const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
+            if (sa.flags & COCO_LAMB_REF_QUIRK) {
+              sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), (float)sa.count);
+              sum_w2 += (double)__fmul_rn(w[e], w[e]);
+            } else {
+              sum_r2 += (double)r * (double)r;
+              sum_w2 += (double)w[e] * (double)w[e];
+            }
+          }
+        }
+        store_f32<V>(ra.m + (i - lo), m);
+        store_f32<V>(ra.v + (i - lo), v);
+      }
+    } else {
+      corrected_moments<V>(h, m, v, m_, v_);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
+        w[e] = __fsub_rn(w[e], __fmul_rn(lr_scale, r));
+      }
+    }
+    if ((PHASE == 0 && OPT != kLAMB) || PHASE == 1) {
+      if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<V>(ra.w + i, w);
+      nvls_gather<LPT, V>(ra, sa.world, i, w);
+    }
+  }
+}
+
 // Grid-stride loops of the direct (register-staged) path over `nunits`
 // 4-element units starting at element `first`.
 template <int OPT, typename GT, typename LPT, int RB>
@@ -905,9 +1050,19 @@ __global__ void __launch_bounds__(512, 2)
       ok = false;
     }
   }
+  // NVLS: whole 16-byte units of the slice go through the switch; the rest
+  // (and everything when unaligned) falls through to the peer-to-peer code.
+  constexpr int NV = Multimem<GT>::kN;
+  const bool nvls = (sa.flags & kFlagNvls) && ra.pad && ra.mc_g && ra.mc_out &&
+                    sa.variant != cocoVariantNccl && tp.ntiles == 0;
+  const size_t nvls_units = nvls ? L / NV : 0;
+  if (ok && nvls)
+    nvls_phase<OPT, GT, LPT, 0>(ra, sa, h, lo, nvls_units, tid, nth, sum_w2, sum_r2, 0.f);
   if (ok) {
     const size_t first = lo + piped;
-    if (R == 1)
+    if (nvls) {
+      // nothing left for the vector loops; the scalar loop below takes the tail
+    } else if (R == 1)
       direct_step<OPT, GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
     else if (R == 2)
       direct_step<OPT, GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
@@ -915,7 +1070,8 @@ __global__ void __launch_bounds__(512, 2)
       direct_step<OPT, GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
     else
       direct_step<OPT, GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
-    for (size_t j = piped + nvec_rest * VEC + tid; j < L; j += nth)
+    const size_t done_elems = nvls ? nvls_units * NV : piped + nvec_rest * VEC;
+    for (size_t j = done_elems + tid; j < L; j += nth)
       step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, lo, lo + j, sum_w2, sum_r2);
   }
 
@@ -989,9 +1145,12 @@ __global__ void __launch_bounds__(512, 2)
         if (threadIdx.x == 0) record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
         ok = false;
       }
+      if (ok && nvls)
+        nvls_phase<OPT, GT, LPT, 1>(ra, sa, h, lo, nvls_units, tid, nth, sum_w2, sum_r2, lr_scale);
       if (ok) {
         const size_t first = lo + piped;
-        if (R == 1)
+        if (nvls) {
+        } else if (R == 1)
           direct_apply<GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
         else if (R == 2)
           direct_apply<GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
@@ -999,7 +1158,8 @@ __global__ void __launch_bounds__(512, 2)
           direct_apply<GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
         else
           direct_apply<GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
-        for (size_t j = piped + nvec_rest * VEC + tid; j < L; j += nth)
+        const size_t done_elems = nvls ? nvls_units * NV : piped + nvec_rest * VEC;
+        for (size_t j = done_elems + tid; j < L; j += nth)
           lamb_apply_unit<LPT, 1, 0>(ra, sa, h, lo, lo + j, lr_scale);
       }
     }

@@ -43,9 +43,14 @@ struct RankArgs {
   float *w;                   // own fp32 weights, element 0 (N elements)
   float *m;                   // own first moment, slice-local (S elements)
   float *v;                   // own second moment, slice-local
+  const void *mc_g;           // NVLS multicast address of the gradient buffers, or null
+  void *mc_out;               // NVLS multicast address of the gathered output, or null
   int rank;
-  int pad;
+  int pad;                    // non-zero: slice start and all pointers are 16-byte aligned
 };
+
+// Internal StepArgs::flags bit (public flags use the low byte).
+constexpr unsigned kFlagNvls = 0x100u;  // reduce / gather through NVSwitch multicast
 
 // Scalars of one fused call, identical on every rank.
 struct StepArgs {

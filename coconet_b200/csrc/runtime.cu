@@ -94,6 +94,7 @@ struct Region {
   char *base = nullptr;
   size_t bytes = 0;
   char *peer[kMaxRanks] = {};
+  char *multicast = nullptr;  // NVLS address of the same buffers, when the caller mapped one
 };
 
 struct IpcBlob {
@@ -142,6 +143,7 @@ struct cocoComm {
   int timeout_ms = 10000;
   int smem_budget_kb = 200;  // shared memory the tile pipeline may use per SM
   bool pipeline = false;     // COCO_PIPELINE=1: stage tiles in shared memory by bulk copies
+  bool nvls = false;         // COCO_ALGO=nvls: reduce / gather through NVSwitch multicast
 };
 
 namespace {
@@ -176,6 +178,10 @@ int init_common(cocoComm *c) {
   c->threads = env_int("COCO_THREADS", 512);
   if (c->threads < 32 || c->threads > 512 || (c->threads % 32) != 0) c->threads = 512;
   c->pipeline = env_int("COCO_PIPELINE", 0) != 0;
+  {
+    const char *algo = getenv("COCO_ALGO");
+    c->nvls = algo && !strcmp(algo, "nvls");
+  }
   c->smem_budget_kb = std::max(16, std::min(220, env_int("COCO_SMEM_KB", 200)));
   c->timeout_ms = env_int("COCO_TIMEOUT_MS", 10000);
   if (c->timeout_ms <= 0) c->timeout_ms = 10000;
@@ -269,7 +275,9 @@ const Region *find_region(const cocoComm *c, const void *ptr, size_t bytes) {
 }
 
 // Peer views of [ptr, ptr+bytes); registers the buffer on first use.
-int peer_views(cocoComm *c, const void *ptr, size_t bytes, char *views[kMaxRanks]) {
+int peer_views(cocoComm *c, const void *ptr, size_t bytes, char *views[kMaxRanks],
+               char **multicast) {
+  *multicast = nullptr;
   if (c->world == 1) {
     views[0] = (char *)ptr;
     return cocoSuccess;
@@ -284,6 +292,7 @@ int peer_views(cocoComm *c, const void *ptr, size_t bytes, char *views[kMaxRanks
   }
   const size_t off = (const char *)ptr - r->base;
   for (int p = 0; p < c->world; ++p) views[p] = r->peer[p] + off;
+  if (r->multicast) *multicast = r->multicast + off;
   return cocoSuccess;
 }
 
@@ -370,11 +379,16 @@ void fill_rank_args(RankArgs *ra, int rank, int world, char *const g_views[], ch
 // Launch of one rank that owns its device alone (process mode, or a
 // single-process rank with a device of its own).
 int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
-                  char *const out_views[]) {
+                  char *const out_views[], char *mc_g, char *mc_out) {
   RankArgs ra;
   fill_rank_args(&ra, c->rank, c->world, g_views, out_views, c->peer_flags, pc);
   LaunchConfig cfg;
   StepArgs sa = pc.sa;
+  if (c->nvls && mc_g && mc_out && aligned16(mc_g) && aligned16(mc_out)) {
+    ra.mc_g = mc_g;
+    ra.mc_out = mc_out;
+    sa.flags |= kFlagNvls;
+  }
   COCO_TRY(pick_launch(c, pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, pc.sa.count,
                        c->world, 1, &sa, &cfg));
   CUDA_TRY(launch_fused_step(pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, sa, ra, nullptr,
@@ -482,12 +496,13 @@ int enqueue(cocoComm *c, PendingCall &pc) {
   DeviceGuard guard(c->device);
   if (!guard.ok) return cocoCudaError;
   char *g_views[kMaxRanks] = {}, *out_views[kMaxRanks] = {};
-  COCO_TRY(peer_views(c, pc.g, pc.sa.count * dtype_size(pc.g_type), g_views));
+  char *mc_g = nullptr, *mc_out = nullptr;
+  COCO_TRY(peer_views(c, pc.g, pc.sa.count * dtype_size(pc.g_type), g_views, &mc_g));
   if (pc.w_lp)
-    COCO_TRY(peer_views(c, pc.w_lp, pc.sa.count * dtype_size(pc.lp_type), out_views));
+    COCO_TRY(peer_views(c, pc.w_lp, pc.sa.count * dtype_size(pc.lp_type), out_views, &mc_out));
   else
-    COCO_TRY(peer_views(c, pc.w, pc.sa.count * sizeof(float), out_views));
-  return launch_single(c, pc, g_views, out_views);
+    COCO_TRY(peer_views(c, pc.w, pc.sa.count * sizeof(float), out_views, &mc_out));
+  return launch_single(c, pc, g_views, out_views, mc_g, mc_out);
 }
 
 void set_denominators(StepArgs *sa, int opt, int step) {
@@ -761,6 +776,30 @@ int cocoRegister(cocoComm_t comm, void *ptr, size_t bytes) {
   Region reg;
   COCO_TRY(map_region_ipc(comm, ptr, bytes, &reg));
   comm->regions.push_back(reg);
+  return cocoSuccess;
+}
+
+int cocoRegisterMapped(cocoComm_t comm, void *ptr, size_t bytes, void *const *peer_ptrs,
+                       void *multicast_ptr) {
+  if (!comm || !ptr || bytes == 0 || !peer_ptrs) return cocoInvalidArgument;
+  if (comm->group) return cocoInvalidUsage;
+  if (peer_ptrs[comm->rank] != ptr) return cocoInvalidArgument;
+  Region reg;
+  reg.base = (char *)ptr;
+  reg.bytes = bytes;
+  for (int p = 0; p < comm->world; ++p) {
+    if (!peer_ptrs[p]) return cocoInvalidArgument;
+    reg.peer[p] = (char *)peer_ptrs[p];
+  }
+  reg.multicast = (char *)multicast_ptr;
+  // newest first, so that it wins over an older registration of the same range
+  comm->regions.insert(comm->regions.begin(), reg);
+  return cocoSuccess;
+}
+
+int cocoSetAlgo(cocoComm_t comm, int algo) {
+  if (!comm || (algo != 0 && algo != 1)) return cocoInvalidArgument;
+  comm->nvls = algo == 1;
   return cocoSuccess;
 }
 

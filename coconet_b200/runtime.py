@@ -51,6 +51,9 @@ _SIGNATURES = {
     "cocoGroupEnd": (C.c_int, []),
     "cocoRegister": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "cocoDeregister": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "cocoRegisterMapped": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p),
+                                     C.c_void_p]),
+    "cocoSetAlgo": (C.c_int, [C.c_void_p, C.c_int]),
     "cocoFusedSGD": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                C.c_size_t, C.c_float, C.c_float, C.c_void_p]),
     "cocoFusedAdam": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
@@ -209,6 +212,16 @@ class Communicator:
 
     def register(self, t):
         _check(lib().cocoRegister(self._h, _ptr(t), t.numel() * t.element_size()), "cocoRegister")
+
+    def register_mapped(self, t, peer_ptrs, multicast_ptr=0):
+        """Register a tensor whose peer mappings (and optional NVLS multicast
+        address) the caller already holds, e.g. torch symmetric memory."""
+        arr = (C.c_void_p * self.world)(*peer_ptrs)
+        _check(lib().cocoRegisterMapped(self._h, _ptr(t), t.numel() * t.element_size(), arr,
+                                        C.c_void_p(multicast_ptr or None)), "cocoRegisterMapped")
+
+    def set_algo(self, nvls):
+        _check(lib().cocoSetAlgo(self._h, 1 if nvls else 0), "cocoSetAlgo")
 
     def set_tunables(self, ctas_per_sm=0, threads=0, timeout_ms=0):
         _check(lib().cocoSetTunables(self._h, ctas_per_sm, threads, timeout_ms), "cocoSetTunables")

@@ -151,6 +151,24 @@ int cocoGroupEnd(void);
 int cocoRegister(cocoComm_t comm, void *ptr, size_t bytes);
 int cocoDeregister(cocoComm_t comm, void *ptr);
 
+/* Local (not collective).  Registers a buffer whose peer mappings the caller
+ * already holds -- symmetric memory made with cuMemCreate/cuMemMap or by
+ * another library: peer_ptrs[r] is this process's address of rank r's buffer
+ * (peer_ptrs[rank] == ptr).  multicast_ptr, when not NULL, is an NVLS
+ * multicast address bound to the same R buffers (cuMulticastCreate /
+ * cuMulticastBindMem); it enables the NVSwitch path selected by
+ * cocoSetAlgo(comm, 1) or COCO_ALGO=nvls: one multimem.ld_reduce per 16 bytes
+ * for the reduce-scatter and one multimem.st for the all-gather.  The
+ * reference's nearest counterpart is CollNet (nccl/src/collectives/device/
+ * all_reduce_computation.h:262-316, left as assert(false) there). */
+int cocoRegisterMapped(cocoComm_t comm, void *ptr, size_t bytes, void *const *peer_ptrs,
+                       void *multicast_ptr);
+/* 0: peer-to-peer loads and stores in fixed rank order (default; results
+ * reproducible bit for bit).  1: NVLS where both buffers have a multicast
+ * address (in-switch summation order; 16-bit sums delivered rounded to 16
+ * bits; within the stated tolerances only). */
+int cocoSetAlgo(cocoComm_t comm, int algo);
+
 /* ---- the fused step -----------------------------------------------------
  * All three enqueue one kernel on `stream` and return.  grad_scale multiplies
  * the reduced gradient (1/loss_scale for mixed precision; pass 1.0f else).

@@ -80,6 +80,84 @@ def case_parity(comm):
              loss_scale=1024.0, exact_w=False)
 
 
+def symmetric_buffers(comm, shapes):
+    """torch symmetric memory as plumbing: peer pointers + NVLS multicast
+    address of each buffer, registered with the communicator."""
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+    out = []
+    for numel, dtype in shapes:
+        t = symm_mem.empty(numel, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        h = symm_mem.rendezvous(t, dist.group.WORLD)
+        mc = int(h.multicast_ptr)
+        comm.register_mapped(t, [int(p) for p in h.buffer_ptrs], mc)
+        out.append((t, mc, h))
+    return out
+
+
+def case_nvls(comm):
+    """NVSwitch multicast path (multimem.ld_reduce / multimem.st).  The in-switch
+    sum has its own order and 16-bit sums arrive rounded to 16 bits, so parity
+    is to tolerance: rel 1e-5 for fp32 gradients, rel 2e-3 for fp16 gradients."""
+    import torch.distributed as dist
+    R, rank = comm.world, comm.rank
+    h = K.HYPER
+    for name, opt, n, g16, lp in [("nvls_adam_mixed", K.ADAM, 1 << 22, True, True),
+                                  ("nvls_adam_fp32", K.ADAM, (1 << 21) + 64, False, False),
+                                  ("nvls_sgd_fp32", K.SGD, 1 << 20, False, False),
+                                  ("nvls_lamb_fp32", K.LAMB, 1 << 21, False, False)]:
+        gdt = torch.float16 if g16 else torch.float32
+        shapes = [(n, gdt), (n, torch.float16 if lp else torch.float32)]
+        (g, mc_g, _h1), (out, mc_o, _h2) = symmetric_buffers(comm, shapes)
+        if not (mc_g and mc_o):
+            if rank == 0:
+                print("skip nvls: no multicast support", flush=True)
+            return
+        comm.set_algo(True)
+        ora = K.OracleState(opt, n, seed=55, lp=lp)
+        if lp:
+            w, w_lp = torch.from_numpy(ora.w.copy()).cuda(), out
+        else:
+            out.copy_(torch.from_numpy(ora.w))
+            w, w_lp = out, None
+        S = (n + R - 1) // R
+        m, v = torch.zeros(S, device="cuda"), torch.zeros(S, device="cuda")
+        lo, hi = K.slice_bounds(n, R, rank)
+        ls = 1024.0 if g16 else 1.0
+        rtol = 2e-3 if g16 else 1e-5
+        for step in range(3):
+            grads = K.make_grads(R, n, 55, step, dtype=np.float16 if g16 else np.float32, loss_scale=ls)
+            g.copy_(torch.from_numpy(grads[rank]))
+            torch.cuda.synchronize()
+            dist.barrier()
+            if opt == K.SGD:
+                comm.fused_sgd(g, w, h["lr"], w_lp=w_lp, grad_scale=1 / ls)
+            elif opt == K.ADAM:
+                comm.fused_adam(g, w, m, v, h["lr"], h["beta1"], h["beta2"], h["eps"], step,
+                                w_lp=w_lp, grad_scale=1 / ls)
+            else:
+                comm.fused_lamb(g, w, m, v, h["lr"], h["beta1"], h["beta2"], h["eps"],
+                                h["weight_decay"], step, w_lp=w_lp, grad_scale=1 / ls)
+            torch.cuda.synchronize()
+            st = comm.status()
+            assert st["code"] == 0, f"{name}: {st}"
+            ora.step(grads, step, inv_scale=1 / ls)
+            wh = w.cpu().numpy()
+            if lp:
+                K.assert_close(wh[lo:hi], ora.w[lo:hi], rtol, f"{name} master")
+                K.assert_close(w_lp.float().cpu().numpy(), ora.w_lp.astype(np.float32), 4e-3, f"{name} w_lp")
+            else:
+                K.assert_close(wh, ora.w, rtol, f"{name} w")
+            if opt != K.SGD:
+                # v = (1-b2) g^2 doubles the relative error of g
+                K.assert_close(m.cpu().numpy()[: hi - lo], ora.m[lo:hi], rtol, f"{name} m")
+                K.assert_close(v.cpu().numpy()[: hi - lo], ora.v[lo:hi], 3 * rtol, f"{name} v")
+            dist.barrier()
+        comm.set_algo(False)
+        if rank == 0:
+            print(f"ok {name} R={R} n={n}", flush=True)
+
+
 def case_timeout(comm):
     """Rank 1 skips one fused call: the others' bounded start wait must give
     up with a status, leave the weights untouched and keep the context alive."""
@@ -110,8 +188,24 @@ if __name__ == "__main__":
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    failed = False
+    if sys.argv[1] == "nvls":
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     comm = coco.Communicator.init_rank(world, rank)
     try:
-        {"parity": case_parity, "timeout": case_timeout}[sys.argv[1]](comm)
-    finally:
-        comm.destroy()
+        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls}[sys.argv[1]](comm)
+    except Exception:  # keep this rank alive until its peers are done with its memory
+        import traceback
+        print("WORKER FAILURE rank %d\n%s" % (rank, traceback.format_exc()), flush=True)
+        failed = True
+    try:
+        comm.barrier()
+    except Exception:
+        pass
+    torch.cuda.synchronize()
+    comm.destroy()
+    if sys.argv[1] == "nvls":
+        dist.barrier()
+        dist.destroy_process_group()
+    sys.exit(1 if failed else 0)

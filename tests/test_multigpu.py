@@ -18,6 +18,11 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
+def _why(r):
+    k = r.stdout.find("WORKER FAILURE")
+    return (r.stdout[k:k + 4000] if k >= 0 else r.stdout[-3000:]) + r.stderr[-1500:]
+
+
 def _launch(case, world, timeout=600):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -36,12 +41,20 @@ def _launch(case, world, timeout=600):
 def test_parity_all_gpus():
     world = min(_ngpu(), 8)
     r = _launch("parity", world)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, _why(r)
     assert r.stdout.count("ok ") >= 8, r.stdout
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
 def test_absent_rank_times_out_cleanly():
     r = _launch("timeout", 2)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, _why(r)
     assert "ok timeout" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_nvls_multicast_path():
+    world = min(_ngpu(), 8)
+    r = _launch("nvls", world)
+    assert r.returncode == 0, _why(r)
+    assert "ok nvls_lamb_fp32" in r.stdout or "skip nvls" in r.stdout, r.stdout
