@@ -152,7 +152,8 @@ def main():
     ap.add_argument("--no-baseline", action="store_true", help="skip the stock NCCL comparison (N > 1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--algo", default=os.environ.get("COCO_BENCH_ALGO", "p2p"), choices=["p2p", "nvls"],
+    ap.add_argument("--algo", default=os.environ.get("COCO_BENCH_ALGO", "auto"),
+                    choices=["auto", "p2p", "nvls"],
                     help="nvls: gradients and fp16 weights in symmetric memory with an NVSwitch "
                          "multicast mapping; reduce-scatter and all-gather go through the switch")
     args = ap.parse_args()
@@ -188,7 +189,8 @@ def main():
     S = (N + R - 1) // R
     gen = torch.Generator(device=dev).manual_seed(1000 + rank)
     # two gradient buffers, alternated, each far larger than L2 (126 MB)
-    use_nvls = args.algo == "nvls" and world > 1
+    # auto: the NVSwitch path from 4 ranks on (fewer bytes per link), else peer-to-peer
+    use_nvls = world > 1 and (args.algo == "nvls" or (args.algo == "auto" and world >= 4))
     symm = []
 
     def comm_buffer(numel):
@@ -200,7 +202,7 @@ def main():
         t = symm_mem.empty(numel, dtype=torch.float16, device=dev)
         h = symm_mem.rendezvous(t, dist.group.WORLD)
         mc = int(h.multicast_ptr)
-        if not mc:
+        if not mc and args.algo == "nvls":
             raise SystemExit("--algo nvls: this node exposes no NVLS multicast")
         comm.register_mapped(t, [int(p) for p in h.buffer_ptrs], mc)
         symm.append(h)
@@ -221,7 +223,8 @@ def main():
     m = torch.zeros(S, device=dev)
     v = torch.zeros(S, device=dev)
     if use_nvls:
-        comm.set_algo(True)
+        comm.set_algo("nvls")
+        use_nvls = all(int(h.multicast_ptr) != 0 for h in symm)  # else the runtime uses peer-to-peer
     else:
         for t in g:
             comm.register(t)

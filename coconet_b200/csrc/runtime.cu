@@ -143,7 +143,7 @@ struct cocoComm {
   int timeout_ms = 10000;
   int smem_budget_kb = 200;  // shared memory the tile pipeline may use per SM
   bool pipeline = false;     // COCO_PIPELINE=1: stage tiles in shared memory by bulk copies
-  bool nvls = false;         // COCO_ALGO=nvls: reduce / gather through NVSwitch multicast
+  int algo = 2;              // 0 p2p, 1 nvls, 2 auto (COCO_ALGO=p2p|nvls|auto)
 };
 
 namespace {
@@ -180,7 +180,7 @@ int init_common(cocoComm *c) {
   c->pipeline = env_int("COCO_PIPELINE", 0) != 0;
   {
     const char *algo = getenv("COCO_ALGO");
-    c->nvls = algo && !strcmp(algo, "nvls");
+    c->algo = !algo ? 2 : !strcmp(algo, "nvls") ? 1 : !strcmp(algo, "p2p") ? 0 : 2;
   }
   c->smem_budget_kb = std::max(16, std::min(220, env_int("COCO_SMEM_KB", 200)));
   c->timeout_ms = env_int("COCO_TIMEOUT_MS", 10000);
@@ -384,7 +384,11 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
   fill_rank_args(&ra, c->rank, c->world, g_views, out_views, c->peer_flags, pc);
   LaunchConfig cfg;
   StepArgs sa = pc.sa;
-  if (c->nvls && mc_g && mc_out && aligned16(mc_g) && aligned16(mc_out)) {
+  // NVLS moves (1 + 1/R) N s bytes per direction, peer-to-peer 2 (R-1)/R N s:
+  // the switch wins from R = 4 on ("auto").  It needs multicast addresses for
+  // both buffers, i.e. buffers registered with cocoRegisterMapped.
+  const bool want_nvls = c->algo == 1 || (c->algo == 2 && c->world >= 4);
+  if (want_nvls && mc_g && mc_out && aligned16(mc_g) && aligned16(mc_out)) {
     ra.mc_g = mc_g;
     ra.mc_out = mc_out;
     sa.flags |= kFlagNvls;
@@ -798,8 +802,8 @@ int cocoRegisterMapped(cocoComm_t comm, void *ptr, size_t bytes, void *const *pe
 }
 
 int cocoSetAlgo(cocoComm_t comm, int algo) {
-  if (!comm || (algo != 0 && algo != 1)) return cocoInvalidArgument;
-  comm->nvls = algo == 1;
+  if (!comm || algo < 0 || algo > 2) return cocoInvalidArgument;
+  comm->algo = algo;
   return cocoSuccess;
 }
 

@@ -220,8 +220,10 @@ class Communicator:
         _check(lib().cocoRegisterMapped(self._h, _ptr(t), t.numel() * t.element_size(), arr,
                                         C.c_void_p(multicast_ptr or None)), "cocoRegisterMapped")
 
-    def set_algo(self, nvls):
-        _check(lib().cocoSetAlgo(self._h, 1 if nvls else 0), "cocoSetAlgo")
+    def set_algo(self, algo):
+        """0 / False / "p2p", 1 / True / "nvls", 2 / "auto"."""
+        code = {"p2p": 0, "nvls": 1, "auto": 2}.get(algo, algo)
+        _check(lib().cocoSetAlgo(self._h, int(code)), "cocoSetAlgo")
 
     def set_tunables(self, ctas_per_sm=0, threads=0, timeout_ms=0):
         _check(lib().cocoSetTunables(self._h, ctas_per_sm, threads, timeout_ms), "cocoSetTunables")

@@ -163,10 +163,13 @@ int cocoDeregister(cocoComm_t comm, void *ptr);
  * all_reduce_computation.h:262-316, left as assert(false) there). */
 int cocoRegisterMapped(cocoComm_t comm, void *ptr, size_t bytes, void *const *peer_ptrs,
                        void *multicast_ptr);
-/* 0: peer-to-peer loads and stores in fixed rank order (default; results
- * reproducible bit for bit).  1: NVLS where both buffers have a multicast
- * address (in-switch summation order; 16-bit sums delivered rounded to 16
- * bits; within the stated tolerances only). */
+/* 0: peer-to-peer loads and stores, gradients summed in fixed rank order
+ * (results reproducible bit for bit).  1: NVLS wherever both buffers have a
+ * multicast address (in-switch summation order; 16-bit sums delivered rounded
+ * to 16 bits; within the stated tolerances, not bit-exact).  2 (default, also
+ * COCO_ALGO=auto): NVLS from world size 4 on, where it moves fewer bytes per
+ * link, else peer-to-peer.  Buffers without a multicast address always take
+ * the peer-to-peer path. */
 int cocoSetAlgo(cocoComm_t comm, int algo);
 
 /* ---- the fused step -----------------------------------------------------

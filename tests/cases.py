@@ -78,3 +78,16 @@ def assert_close(actual, expect, rtol, what):
         i = int(np.argmax(err - tol))
         raise AssertionError(f"{what}: {int(bad.sum())} of {a.size} outside rtol {rtol}; "
                              f"worst at [{i}]: got {a[i]!r}, want {b[i]!r}")
+
+
+def assert_close_most(actual, expect, rtol, what, frac=1e-3, rtol_all=2e-3):
+    """For sums whose order is not fixed (in-switch reduction): all but a
+    fraction `frac` of the elements within rtol, every element within
+    rtol_all.  The outliers are elements whose gradient sum nearly cancels, on
+    which Adam's m/sqrt(v) amplifies the last-bit difference of the sum."""
+    assert_close(actual, expect, rtol_all, what + " (all elements)")
+    a = np.asarray(actual, np.float64)
+    b = np.asarray(expect, np.float64)
+    tol = rtol * np.maximum(np.abs(a), np.abs(b)) + rtol * 1e-3
+    bad = int((np.abs(a - b) > tol).sum())
+    assert bad <= frac * a.size, f"{what}: {bad} of {a.size} outside rtol {rtol}"
