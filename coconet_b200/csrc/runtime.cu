@@ -95,6 +95,13 @@ struct Region {
   size_t bytes = 0;
   char *peer[kMaxRanks] = {};
   char *multicast = nullptr;  // NVLS address of the same buffers, when the caller mapped one
+  std::vector<std::string> ipc_keys;  // mappings this region holds a reference on
+  bool external = false;              // registered with cocoRegisterMapped: nothing to close
+};
+
+struct IpcMapping {
+  void *base = nullptr;
+  int refs = 0;
 };
 
 struct IpcBlob {
@@ -128,7 +135,7 @@ struct cocoComm {
   // process mode
   std::unique_ptr<Bootstrap> boot;
   std::vector<Region> regions;
-  std::map<std::string, void *> ipc_open;  // "<peer>:<handle bytes>" -> mapped base
+  std::map<std::string, IpcMapping> ipc_open;  // "<peer>:<handle bytes>" -> mapped base
   // single-process mode
   std::shared_ptr<LocalGroup> group;
   bool has_pending = false;
@@ -252,7 +259,8 @@ int map_region_ipc(cocoComm *c, void *ptr, size_t bytes, Region *out) {
     void *mapped = nullptr;
     auto it = c->ipc_open.find(key);
     if (it != c->ipc_open.end()) {
-      mapped = it->second;
+      mapped = it->second.base;
+      it->second.refs++;
     } else {
       cudaError_t e = cudaIpcOpenMemHandle(&mapped, all[r].handle, cudaIpcMemLazyEnablePeerAccess);
       if (e != cudaSuccess) {
@@ -260,8 +268,12 @@ int map_region_ipc(cocoComm *c, void *ptr, size_t bytes, Region *out) {
         (void)cudaGetLastError();
         return cocoPeerError;
       }
-      c->ipc_open[key] = mapped;
+      IpcMapping mp;
+      mp.base = mapped;
+      mp.refs = 1;
+      c->ipc_open[key] = mp;
     }
+    out->ipc_keys.push_back(key);
     out->peer[r] = (char *)mapped + all[r].offset;
   }
   return cocoSuccess;
@@ -661,7 +673,7 @@ int cocoCommDestroy(cocoComm_t comm) {
   if (!comm) return cocoInvalidArgument;
   DeviceGuard guard(comm->device);
   cudaDeviceSynchronize();
-  for (auto &kv : comm->ipc_open) cudaIpcCloseMemHandle(kv.second);
+  for (auto &kv : comm->ipc_open) cudaIpcCloseMemHandle(kv.second.base);
   if (comm->group) {
     std::lock_guard<std::mutex> lock(comm->group->mu);
     auto &v = comm->group->comms;
@@ -796,6 +808,7 @@ int cocoRegisterMapped(cocoComm_t comm, void *ptr, size_t bytes, void *const *pe
     reg.peer[p] = (char *)peer_ptrs[p];
   }
   reg.multicast = (char *)multicast_ptr;
+  reg.external = true;
   // newest first, so that it wins over an older registration of the same range
   comm->regions.insert(comm->regions.begin(), reg);
   return cocoSuccess;
@@ -809,13 +822,32 @@ int cocoSetAlgo(cocoComm_t comm, int algo) {
 
 int cocoDeregister(cocoComm_t comm, void *ptr) {
   if (!comm || !ptr) return cocoInvalidArgument;
+  if (comm->world == 1 || comm->group) return cocoSuccess;
+  DeviceGuard guard(comm->device);
+  // finish whatever still uses the mapping on this rank
+  CUDA_TRY(cudaDeviceSynchronize());
   auto &v = comm->regions;
+  bool found = false, external = false;
   for (size_t k = 0; k < v.size(); ++k)
     if (v[k].base == (char *)ptr) {
+      external = v[k].external;
+      for (const std::string &key : v[k].ipc_keys) {
+        auto it = comm->ipc_open.find(key);
+        if (it != comm->ipc_open.end() && --it->second.refs == 0) {
+          cudaIpcCloseMemHandle(it->second.base);
+          comm->ipc_open.erase(it);
+        }
+      }
       v.erase(v.begin() + k);
-      return cocoSuccess;
+      found = true;
+      break;
     }
-  return (comm->world == 1 || comm->group) ? cocoSuccess : cocoInvalidArgument;
+  if (external) return cocoSuccess;  // local registration, local removal
+  // collective: nobody may free its buffer before every peer has unmapped it
+  int ok = found ? 1 : 0;
+  std::vector<int> all(comm->world);
+  COCO_TRY(comm->boot->all_gather(&ok, all.data(), sizeof(int)));
+  return found ? cocoSuccess : cocoInvalidArgument;
 }
 
 int cocoFusedSGD(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w, void *w_lp,

@@ -1,0 +1,115 @@
+// Data-parallel optimizer steps written in the CoCoNet DSL, in the three
+// schedules of the CoCoNet paper:
+//   AR_C          AllReduce, then the update on every element on every rank
+//   RS_C_AG       ReduceScatter, update of the rank's slice, AllGather
+//   fuse_RS_C_AG  the same, fused into one kernel (the B200 runtime's path)
+// usage: optimizers <sgd|adam|lamb> <AR_C|RS_C_AG|fuse_RS_C_AG> [output.cu]
+#include <dsl.hpp>
+#include <pipeline.hpp>
+
+#include <iostream>
+#include <string>
+
+using namespace ACCCDSL;
+
+static void sgd(const std::string &schedule, const std::string &out) {
+  Variable N(Int32, "N");
+  Variable lr(Float32, "lr");
+  Tensor g(Float32, N, Local, "g");
+  Tensor w(Float32, N, Replicated, "w");
+  if (schedule == "AR_C") {
+    Stage gsum = AllReduce(Summation, g);
+    Stage wnew = Update(w, w - lr * gsum);
+    Pipeline pipeline("sgd", {g, w, lr}, {wnew});
+    pipeline.codegen(out);
+    return;
+  }
+  Stage gslice = ReduceScatter(Summation, g);
+  Stage wslice = Scatter(w) - lr * gslice;
+  Stage wnew = Update(w, AllGather(wslice));
+  Pipeline pipeline("sgd", {g, w, lr}, {wnew});
+  if (schedule == "fuse_RS_C_AG") pipeline.fuse({gslice, wslice, wnew});
+  pipeline.codegen(out);
+}
+
+static void adam(const std::string &schedule, const std::string &out) {
+  Variable N(Int32, "N");
+  Variable lr(Float32, "lr"), beta1(Float32, "beta1"), beta2(Float32, "beta2");
+  Tensor g(Float32, N, Local, "g");
+  Tensor w(Float32, N, Replicated, "w");
+  const bool sliced = schedule != "AR_C";
+  Tensor m(Float32, N, sliced ? Sliced : Replicated, "m");
+  Tensor v(Float32, N, sliced ? Sliced : Replicated, "v");
+  Stage gred = sliced ? Stage(ReduceScatter(Summation, g)) : Stage(AllReduce(Summation, g));
+  Stage mnew = Update(m, beta1 * m + (1 - beta1) * gred);
+  Stage vnew = Update(v, beta2 * v + (1 - beta2) * gred * gred);
+  Stage mhat = mnew / beta1;
+  Stage vhat = vnew / beta2;
+  if (!sliced) {
+    Stage wnew = Update(w, w - lr * mhat / vhat);
+    Pipeline pipeline("adam", {g, w, m, v, lr, beta1, beta2}, {mnew, vnew, wnew});
+    pipeline.fuse({mnew, vnew, mhat, vhat, wnew});
+    pipeline.codegen(out);
+    return;
+  }
+  Stage wslice = Scatter(w) - lr * mhat / vhat;
+  Stage wnew = Update(w, AllGather(wslice));
+  Pipeline pipeline("adam", {g, w, m, v, lr, beta1, beta2}, {mnew, vnew, wnew});
+  if (schedule == "fuse_RS_C_AG")
+    pipeline.fuse({gred, mnew, vnew, mhat, vhat, wslice, wnew});
+  else
+    pipeline.fuse({mnew, vnew, mhat, vhat, wslice});
+  pipeline.codegen(out);
+}
+
+static void lamb(const std::string &schedule, const std::string &out) {
+  Variable N(Int32, "N");
+  Variable lr(Float32, "lr"), beta1(Float32, "beta1"), beta2(Float32, "beta2");
+  Variable decay(Float32, "decay");
+  Tensor g(Float32, N, Local, "g");
+  Tensor w(Float32, N, Replicated, "w");
+  const bool sliced = schedule != "AR_C";
+  Tensor m(Float32, N, sliced ? Sliced : Replicated, "m");
+  Tensor v(Float32, N, sliced ? Sliced : Replicated, "v");
+  Stage gred = sliced ? Stage(ReduceScatter(Summation, g)) : Stage(AllReduce(Summation, g));
+  Stage mnew = Update(m, beta1 * m + (1.0 - beta1) * gred);
+  Stage vnew = Update(v, beta2 * v + (1.0 - beta2) * gred * gred);
+  Stage mhat = mnew / (1.0 - beta1);
+  Stage vhat = vnew / (1.0 - beta2);
+  Stage r = mhat / Sqrt(vhat) + decay * w;
+  Stage rnorm = Norm(r);
+  Stage wnorm = Norm(w);
+  Stage wstep = w - lr * (wnorm / rnorm) * r;
+  if (!sliced) {
+    Stage wnew = Update(w, wstep);
+    Pipeline pipeline("lamb", {g, w, m, v, lr, beta1, beta2, decay}, {wnew});
+    pipeline.fuse({mnew, vnew, mhat, vhat, r, rnorm, wnorm, wstep, wnew});
+    pipeline.codegen(out);
+    return;
+  }
+  Stage wnew = Update(w, AllGather(wstep));
+  Pipeline pipeline("lamb", {g, w, m, v, lr, beta1, beta2, decay}, {wnew});
+  if (schedule == "fuse_RS_C_AG")
+    pipeline.fuse({gred, mnew, vnew, mhat, vhat, r, rnorm, wnorm, wstep, wnew});
+  else
+    pipeline.fuse({mnew, vnew, mhat, vhat, r, rnorm, wnorm, wstep});
+  pipeline.codegen(out);
+}
+
+int main(int argc, char **argv) {
+  if (argc < 3) {
+    std::cout << "usage: " << argv[0] << " <sgd|adam|lamb> <AR_C|RS_C_AG|fuse_RS_C_AG> [out.cu]\n";
+    return 1;
+  }
+  const std::string opt = argv[1], schedule = argv[2];
+  if (schedule != "AR_C" && schedule != "RS_C_AG" && schedule != "fuse_RS_C_AG") {
+    std::cout << "Invalid schedule" << std::endl;
+    return 1;
+  }
+  const std::string out = argc > 3 ? argv[3] : opt + "-" + schedule + ".cu";
+  if (opt == "sgd") sgd(schedule, out);
+  else if (opt == "adam") adam(schedule, out);
+  else if (opt == "lamb") lamb(schedule, out);
+  else { std::cout << "Invalid optimizer" << std::endl; return 1; }
+  return 0;
+}

@@ -1,0 +1,373 @@
+// Pipeline: stage discovery, fusion groups, recognition of the fused update
+// rule.  (What the reference does in src/pipeline.cpp:223-240, 298-426,
+// 905-935 with visitors over its AST is done here on the node DAG.)
+#include "pipeline.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <fstream>
+#include <functional>
+#include <random>
+
+namespace ACCCDSL {
+
+namespace {
+
+[[noreturn]] void fail(const std::string &msg) {
+  std::fprintf(stderr, "coconet pipeline: %s\n", msg.c_str());
+  std::exit(1);
+}
+
+// Stages that stage `s` reads directly (walking through unnamed nodes).
+void direct_deps(const NodeRef &n, bool root, std::vector<const Node *> *out) {
+  if (!root && n->stage_id >= 0) {
+    out->push_back(n.get());
+    return;
+  }
+  for (const NodeRef &c : n->in) direct_deps(c, false, out);
+}
+
+}  // namespace
+
+// All nodes owned by a stage: its expression tree down to (not including)
+// other stages.
+void ownedNodes(const NodeRef &n, bool root, std::vector<NodeRef> *out) {
+  if (!root && n->stage_id >= 0) return;
+  out->push_back(n);
+  for (const NodeRef &c : n->in) ownedNodes(c, false, out);
+}
+
+Pipeline::Pipeline(const std::string &name, std::initializer_list<Expression> args,
+                   std::initializer_list<Stage> outputs)
+    : name_(name) {
+  for (const Expression &a : args) {
+    if (!a.node() || (a.node()->kind != NodeKind::Variable && a.node()->kind != NodeKind::Tensor))
+      fail("pipeline '" + name + "': arguments must be Variables or Tensors");
+    args_.push_back(a.node());
+  }
+  for (const Stage &s : outputs) outputs_.push_back(s.node());
+  if (outputs_.empty()) fail("pipeline '" + name + "' has no outputs");
+
+  // post-order DFS from the outputs = a topological order of the stages
+  std::set<const Node *> seen;
+  std::function<void(const NodeRef &)> visit = [&](const NodeRef &n) {
+    if (!seen.insert(n.get()).second) return;
+    for (const NodeRef &c : n->in) visit(c);
+    if (n->stage_id >= 0) stages_.push_back(n);
+    if ((n->kind == NodeKind::Variable || n->kind == NodeKind::Tensor)) {
+      bool declared = false;
+      for (const NodeRef &a : args_) declared = declared || a.get() == n.get();
+      // the size Variable of a tensor need not be listed (the examples omit N)
+      if (!declared && !(n->kind == NodeKind::Variable && n->type == Int32))
+        fail("pipeline '" + name_ + "' uses '" + n->name + "' which is not among its arguments");
+    }
+  };
+  for (const NodeRef &o : outputs_) visit(o);
+}
+
+bool Pipeline::canFuse(const std::vector<NodeRef> &stages, std::string *why) const {
+  auto say = [&](const std::string &m) {
+    if (why) *why = m;
+    return false;
+  };
+  if (stages.empty()) return say("empty fusion set");
+  std::set<const Node *> members;
+  for (const NodeRef &s : stages) {
+    if (!s || s->stage_id < 0) return say("not a stage");
+    if (std::find(stages_.begin(), stages_.end(), s) == stages_.end())
+      return say("stage " + s->name + " is not part of pipeline '" + name_ + "'");
+    members.insert(s.get());
+  }
+  // include stages already fused with any member
+  for (const auto &g : fused_) {
+    bool touches = false;
+    for (const Node *m : members) touches = touches || g.count(m);
+    if (touches) members.insert(g.begin(), g.end());
+  }
+  // transitive dependencies between stages
+  std::map<const Node *, std::set<const Node *>> deps;
+  for (const NodeRef &s : stages_) {  // topological: deps of deps are complete
+    std::vector<const Node *> d;
+    direct_deps(s, true, &d);
+    for (const Node *x : d) {
+      deps[s.get()].insert(x);
+      deps[s.get()].insert(deps[x].begin(), deps[x].end());
+    }
+  }
+  // A stage outside the set that both depends on a member and is depended on
+  // by a member would have to run in the middle of the fused kernel.
+  for (const NodeRef &x : stages_) {
+    if (members.count(x.get())) continue;
+    bool uses_member = false, used_by_member = false;
+    for (const Node *m : members) {
+      uses_member = uses_member || deps[x.get()].count(m);
+      used_by_member = used_by_member || deps[m].count(x.get());
+    }
+    if (uses_member && used_by_member)
+      return say("fusing would create a cycle through stage " + x->name);
+  }
+  return true;
+}
+
+void Pipeline::fuse(std::initializer_list<Stage> stages) {
+  std::vector<NodeRef> v;
+  for (const Stage &s : stages) v.push_back(s.node());
+  std::string why;
+  if (!canFuse(v, &why)) fail("invalid fuse in pipeline '" + name_ + "': " + why);
+  std::set<const Node *> merged;
+  for (const NodeRef &s : v) merged.insert(s.get());
+  for (auto it = fused_.begin(); it != fused_.end();) {
+    bool touches = false;
+    for (const Node *m : merged) touches = touches || it->count(m);
+    if (touches) {
+      merged.insert(it->begin(), it->end());
+      it = fused_.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  fused_.push_back(merged);
+}
+
+std::vector<std::vector<NodeRef>> Pipeline::groups() const {
+  // group id per stage
+  std::map<const Node *, int> gid;
+  std::vector<std::vector<NodeRef>> groups;
+  for (const NodeRef &s : stages_) {
+    if (gid.count(s.get())) continue;
+    const std::set<const Node *> *fs = nullptr;
+    for (const auto &g : fused_)
+      if (g.count(s.get())) fs = &g;
+    std::vector<NodeRef> members;
+    if (fs) {
+      for (const NodeRef &t : stages_)
+        if (fs->count(t.get())) members.push_back(t);
+    } else {
+      members.push_back(s);
+    }
+    for (const NodeRef &t : members) gid[t.get()] = (int)groups.size();
+    groups.push_back(members);
+  }
+  // order the groups topologically (Kahn; ties by first stage)
+  const int G = (int)groups.size();
+  std::vector<std::set<int>> before(G);
+  for (int g = 0; g < G; ++g)
+    for (const NodeRef &s : groups[g]) {
+      std::vector<const Node *> d;
+      direct_deps(s, true, &d);
+      for (const Node *x : d)
+        if (gid[x] != g) before[g].insert(gid[x]);
+    }
+  std::vector<std::vector<NodeRef>> ordered;
+  std::vector<bool> done(G, false);
+  for (int round = 0; round < G; ++round) {
+    int pick = -1;
+    for (int g = 0; g < G && pick < 0; ++g) {
+      if (done[g]) continue;
+      bool ready = true;
+      for (int b : before[g]) ready = ready && done[b];
+      if (ready) pick = g;
+    }
+    if (pick < 0) fail("cyclic fusion groups in pipeline '" + name_ + "'");
+    done[pick] = true;
+    ordered.push_back(groups[pick]);
+  }
+  return ordered;
+}
+
+// ---------------------------------------------------------------------------
+// Recognising the update rule of a fused group.
+//
+// The reference keys on pipeline.name() (src/codegen.cpp:1906-1917).  Here the
+// group is evaluated as scalar arithmetic on random sample values -- a
+// collective is the identity on one element of the summed gradient, a Norm is
+// a free symbol -- and compared with the closed form of each rule under every
+// assignment of the program's tensors and variables to the rule's roles.
+// ---------------------------------------------------------------------------
+namespace {
+
+struct Probe {
+  std::map<const Node *, double> leaf;   // Variables, Tensors, Norm symbols
+  std::map<const Node *, double> memo;
+  std::map<const Node *, double> updated;  // target tensor -> new value
+
+  double eval(const NodeRef &n) {
+    auto it = memo.find(n.get());
+    if (it != memo.end()) return it->second;
+    double r = 0;
+    switch (n->kind) {
+      case NodeKind::Const: r = n->value; break;
+      case NodeKind::Variable:
+      case NodeKind::Tensor:
+      case NodeKind::Norm: r = leaf.at(n.get()); break;
+      case NodeKind::Binary: {
+        const double a = eval(n->in[0]), b = eval(n->in[1]);
+        r = n->op == '+' ? a + b : n->op == '-' ? a - b : n->op == '*' ? a * b : a / b;
+        break;
+      }
+      case NodeKind::Sqrt: r = std::sqrt(eval(n->in[0])); break;
+      case NodeKind::Cast:
+      case NodeKind::Scatter:
+      case NodeKind::AllReduce:
+      case NodeKind::ReduceScatter:
+      case NodeKind::AllGather:
+      case NodeKind::Broadcast: r = eval(n->in[0]); break;
+      case NodeKind::Update:
+        r = eval(n->in[1]);
+        updated[n->in[0].get()] = r;
+        break;
+    }
+    memo[n.get()] = r;
+    return r;
+  }
+};
+
+bool close(double a, double b) {
+  return std::fabs(a - b) <= 1e-9 * std::max(1.0, std::max(std::fabs(a), std::fabs(b)));
+}
+
+}  // namespace
+
+FusedUpdate Pipeline::classify(const std::vector<NodeRef> &group) const {
+  FusedUpdate fu;
+  std::vector<NodeRef> nodes;
+  for (const NodeRef &s : group) ownedNodes(s, true, &nodes);
+
+  std::vector<NodeRef> updates, norms;
+  NodeRef reduce;
+  for (const NodeRef &n : nodes) {
+    if (n->kind == NodeKind::ReduceScatter || n->kind == NodeKind::AllReduce) {
+      if (reduce && reduce != n) return fu;  // one gradient reduction per fused group
+      reduce = n;
+    }
+    if (n->kind == NodeKind::Update) updates.push_back(n);
+    if (n->kind == NodeKind::Norm) norms.push_back(n);
+  }
+  if (!reduce || reduce->red != Summation || reduce->in[0]->kind != NodeKind::Tensor) return fu;
+  fu.grad = reduce->in[0];
+  std::vector<NodeRef> state;
+  NodeRef wupd;
+  for (const NodeRef &u : updates) {
+    if (u->in[0]->layout == Replicated) {
+      if (wupd) return fu;
+      wupd = u;
+    } else {
+      state.push_back(u);
+    }
+  }
+  if (!wupd) return fu;
+  fu.weight = wupd->in[0];
+
+  std::vector<NodeRef> fvars;  // float Variables of the program
+  for (const NodeRef &a : args_)
+    if (a->kind == NodeKind::Variable && (a->type == Float32 || a->type == Float16 || a->type == Float64))
+      fvars.push_back(a);
+
+  // sample environments
+  std::mt19937 rng(12345);
+  std::uniform_real_distribution<double> U(0.3, 0.9);
+  const int kSamples = 3;
+  std::vector<Probe> probes(kSamples);
+  for (Probe &p : probes) {
+    for (const NodeRef &a : args_) p.leaf[a.get()] = U(rng);
+    for (const NodeRef &n : norms) p.leaf[n.get()] = U(rng) + 1.0;
+    for (const NodeRef &n : nodes)
+      if (n->kind == NodeKind::Variable && !p.leaf.count(n.get())) p.leaf[n.get()] = 8.0;  // sizes
+    for (const NodeRef &s : group) p.eval(s);
+  }
+  auto val = [&](const Probe &p, const NodeRef &n) { return p.leaf.at(n.get()); };
+  auto opt = [&](const Probe &p, const NodeRef &n) { return n ? p.leaf.at(n.get()) : 1.0; };
+  std::vector<NodeRef> with_absent = fvars;
+  with_absent.push_back(nullptr);
+
+  if (state.empty() && norms.empty()) {  // SGD: w' = w - lr * g
+    for (const NodeRef &lr : with_absent) {
+      bool ok = true;
+      for (const Probe &p : probes)
+        ok = ok && close(p.updated.at(fu.weight.get()),
+                         val(p, fu.weight) - opt(p, lr) * val(p, fu.grad));
+      if (ok) {
+        fu.rule = FusedUpdate::SGD;
+        fu.lr = lr ? lr->name : "";
+        return fu;
+      }
+    }
+    return fu;
+  }
+  if (state.size() != 2) return fu;
+
+  for (int perm = 0; perm < 2; ++perm) {
+    const NodeRef m = state[perm]->in[0], v = state[1 - perm]->in[0];
+    for (const NodeRef &b1 : fvars)
+      for (const NodeRef &b2 : fvars) {
+        bool moments_ok = true;
+        for (const Probe &p : probes) {
+          const double g = val(p, fu.grad);
+          moments_ok = moments_ok &&
+                       close(p.updated.at(m.get()), val(p, b1) * val(p, m) + (1 - val(p, b1)) * g) &&
+                       close(p.updated.at(v.get()), val(p, b2) * val(p, v) + (1 - val(p, b2)) * g * g);
+        }
+        if (!moments_ok) continue;
+        if (norms.empty()) {  // Adam as the DSL writes it: w - lr * (m'/b1) / (v'/b2)
+          for (const NodeRef &lr : with_absent) {
+            bool ok = true;
+            for (const Probe &p : probes) {
+              const double mh = p.updated.at(m.get()) / val(p, b1);
+              const double vh = p.updated.at(v.get()) / val(p, b2);
+              ok = ok && close(p.updated.at(fu.weight.get()), val(p, fu.weight) - opt(p, lr) * mh / vh);
+            }
+            if (ok) {
+              fu.rule = FusedUpdate::Adam;
+              fu.m = m, fu.v = v;
+              fu.beta1 = b1->name, fu.beta2 = b2->name, fu.lr = lr ? lr->name : "";
+              return fu;
+            }
+          }
+        } else if (norms.size() == 2) {  // LAMB: r = m^/sqrt(v^) + decay*w; w - lr*(|w|/|r|)*r
+          for (int np = 0; np < 2; ++np) {
+            const NodeRef nw = norms[np], nr = norms[1 - np];
+            for (const NodeRef &lr : with_absent)
+              for (const NodeRef &wd : with_absent) {
+                bool ok = true;
+                for (Probe &p : probes) {
+                  const double mh = p.updated.at(m.get()) / (1 - val(p, b1));
+                  const double vh = p.updated.at(v.get()) / (1 - val(p, b2));
+                  const double r = mh / std::sqrt(vh) + opt(p, wd) * val(p, fu.weight);
+                  ok = ok && close(p.eval(nr->in[0]), r) && close(p.eval(nw->in[0]), val(p, fu.weight)) &&
+                       close(p.updated.at(fu.weight.get()),
+                             val(p, fu.weight) - opt(p, lr) * (val(p, nw) / val(p, nr)) * r);
+                }
+                if (ok) {
+                  fu.rule = FusedUpdate::LAMB;
+                  fu.m = m, fu.v = v;
+                  fu.beta1 = b1->name, fu.beta2 = b2->name;
+                  fu.lr = lr ? lr->name : "", fu.decay = wd ? wd->name : "";
+                  return fu;
+                }
+              }
+          }
+        }
+      }
+  }
+  return fu;
+}
+
+void Pipeline::print(std::ostream &os) const {
+  os << "pipeline " << name_ << " {\n";
+  for (const auto &g : groups()) {
+    os << "  group:";
+    for (const NodeRef &s : g) os << " " << s->name;
+    os << "\n";
+  }
+  os << "}\n";
+}
+
+void Pipeline::codegen(const std::string &filename) {
+  std::ofstream f(filename);
+  if (!f) fail("cannot write " + filename);
+  codegen(f);
+}
+
+}  // namespace ACCCDSL

@@ -149,6 +149,9 @@ int cocoGroupEnd(void);
  * between processes; peer access inside one process), the counterpart of the
  * reference's P2P transport set-up (nccl/src/transport/p2p.cc:118-238). */
 int cocoRegister(cocoComm_t comm, void *ptr, size_t bytes);
+/* Collective (for buffers registered by cocoRegister or on first use): every
+ * rank unmaps its peers' buffers and waits for the others, so that the buffer
+ * may be freed afterwards.  `ptr` is the pointer that was registered. */
 int cocoDeregister(cocoComm_t comm, void *ptr);
 
 /* Local (not collective).  Registers a buffer whose peer mappings the caller

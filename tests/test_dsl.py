@@ -1,0 +1,129 @@
+"""CPU tests of the DSL front end and the emitter: the library builds, the
+reference's own example programs compile against it unchanged (when the
+reference tree is present), every schedule emits, fused groups are recognised
+from what they compute, fusion validity, and emitted programs compile with
+nvcc for sm_100a."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DSL = os.path.join(ROOT, "coconet_b200", "dsl")
+REF = os.environ.get("COCONET_REFERENCE", "/root/reference")
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+
+
+@pytest.fixture(scope="module")
+def dsl_build():
+    subprocess.check_call(["make", "-C", DSL, "-s"])
+    return os.path.join(DSL, "build")
+
+
+def _gen(build, opt, schedule, tmp_path):
+    out = str(tmp_path / f"{opt}-{schedule}.cu")
+    subprocess.check_call([os.path.join(build, "optimizers"), opt, schedule, out])
+    return open(out).read()
+
+
+@pytest.mark.parametrize("opt,call", [
+    ("sgd", "cocoFusedSGD(comm, g, cocoFloat32, w, NULL, cocoFloat16, N, lr, 1.0f, stream)"),
+    ("adam", "cocoFusedAdam(comm, g, cocoFloat32, w, NULL, cocoFloat16, m, v, N, lr, beta1, beta2, "
+             "0.0f, iter, 1.0f, cocoVariantDsl, stream)"),
+    ("lamb", "cocoFusedLAMB(comm, g, cocoFloat32, w, NULL, cocoFloat16, m, v, N, lr, beta1, beta2, "
+             "0.0f, decay, iter, 1.0f, cocoVariantDsl, 0, stream)"),
+])
+def test_fused_schedule_emits_one_runtime_call(dsl_build, tmp_path, opt, call):
+    text = _gen(dsl_build, opt, "fuse_RS_C_AG", tmp_path)
+    assert call in text
+    assert "nccl" not in text and "mpi" not in text.lower()
+    assert "__global__" not in text            # no separate kernel: everything is in the fused step
+    assert "FusedAllReduce: %f, Total: %f}" in text   # the reference's report line
+    assert "cocoCommInitRank(&comm, comm_size, rank, NULL)" in text
+
+
+@pytest.mark.parametrize("opt", ["sgd", "adam", "lamb"])
+@pytest.mark.parametrize("schedule", ["AR_C", "RS_C_AG"])
+def test_unfused_schedules_emit_stock_collectives_and_kernels(dsl_build, tmp_path, opt, schedule):
+    text = _gen(dsl_build, opt, schedule, tmp_path)
+    assert "cocoFused" not in text
+    assert "__global__ void binOpFunc0" in text
+    if schedule == "AR_C":
+        assert "ncclAllReduce(g, g, N, ncclFloat32, ncclSum, nccl, stream)" in text
+    else:
+        assert "ncclReduceScatter(g, g + (size_t)DIVUP(N, comm_size) * rank" in text
+        assert "ncclAllGather(" in text
+        assert "m[i0]" in text or opt == "sgd"     # Sliced state is indexed from the slice start
+    if opt == "lamb":
+        assert text.count("coconetSumSquares<<<") == 2
+
+
+def test_dsl_cases(dsl_build, tmp_path):
+    exe = str(tmp_path / "dsl_cases")
+    subprocess.check_call(["g++", "-std=c++17", "-I", os.path.join(DSL, "include"),
+                           os.path.join(ROOT, "tests", "dsl_cases.cpp"),
+                           os.path.join(dsl_build, "libcoconet_dsl.a"), "-o", exe])
+    out = dict(line.split(": ", 1) for line in subprocess.check_output([exe], text=True).splitlines())
+    assert out["base"] == "1" and out["three"] == "1"
+    assert out["unused"] == "0"
+    assert out["cycle"] == "0" and out["cycle_reason"] == "1" and out["cycle_all"] == "1"
+    assert int(out["groups_after"]) == int(out["groups_before"]) - 1
+    assert out["sgd_commuted"] == "SGD lr=''"
+    assert out["adam_permuted"] == "Adam m=first v=second b1=b1 b2=b2 lr=lr"
+    assert out["momentum"] == "Unknown"
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "examples", "adam")),
+                    reason="reference tree not present")
+@pytest.mark.parametrize("ex", ["sgd", "adam", "lamb"])
+def test_reference_example_programs_are_a_drop_in(dsl_build, tmp_path, ex):
+    # the reference's own DSL programs, compiled unchanged from where they lie
+    exe = str(tmp_path / ex)
+    subprocess.check_call(["g++", "-std=c++17", "-w", "-I", os.path.join(DSL, "include"),
+                           os.path.join(REF, "examples", ex, f"{ex}.cpp"),
+                           os.path.join(dsl_build, "libcoconet_dsl.a"), "-o", exe])
+    for schedule, suffix in [("AR_C", "ar-c"), ("RS_C_AG", "rs-c-ag"), ("fuse_RS_C_AG", "fuse-rs-c-ag")]:
+        subprocess.check_call([exe, schedule], cwd=tmp_path)
+        text = open(tmp_path / f"{ex}-{suffix}.cu").read()
+        assert ("cocoFused" in text) == (schedule == "fuse_RS_C_AG")
+    fused = open(tmp_path / f"{ex}-fuse-rs-c-ag.cu").read()
+    want = {"sgd": "cocoFusedSGD(comm, g, cocoFloat32, w, NULL, cocoFloat16, N, lr, 1.0f, stream)",
+            # adam.cpp:70 has no learning rate; lamb.cpp names its decay variable "gamma"
+            "adam": "m, v, N, 1.0f, beta1, beta2, 0.0f, iter, 1.0f, cocoVariantDsl, stream)",
+            "lamb": "m, v, N, lr, beta1, beta2, 0.0f, gamma, iter, 1.0f, cocoVariantDsl, 0, stream)"}[ex]
+    assert want in fused
+    out = subprocess.run([exe, "fuse(RS_C_AG)"], cwd=tmp_path, capture_output=True, text=True)
+    assert "Invalid schedule" in out.stdout     # as the reference (examples/sgd/sgd.cpp:67)
+
+
+@pytest.mark.parametrize("opt,schedule", [("adam", "fuse_RS_C_AG"), ("lamb", "fuse_RS_C_AG"),
+                                          ("lamb", "RS_C_AG"), ("sgd", "AR_C")])
+def test_emitted_programs_compile_for_sm100a(dsl_build, tmp_path, opt, schedule):
+    _gen(dsl_build, opt, schedule, tmp_path)
+    src = str(tmp_path / f"{opt}-{schedule}.cu")
+    subprocess.check_call([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                           os.path.join(DSL, "rt"), "-I", os.path.join(ROOT, "include"), "-c", src,
+                           "-o", str(tmp_path / "x.o")])
+
+
+def test_unrecognised_fused_group_is_an_error(dsl_build, tmp_path):
+    prog = tmp_path / "bad.cpp"
+    prog.write_text('''
+#include <dsl.hpp>
+#include <pipeline.hpp>
+using namespace ACCCDSL;
+int main() {
+  Variable N(Int32, "N"); Variable lr(Float32, "lr");
+  Tensor g(Float32, N, Local, "g"); Tensor w(Float32, N, Replicated, "w");
+  Stage gs = ReduceScatter(Summation, g);
+  Stage ws = Scatter(w) * gs;              // not an optimizer step
+  Stage wn = Update(w, AllGather(ws));
+  Pipeline p("odd", {g, w, lr}, {wn});
+  p.fuse({gs, ws, wn});
+  p.codegen("odd.cu");
+}''')
+    exe = str(tmp_path / "bad")
+    subprocess.check_call(["g++", "-std=c++17", "-I", os.path.join(DSL, "include"), str(prog),
+                           os.path.join(dsl_build, "libcoconet_dsl.a"), "-o", exe])
+    r = subprocess.run([exe], cwd=tmp_path, capture_output=True, text=True)
+    assert r.returncode == 2 and "is not a ReduceScatter -> SGD | Adam | LAMB" in r.stderr

@@ -58,3 +58,25 @@ def test_nvls_multicast_path():
     r = _launch("nvls", world)
     assert r.returncode == 0, _why(r)
     assert "ok nvls_lamb_fp32" in r.stdout or "skip nvls" in r.stdout, r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+@pytest.mark.parametrize("opt,schedule", [("adam", "fuse_RS_C_AG"), ("lamb", "fuse_RS_C_AG"),
+                                          ("sgd", "RS_C_AG")])
+def test_emitted_program_multi_rank(tmp_path, opt, schedule):
+    """A DSL-emitted C++ program, one process per GPU, started without MPI."""
+    import dsl_build_util as B
+    exe = B.build_program(opt, schedule, str(tmp_path))
+    world = min(_ngpu(), 8)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **B.SCALARS)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--no-python", "--nnodes=1",
+           f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(port),
+           exe, "3", "12", "20", "check"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert r.stdout.count("PASSED") == 8 * world and "FAILED" not in r.stdout
+    assert "{SZ: 524288, Epochs: 3" in r.stdout
