@@ -142,6 +142,148 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_sweep(args, rank, world, local_rank):
+    """Message-size sweep (BASELINE config 4) plus the named configs: fused SGD,
+    fp32 Adam, mixed-precision Adam and fp32 LAMB at N = 4^k elements, each next
+    to stock NCCL all-reduce + the update kernel over all elements.  L2 is
+    flushed (a 256 MB memset) between timed iterations; every iteration is
+    timed with its own CUDA event pair."""
+    import torch
+    import torch.distributed as dist
+    import coconet_b200 as coco
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        comm = coco.Communicator.from_torch_distributed()
+    else:
+        comm = coco.Communicator.init_all(1, [local_rank])[0]
+    local = coco.Communicator.init_all(1, [local_rank])[0]
+    R = world
+    use_nvls = world > 1 and (args.algo == "nvls" or (args.algo == "auto" and world >= 4))
+    max_n = max(1 << args.sweep_max_log, COUNT)
+    keep = []
+
+    def comm_buffer(numel, dtype):
+        if not use_nvls:
+            t = torch.empty(numel, dtype=dtype, device=dev)
+            comm.register(t)
+            return t
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(numel, dtype=dtype, device=dev)
+        h = symm_mem.rendezvous(t, dist.group.WORLD)
+        comm.register_mapped(t, [int(p) for p in h.buffer_ptrs], int(h.multicast_ptr))
+        keep.append(h)
+        return t
+
+    # one set of maximum-size buffers; smaller points use leading views of them
+    g32 = comm_buffer(max_n, torch.float32)
+    g16 = comm_buffer(max_n, torch.float16)
+    w32 = comm_buffer(max_n, torch.float32)
+    w16 = comm_buffer(max_n, torch.float16)
+    g32.normal_(0, 1e-3)
+    g16.copy_(g32 * LOSS_SCALE)
+    w32.normal_(0, 0.02)
+    Smax = (max_n + R - 1) // R
+    m = torch.zeros(Smax, device=dev)
+    v = torch.zeros(Smax, device=dev)
+    mf = torch.zeros(max_n, device=dev)     # un-sharded state of the baseline
+    vf = torch.zeros(max_n, device=dev)
+    gb32 = torch.empty(max_n, dtype=torch.float32, device=dev)
+    gb16 = torch.empty(max_n, dtype=torch.float16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    if use_nvls:
+        comm.set_algo("nvls")
+
+    def time_ms(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        total = 0.0
+        for i in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if world > 1:
+                dist.barrier()
+            e0.record()
+            fn(warmup + i)
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        t = torch.tensor([total / steps], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    hbm_peak, _ = measured_peaks()
+    points = [("sgd", "f32", 4 ** k) for k in range(5, args.sweep_max_log // 2 + 1)]
+    points += [("adam", "f32", 4 ** k) for k in range(5, args.sweep_max_log // 2 + 1)]
+    points += [("adam", "f16", 4 ** k) for k in range(5, args.sweep_max_log // 2 + 1)]
+    points += [("adam", "f16", COUNT), ("lamb", "f32", COUNT), ("lamb", "f32", 1 << 26)]
+    out = []
+    for opt, gt, n in points:
+        if n > max_n:
+            continue
+        g = (g16 if gt == "f16" else g32)[:n]
+        gb = (gb16 if gt == "f16" else gb32)[:n]
+        w = w32[:n]
+        lp = w16[:n] if gt == "f16" else None
+        gs = 1.0 / LOSS_SCALE if gt == "f16" else 1.0
+        S = (n + R - 1) // R
+        h = HYPER
+
+        def fused(i, c=comm, mm=m[:S], vv=v[:S], gg=g):
+            if opt == "sgd":
+                c.fused_sgd(gg, w, 1e-3, w_lp=lp, grad_scale=gs)
+            elif opt == "adam":
+                c.fused_adam(gg, w, mm, vv, h["lr"], h["beta1"], h["beta2"], h["eps"], i, w_lp=lp,
+                             grad_scale=gs)
+            else:
+                c.fused_lamb(gg, w, mm, vv, h["lr"], h["beta1"], h["beta2"], h["eps"], 0.01, i,
+                             w_lp=lp, grad_scale=gs)
+
+        def stock(i):
+            gb.copy_(g)
+            if world > 1:
+                dist.all_reduce(gb)
+            fused(i, c=local, mm=mf[:n], vv=vf[:n], gg=gb)
+
+        def stock_copy_only(i):
+            gb.copy_(g)
+
+        steps = 5 if n >= (1 << 26) else 10
+        ms = time_ms(fused, steps, 3)
+        base = time_ms(stock, steps, 3) - time_ms(stock_copy_only, steps, 3)
+        s_g = 2 if gt == "f16" else 4
+        s_o = 2 if gt == "f16" else 4
+        state = {"sgd": 8, "adam": 24, "lamb": 36}[opt] + (s_o if gt == "f16" else 0)
+        b_bus = (R - 1) * S * (s_g + s_o)
+        b_hbm = n * s_g + S * state + (R - 1) * S * s_o
+        t_roof = max(b_bus / (NVLINK_PEER_GBS * 1e9), b_hbm / (hbm_peak * 1e9))
+        out.append({"opt": opt, "grad": gt, "count": n, "world": R,
+                    "algo": "nvls" if use_nvls else "p2p", "ms": ms, "bus_gbs": b_bus / ms / 1e6,
+                    "hbm_gbs": b_hbm / ms / 1e6, "roof_frac": t_roof / (ms * 1e-3),
+                    "stock_nccl_plus_update_ms": base, "speedup": base / ms})
+        if rank == 0:
+            p = out[-1]
+            print(f"# {opt:5s} {gt} n={n:>11d} fused {ms:9.4f} ms  bus {p['bus_gbs']:7.1f} GB/s  "
+                  f"hbm {p['hbm_gbs']:7.1f} GB/s  roof {p['roof_frac']:.3f}  stock {base:9.4f} ms  "
+                  f"x{p['speedup']:.2f}", flush=True)
+    st = comm.status()
+    if rank == 0:
+        line = {"sweep": out, "n_gpus": R, "status": st["code"],
+                "timing": "CUDA events per iteration, L2 flushed between iterations, max over ranks"}
+        print(json.dumps(line), flush=True)
+    local.destroy()
+    comm.destroy()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -152,6 +294,8 @@ def main():
     ap.add_argument("--no-baseline", action="store_true", help="skip the stock NCCL comparison (N > 1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="message-size sweep instead of the headline workload")
+    ap.add_argument("--sweep-max-log", type=int, default=30)
     ap.add_argument("--algo", default=os.environ.get("COCO_BENCH_ALGO", "auto"),
                     choices=["auto", "p2p", "nvls"],
                     help="nvls: gradients and fp16 weights in symmetric memory with an NVSwitch "
@@ -168,6 +312,10 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, max(world, args.gpus))
+        return
+
+    if args.sweep:
+        run_sweep(args, rank, world, local_rank)
         return
 
     import torch

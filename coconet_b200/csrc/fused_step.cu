@@ -195,6 +195,17 @@ template <typename GT> struct RawUnit<GT, 4> {
   }
   __device__ __forceinline__ float get(int k) const { return Bits16<GT>::to_f32(bits(k)); }
 };
+template <typename GT> struct RawUnit<GT, 8> {
+  uint4 q;
+  __device__ __forceinline__ void load(const void *base, size_t i) {
+    q = ld_sys_16((const unsigned short *)base + i);
+  }
+  __device__ __forceinline__ unsigned short bits(int k) const {
+    const unsigned wd = (k >> 1) == 0 ? q.x : (k >> 1) == 1 ? q.y : (k >> 1) == 2 ? q.z : q.w;
+    return (unsigned short)((k & 1) ? (wd >> 16) : (wd & 0xffffu));
+  }
+  __device__ __forceinline__ float get(int k) const { return Bits16<GT>::to_f32(bits(k)); }
+};
 template <typename GT> struct RawUnit<GT, 1> {
   unsigned short q;
   __device__ __forceinline__ void load(const void *base, size_t i) {
@@ -699,22 +710,35 @@ __device__ __forceinline__ void nvls_phase(const RankArgs &ra, const StepArgs &s
 
 // Grid-stride loops of the direct (register-staged) path over `nunits`
 // 4-element units starting at element `first`.
+// 16-bit gradients read from one or two ranks use 8-element units (16-byte
+// loads and stores); with more ranks in flight the registers only allow 4.
+template <typename GT, int RB> struct DirectVec {
+  static constexpr int kVec = (GradTraits<GT>::kIs16 && RB <= 2) ? 8 : 4;
+};
+
 template <int OPT, typename GT, typename LPT, int RB>
 __device__ __forceinline__ void direct_step(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
-                                            size_t lo, size_t first, size_t nunits, size_t tid,
+                                            size_t lo, size_t first, size_t nelems, size_t tid,
                                             size_t nth, double &sum_w2, double &sum_r2) {
-  constexpr int VEC = GradTraits<GT>::kVec;
+  constexpr int VEC = DirectVec<GT, RB>::kVec;
+  const size_t nunits = nelems / VEC;
   for (size_t u = tid; u < nunits; u += nth)
     step_unit<OPT, GT, LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, sum_w2, sum_r2);
+  // up to one 4-element unit may remain (nelems is a multiple of 4)
+  if (VEC == 8 && (nelems & 4) && tid == 0)
+    step_unit<OPT, GT, LPT, 4, RB>(ra, sa, h, lo, first + nunits * VEC, sum_w2, sum_r2);
 }
 template <typename GT, typename LPT, int RB>
 __device__ __forceinline__ void direct_apply(const RankArgs &ra, const StepArgs &sa,
                                              const Hyper &h, size_t lo, size_t first,
-                                             size_t nunits, size_t tid, size_t nth,
+                                             size_t nelems, size_t tid, size_t nth,
                                              float lr_scale) {
-  constexpr int VEC = GradTraits<GT>::kVec;
+  constexpr int VEC = DirectVec<GT, RB>::kVec;
+  const size_t nunits = nelems / VEC;
   for (size_t u = tid; u < nunits; u += nth)
     lamb_apply_unit<LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, lr_scale);
+  if (VEC == 8 && (nelems & 4) && tid == 0)
+    lamb_apply_unit<LPT, 4, RB>(ra, sa, h, lo, first + nunits * VEC, lr_scale);
 }
 
 __device__ __forceinline__ double warp_sum(double x) {
@@ -1063,13 +1087,13 @@ __global__ void __launch_bounds__(512, 2)
     if (nvls) {
       // nothing left for the vector loops; the scalar loop below takes the tail
     } else if (R == 1)
-      direct_step<OPT, GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
+      direct_step<OPT, GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     else if (R == 2)
-      direct_step<OPT, GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
+      direct_step<OPT, GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     else if (R <= 4)
-      direct_step<OPT, GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
+      direct_step<OPT, GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     else
-      direct_step<OPT, GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest, tid, nth, sum_w2, sum_r2);
+      direct_step<OPT, GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     const size_t done_elems = nvls ? nvls_units * NV : piped + nvec_rest * VEC;
     for (size_t j = done_elems + tid; j < L; j += nth)
       step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, lo, lo + j, sum_w2, sum_r2);
@@ -1151,13 +1175,13 @@ __global__ void __launch_bounds__(512, 2)
         const size_t first = lo + piped;
         if (nvls) {
         } else if (R == 1)
-          direct_apply<GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
+          direct_apply<GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
         else if (R == 2)
-          direct_apply<GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
+          direct_apply<GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
         else if (R <= 4)
-          direct_apply<GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
+          direct_apply<GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
         else
-          direct_apply<GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest, tid, nth, lr_scale);
+          direct_apply<GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
         const size_t done_elems = nvls ? nvls_units * NV : piped + nvec_rest * VEC;
         for (size_t j = done_elems + tid; j < L; j += nth)
           lamb_apply_unit<LPT, 1, 0>(ra, sa, h, lo, lo + j, lr_scale);
