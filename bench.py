@@ -196,6 +196,26 @@ def run_sweep(args, rank, world, local_rank):
     if use_nvls:
         comm.set_algo("nvls")
 
+    def time_back_to_back(fn, steps, warmup):
+        """Steps enqueued one after the other as a training loop would (no L2
+        flush, one event pair around all of them): the latency a small
+        message sees once the ranks run in step."""
+        for i in range(warmup):
+            fn(i)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     def time_ms(fn, steps, warmup):
         for i in range(warmup):
             fn(i)
@@ -263,7 +283,8 @@ def run_sweep(args, rank, world, local_rank):
         b_bus = (R - 1) * S * (s_g + s_o)
         b_hbm = n * s_g + S * state + (R - 1) * S * s_o
         t_roof = max(b_bus / (NVLINK_PEER_GBS * 1e9), b_hbm / (hbm_peak * 1e9))
-        out.append({"opt": opt, "grad": gt, "count": n, "world": R,
+        b2b = time_back_to_back(fused, 50, 5) if n <= (1 << 22) else None
+        out.append({"opt": opt, "grad": gt, "count": n, "world": R, "ms_back_to_back": b2b,
                     "algo": "nvls" if use_nvls else "p2p", "ms": ms, "bus_gbs": b_bus / ms / 1e6,
                     "hbm_gbs": b_hbm / ms / 1e6, "roof_frac": t_roof / (ms * 1e-3),
                     "stock_nccl_plus_update_ms": base, "speedup": base / ms})
@@ -271,7 +292,7 @@ def run_sweep(args, rank, world, local_rank):
             p = out[-1]
             print(f"# {opt:5s} {gt} n={n:>11d} fused {ms:9.4f} ms  bus {p['bus_gbs']:7.1f} GB/s  "
                   f"hbm {p['hbm_gbs']:7.1f} GB/s  roof {p['roof_frac']:.3f}  stock {base:9.4f} ms  "
-                  f"x{p['speedup']:.2f}", flush=True)
+                  f"x{p['speedup']:.2f}" + (f"  back-to-back {b2b * 1e3:7.1f} us" if b2b else ""), flush=True)
     st = comm.status()
     if rank == 0:
         line = {"sweep": out, "n_gpus": R, "status": st["code"],

@@ -21,16 +21,30 @@ def _stale():
 
 
 def build_library(force=False, verbose=False):
-    """Compile for sm_100a only; returns the path of the shared library."""
+    """Compile for sm_100a only; returns the path of the shared library.  The
+    kernel file is compiled as four parts in parallel (see COCO_PART in
+    fused_step.cu)."""
     if not force and not _stale():
         return LIB
-    cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-shared", "-cudart", "shared", "-Xcompiler", "-fPIC",
-           "-I" + os.path.join(ROOT, "include"), "-I" + CSRC, "-o", LIB]
+    from concurrent.futures import ThreadPoolExecutor
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    base = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+            "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES]
-    subprocess.check_call(cmd)
+        base += ["-Xptxas", "-v"]
+    jobs = []
+    for part in range(4):
+        obj = os.path.join(objdir, f"fused_step_{part}.o")
+        jobs.append((base + [f"-DCOCO_PART={part}", "-c", os.path.join(CSRC, "fused_step.cu"), "-o", obj], obj))
+    for src in SOURCES:
+        if src == "fused_step.cu":
+            continue
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
+        jobs.append((base + ["-c", os.path.join(CSRC, src), "-o", obj], obj))
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
+        list(pool.map(lambda j: subprocess.check_call(j[0]), jobs))
+    subprocess.check_call([NVCC, "-shared", "-cudart", "shared", "-o", LIB] + [j[1] for j in jobs])
     return LIB
 
 

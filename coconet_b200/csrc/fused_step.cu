@@ -32,6 +32,9 @@
 #include <type_traits>
 
 namespace coco {
+
+typedef void (*KernelPtr)(const StepArgs, const RankArgs, const RankArgs *);
+
 namespace {
 
 // ---------------------------------------------------------------------------
@@ -102,7 +105,7 @@ __device__ __forceinline__ double ld_volatile_f64(const double *p) {
 // ---------------------------------------------------------------------------
 constexpr unsigned kSpinHardCap = 1u << 28;  // backstop if the timer misbehaves
 
-__device__ void record_status(FlagPage *me, int code, int rank, int phase, int peer,
+__device__ __noinline__ void record_status(FlagPage *me, int code, int rank, int phase, int peer,
                               unsigned long long seq) {
   if (atomicCAS(&me->status[0], 0, code) == 0) {
     me->status[1] = rank;
@@ -115,7 +118,7 @@ __device__ void record_status(FlagPage *me, int code, int rank, int phase, int p
 
 // Waits until flags[p] >= seq for every p in [0, world) except `skip`.
 // Returns -1 on success, else the first peer that did not show up in time.
-__device__ int wait_all(const unsigned long long *flags, int world, int skip,
+__device__ __noinline__ int wait_all(const unsigned long long *flags, int world, int skip,
                         unsigned long long seq, unsigned long long timeout_ns) {
   const unsigned long long t0 = globaltimer_ns();
   for (int p = 0; p < world; ++p) {
@@ -130,6 +133,43 @@ __device__ int wait_all(const unsigned long long *flags, int world, int skip,
     }
   }
   return -1;
+}
+
+// One flag.  Returns false if it did not reach seq in time.
+__device__ __noinline__ bool wait_one(const unsigned long long *flag, unsigned long long seq,
+                         unsigned long long timeout_ns) {
+  if (ld_acquire_sys(flag) >= seq) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (unsigned spins = 1; spins <= kSpinHardCap; ++spins) {
+    if (ld_acquire_sys(flag) >= seq) return true;
+    if ((spins & 63u) == 0u) {
+      if (globaltimer_ns() - t0 > timeout_ns) return false;
+      __nanosleep(32);
+    }
+  }
+  return false;
+}
+
+// Flags are exchanged by the first warp of a CTA, lane p talking to rank p, so
+// that the R-1 remote stores (each a release: fence + store) and the R-1 polls
+// proceed in parallel instead of one after the other.
+// signal: store seq into slot `rank` of flags_of(p) for every peer p.
+// wait:   until own slot p >= seq for every peer p; returns the first late peer or -1.
+// Must be called by all 32 lanes of warp 0.
+template <typename SlotOf>
+__device__ __forceinline__ void warp_signal_peers(const RankArgs &ra, int R, int rank,
+                                                  unsigned long long seq, SlotOf slot_of) {
+  const int p = threadIdx.x & 31;
+  if (p < R && p != rank) st_release_sys(slot_of(ra.flags[p]) + rank, seq);
+}
+__device__ __forceinline__ int warp_wait_peers(const unsigned long long *slots, int R, int rank,
+                                               unsigned long long seq,
+                                               unsigned long long timeout_ns) {
+  const int p = threadIdx.x & 31;
+  bool late = false;
+  if (p < R && p != rank) late = !wait_one(slots + p, seq, timeout_ns);
+  const unsigned bad = __ballot_sync(0xffffffffu, late);
+  return bad ? __ffs(bad) - 1 : -1;
 }
 
 // ---------------------------------------------------------------------------
@@ -710,10 +750,11 @@ __device__ __forceinline__ void nvls_phase(const RankArgs &ra, const StepArgs &s
 
 // Grid-stride loops of the direct (register-staged) path over `nunits`
 // 4-element units starting at element `first`.
-// 16-bit gradients read from one or two ranks use 8-element units (16-byte
-// loads and stores); with more ranks in flight the registers only allow 4.
+// 16-bit gradients on a single rank use 8-element units (16-byte loads and
+// stores: +2 % there); with peers in flight the registers only allow 4
+// (8-element units measured 10 % slower at two ranks).
 template <typename GT, int RB> struct DirectVec {
-  static constexpr int kVec = (GradTraits<GT>::kIs16 && RB <= 2) ? 8 : 4;
+  static constexpr int kVec = (GradTraits<GT>::kIs16 && RB == 1) ? 8 : 4;
 };
 
 template <int OPT, typename GT, typename LPT, int RB>
@@ -991,7 +1032,15 @@ __device__ __forceinline__ bool run_tiles(const RankArgs &ra, const StepArgs &sa
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <int OPT, typename GT, typename LPT>
+// PATH selects the data path at compile time so that each gets a register
+// allocation of its own (with all three in one kernel the peer-to-peer loop
+// spilled 376 bytes and lost 6 %): kPathDirect = register-staged peer loads
+// and stores for world sizes 2..8, kPathLocal = the same for world size 1
+// (wider units), kPathNvls = NVSwitch multimem, kPathTiles = bulk-copy pipeline.
+// Every path ends with the same scalar loop for what it does not cover.
+enum : int { kPathDirect = 0, kPathNvls = 1, kPathTiles = 2, kPathLocal = 3 };
+
+template <int OPT, typename GT, typename LPT, int PATH>
 __global__ void __launch_bounds__(512, 2)
     fused_step_kernel(const __grid_constant__ StepArgs sa, const __grid_constant__ RankArgs one,
                       const RankArgs *__restrict__ table) {
@@ -1026,13 +1075,11 @@ __global__ void __launch_bounds__(512, 2)
 
   // ---- start barrier ------------------------------------------------------
   if (R > 1) {
-    if (threadIdx.x == 0) {
-      if (blockIdx.x == 0) {
-        for (int p = 0; p < R; ++p)
-          if (p != rank) st_release_sys(&ra.flags[p]->arrive[rank], seq);
-      }
-      const int late = wait_all(me->arrive, R, rank, seq, sa.timeout_ns);
-      if (late >= 0) {
+    if (threadIdx.x < 32) {
+      if (blockIdx.x == 0)
+        warp_signal_peers(ra, R, rank, seq, [](FlagPage *f) { return f->arrive; });
+      const int late = warp_wait_peers(me->arrive, R, rank, seq, sa.timeout_ns);
+      if (late >= 0 && threadIdx.x == 0) {
         record_status(me, cocoTimeout, rank, kPhaseStart, late, seq);
         s_ok = 0;
       }
@@ -1057,7 +1104,7 @@ __global__ void __launch_bounds__(512, 2)
   // done with direct loads.
   TilePlan tp;
   const size_t T = (size_t)kTileElemsPerThread * blockDim.x;
-  tp.stages = ra.pad ? sa.pipe_stages : 0;
+  tp.stages = (PATH == kPathTiles && ra.pad) ? sa.pipe_stages : 0;
   tp.g_bytes = (unsigned)(T * sizeof(GT));
   tp.stage_bytes = (unsigned)(R * tp.g_bytes + (OPT == kSGD ? 1 : 3) * T * 4);
   tp.ntiles = tp.stages > 0 ? L / T : 0;
@@ -1066,8 +1113,8 @@ __global__ void __launch_bounds__(512, 2)
   unsigned iter = 0;
 
   double sum_w2 = 0.0, sum_r2 = 0.0;
-  if (ok) {
-    if (tp.ntiles > 0 &&
+  if constexpr (PATH == kPathTiles) {
+    if (ok && tp.ntiles > 0 &&
         !run_tiles<OPT, GT, LPT, 0>(ra, sa, h, tp, tile_smem, s_full, &s_fail, lo, iter, sum_w2,
                                     sum_r2, 0.f)) {
       if (threadIdx.x == 0) record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
@@ -1077,24 +1124,29 @@ __global__ void __launch_bounds__(512, 2)
   // NVLS: whole 16-byte units of the slice go through the switch; the rest
   // (and everything when unaligned) falls through to the peer-to-peer code.
   constexpr int NV = Multimem<GT>::kN;
-  const bool nvls = (sa.flags & kFlagNvls) && ra.pad && ra.mc_g && ra.mc_out &&
-                    sa.variant != cocoVariantNccl && tp.ntiles == 0;
+  const bool nvls = PATH == kPathNvls && (sa.flags & kFlagNvls) && ra.pad && ra.mc_g &&
+                    ra.mc_out && sa.variant != cocoVariantNccl;
   const size_t nvls_units = nvls ? L / NV : 0;
-  if (ok && nvls)
-    nvls_phase<OPT, GT, LPT, 0>(ra, sa, h, lo, nvls_units, tid, nth, sum_w2, sum_r2, 0.f);
+  if constexpr (PATH == kPathNvls) {
+    if (ok && nvls)
+      nvls_phase<OPT, GT, LPT, 0>(ra, sa, h, lo, nvls_units, tid, nth, sum_w2, sum_r2, 0.f);
+  }
   if (ok) {
     const size_t first = lo + piped;
-    if (nvls) {
-      // nothing left for the vector loops; the scalar loop below takes the tail
-    } else if (R == 1)
+    if constexpr (PATH == kPathLocal) {
       direct_step<OPT, GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
-    else if (R == 2)
+    } else if constexpr (PATH != kPathDirect) {
+      // vector loops of the direct path are not part of this kernel; the
+      // scalar loop below takes what the path left over
+      (void)first;
+    } else if (R == 2)
       direct_step<OPT, GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     else if (R <= 4)
       direct_step<OPT, GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     else
       direct_step<OPT, GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
-    const size_t done_elems = nvls ? nvls_units * NV : piped + nvec_rest * VEC;
+    const size_t done_elems = PATH == kPathNvls ? nvls_units * NV
+                              : PATH == kPathTiles ? piped : piped + nvec_rest * VEC;
     for (size_t j = done_elems + tid; j < L; j += nth)
       step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, lo, lo + j, sum_w2, sum_r2);
   }
@@ -1163,26 +1215,33 @@ __global__ void __launch_bounds__(512, 2)
     ok = s_ok != 0;
     if (ok) {
       const float lr_scale = s_lr_scale;
-      if (tp.ntiles > 0 &&
-          !run_tiles<OPT, GT, LPT, 1>(ra, sa, h, tp, tile_smem, s_full, &s_fail, lo, iter, sum_w2,
-                                      sum_r2, lr_scale)) {
-        if (threadIdx.x == 0) record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
-        ok = false;
+      if constexpr (PATH == kPathTiles) {
+        if (tp.ntiles > 0 &&
+            !run_tiles<OPT, GT, LPT, 1>(ra, sa, h, tp, tile_smem, s_full, &s_fail, lo, iter,
+                                        sum_w2, sum_r2, lr_scale)) {
+          if (threadIdx.x == 0) record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
+          ok = false;
+        }
       }
-      if (ok && nvls)
-        nvls_phase<OPT, GT, LPT, 1>(ra, sa, h, lo, nvls_units, tid, nth, sum_w2, sum_r2, lr_scale);
+      if constexpr (PATH == kPathNvls) {
+        if (ok && nvls)
+          nvls_phase<OPT, GT, LPT, 1>(ra, sa, h, lo, nvls_units, tid, nth, sum_w2, sum_r2,
+                                      lr_scale);
+      }
       if (ok) {
         const size_t first = lo + piped;
-        if (nvls) {
-        } else if (R == 1)
+        if constexpr (PATH == kPathLocal) {
           direct_apply<GT, LPT, 1>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
-        else if (R == 2)
+        } else if constexpr (PATH != kPathDirect) {
+          (void)first;
+        } else if (R == 2)
           direct_apply<GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
         else if (R <= 4)
           direct_apply<GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
         else
           direct_apply<GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
-        const size_t done_elems = nvls ? nvls_units * NV : piped + nvec_rest * VEC;
+        const size_t done_elems = PATH == kPathNvls ? nvls_units * NV
+                                  : PATH == kPathTiles ? piped : piped + nvec_rest * VEC;
         for (size_t j = done_elems + tid; j < L; j += nth)
           lamb_apply_unit<LPT, 1, 0>(ra, sa, h, lo, lo + j, lr_scale);
       }
@@ -1193,17 +1252,23 @@ __global__ void __launch_bounds__(512, 2)
   if (R > 1) {
     __threadfence_system();  // this thread's peer stores before the "done" signal
     __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
-      const unsigned prev = atomicAdd(&me->done_count, 1u);
-      if (prev == gridDim.x - 1) {  // last CTA of the rank
-        me->done_count = 0;
+    if (threadIdx.x < 32) {
+      unsigned prev = 0;
+      if (threadIdx.x == 0) {
         __threadfence_system();
-        for (int p = 0; p < R; ++p)
-          if (p != rank) st_release_sys(&ra.flags[p]->done[rank], seq);
+        prev = atomicAdd(&me->done_count, 1u);
+        if (prev == gridDim.x - 1) me->done_count = 0;
+        __threadfence_system();
+      }
+      __syncwarp();
+      prev = __shfl_sync(0xffffffffu, prev, 0);
+      if (prev == gridDim.x - 1) {  // last CTA of the rank
+        __threadfence_system();
+        warp_signal_peers(ra, R, rank, seq, [](FlagPage *f) { return f->done; });
         if (ok) {
-          const int late = wait_all(me->done, R, rank, seq, sa.timeout_ns);
-          if (late >= 0) record_status(me, cocoTimeout, rank, kPhaseEnd, late, seq);
+          const int late = warp_wait_peers(me->done, R, rank, seq, sa.timeout_ns);
+          if (late >= 0 && threadIdx.x == 0)
+            record_status(me, cocoTimeout, rank, kPhaseEnd, late, seq);
         }
       }
     }
@@ -1213,27 +1278,69 @@ __global__ void __launch_bounds__(512, 2)
 // ---------------------------------------------------------------------------
 // host-side dispatch
 // ---------------------------------------------------------------------------
-typedef void (*KernelPtr)(const StepArgs, const RankArgs, const RankArgs *);
+template <int OPT, typename GT, typename LPT> KernelPtr pick_path(int path) {
+  switch (path) {
+    case kPathNvls: return fused_step_kernel<OPT, GT, LPT, kPathNvls>;
+    case kPathTiles: return fused_step_kernel<OPT, GT, LPT, kPathTiles>;
+    case kPathLocal: return fused_step_kernel<OPT, GT, LPT, kPathLocal>;
+    default: return fused_step_kernel<OPT, GT, LPT, kPathDirect>;
+  }
+}
+template <int OPT, typename GT> KernelPtr pick_lp(bool has_lp, cocoDataType_t lp, int path) {
+  if (!has_lp) return pick_path<OPT, GT, NoLp>(path);
+  if (lp == cocoFloat16) return pick_path<OPT, GT, __half>(path);
+  if (lp == cocoBfloat16) return pick_path<OPT, GT, __nv_bfloat16>(path);
+  return nullptr;
+}
+template <int OPT> KernelPtr pick_g(cocoDataType_t g, bool has_lp, cocoDataType_t lp, int path) {
+  if (g == cocoFloat32) return pick_lp<OPT, float>(has_lp, lp, path);
+  if (g == cocoFloat16) return pick_lp<OPT, __half>(has_lp, lp, path);
+  if (g == cocoBfloat16) return pick_lp<OPT, __nv_bfloat16>(has_lp, lp, path);
+  return nullptr;
+}
+}  // namespace
 
-template <int OPT, typename GT> KernelPtr pick_lp(bool has_lp, cocoDataType_t lp) {
-  if (!has_lp) return fused_step_kernel<OPT, GT, NoLp>;
-  if (lp == cocoFloat16) return fused_step_kernel<OPT, GT, __half>;
-  if (lp == cocoBfloat16) return fused_step_kernel<OPT, GT, __nv_bfloat16>;
-  return nullptr;
+// The kernels are instantiated in three translation units (COCO_PART = 0, 1,
+// 2: SGD, Adam, LAMB) so that they compile in parallel; COCO_PART = 3 holds
+// the dispatch.  Without COCO_PART everything is in one unit.
+#if !defined(COCO_PART) || COCO_PART == 0
+KernelPtr pick_sgd(cocoDataType_t g, bool has_lp, cocoDataType_t lp, int path) {
+  return pick_g<kSGD>(g, has_lp, lp, path);
 }
-template <int OPT> KernelPtr pick_g(cocoDataType_t g, bool has_lp, cocoDataType_t lp) {
-  if (g == cocoFloat32) return pick_lp<OPT, float>(has_lp, lp);
-  if (g == cocoFloat16) return pick_lp<OPT, __half>(has_lp, lp);
-  if (g == cocoBfloat16) return pick_lp<OPT, __nv_bfloat16>(has_lp, lp);
-  return nullptr;
+#endif
+#if !defined(COCO_PART) || COCO_PART == 1
+KernelPtr pick_adam(cocoDataType_t g, bool has_lp, cocoDataType_t lp, int path) {
+  return pick_g<kAdam>(g, has_lp, lp, path);
 }
-KernelPtr pick(int opt, cocoDataType_t g, bool has_lp, cocoDataType_t lp) {
+#endif
+#if !defined(COCO_PART) || COCO_PART == 2
+KernelPtr pick_lamb(cocoDataType_t g, bool has_lp, cocoDataType_t lp, int path) {
+  return pick_g<kLAMB>(g, has_lp, lp, path);
+}
+#endif
+
+#if !defined(COCO_PART) || COCO_PART == 3
+KernelPtr pick_sgd(cocoDataType_t g, bool has_lp, cocoDataType_t lp, int path);
+KernelPtr pick_adam(cocoDataType_t g, bool has_lp, cocoDataType_t lp, int path);
+KernelPtr pick_lamb(cocoDataType_t g, bool has_lp, cocoDataType_t lp, int path);
+
+namespace {
+
+KernelPtr pick(int opt, cocoDataType_t g, bool has_lp, cocoDataType_t lp, int path) {
   switch (opt) {
-    case kSGD: return pick_g<kSGD>(g, has_lp, lp);
-    case kAdam: return pick_g<kAdam>(g, has_lp, lp);
-    case kLAMB: return pick_g<kLAMB>(g, has_lp, lp);
+    case kSGD: return pick_sgd(g, has_lp, lp, path);
+    case kAdam: return pick_adam(g, has_lp, lp, path);
+    case kLAMB: return pick_lamb(g, has_lp, lp, path);
   }
   return nullptr;
+}
+
+// The path a launch takes: NVLS when the call carries multicast addresses,
+// the tile pipeline when it was given stages, else the register-staged path.
+int path_of(const StepArgs &sa) {
+  if (sa.flags & kFlagNvls) return kPathNvls;
+  if (sa.pipe_stages > 0) return kPathTiles;
+  return sa.world == 1 ? kPathLocal : kPathDirect;
 }
 
 }  // namespace
@@ -1241,7 +1348,7 @@ KernelPtr pick(int opt, cocoDataType_t g, bool has_lp, cocoDataType_t lp) {
 cudaError_t launch_fused_step(int opt, cocoDataType_t g_type, bool has_lp, cocoDataType_t lp_type,
                               const StepArgs &sa, const RankArgs &one, const RankArgs *table,
                               const LaunchConfig &cfg, cudaStream_t stream) {
-  KernelPtr k = pick(opt, g_type, has_lp, lp_type);
+  KernelPtr k = pick(opt, g_type, has_lp, lp_type, path_of(sa));
   if (!k) return cudaErrorInvalidValue;
   const dim3 grid(cfg.ctas, cfg.nvirt > 1 ? cfg.nvirt : 1, 1);
   const dim3 block(cfg.threads, 1, 1);
@@ -1260,7 +1367,8 @@ cudaError_t launch_fused_step(int opt, cocoDataType_t g_type, bool has_lp, cocoD
 cudaError_t fused_step_occupancy(int opt, cocoDataType_t g_type, bool has_lp,
                                  cocoDataType_t lp_type, int threads, size_t smem_bytes,
                                  int *ctas_per_sm) {
-  KernelPtr k = pick(opt, g_type, has_lp, lp_type);
+  // all three paths are built under the same launch bounds
+  KernelPtr k = pick(opt, g_type, has_lp, lp_type, smem_bytes > 0 ? kPathTiles : kPathDirect);
   if (!k) return cudaErrorInvalidValue;
   if (smem_bytes > 0) {
     cudaError_t e = cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1270,5 +1378,6 @@ cudaError_t fused_step_occupancy(int opt, cocoDataType_t g_type, bool has_lp,
   return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctas_per_sm, (const void *)k, threads,
                                                        smem_bytes);
 }
+#endif  // dispatch part
 
 }  // namespace coco

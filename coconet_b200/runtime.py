@@ -25,7 +25,8 @@ class _Status(C.Structure):
 
 
 def library_path():
-    return os.path.join(HERE, "libcoconet_rt.so")
+    """The in-tree library; COCO_RT_LIBRARY points at another build (A/B runs)."""
+    return os.environ.get("COCO_RT_LIBRARY") or os.path.join(HERE, "libcoconet_rt.so")
 
 
 _lib = None
@@ -88,6 +89,8 @@ def lib():
                 "(or __graft_entry__.build()); coconet_b200 has no fallback path")
         L = C.CDLL(path)
         for name, (res, args) in _SIGNATURES.items():
+            if os.environ.get("COCO_RT_LIBRARY") and not hasattr(L, name):
+                continue  # an older build under comparison
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args
