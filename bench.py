@@ -170,11 +170,8 @@ def run_sweep(args, rank, world, local_rank):
             t = torch.empty(numel, dtype=dtype, device=dev)
             comm.register(t)
             return t
-        import torch.distributed._symmetric_memory as symm_mem
-        t = symm_mem.empty(numel, dtype=dtype, device=dev)
-        h = symm_mem.rendezvous(t, dist.group.WORLD)
-        comm.register_mapped(t, [int(p) for p in h.buffer_ptrs], int(h.multicast_ptr))
-        keep.append(h)
+        t = comm.mem_alloc(numel, dtype)
+        keep.append(t)
         return t
 
     # one set of maximum-size buffers; smaller points use leading views of them
@@ -298,6 +295,9 @@ def run_sweep(args, rank, world, local_rank):
         line = {"sweep": out, "n_gpus": R, "status": st["code"],
                 "timing": "CUDA events per iteration, L2 flushed between iterations, max over ranks"}
         print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()
+    for t in keep:
+        comm.mem_free(t)
     local.destroy()
     comm.destroy()
     if world > 1:
@@ -315,6 +315,8 @@ def main():
     ap.add_argument("--no-baseline", action="store_true", help="skip the stock NCCL comparison (N > 1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--symm", default="runtime", choices=["runtime", "torch"],
+                    help="who makes the symmetric memory of the NVLS path")
     ap.add_argument("--sweep", action="store_true", help="message-size sweep instead of the headline workload")
     ap.add_argument("--sweep-max-log", type=int, default=30)
     ap.add_argument("--algo", default=os.environ.get("COCO_BENCH_ALGO", "auto"),
@@ -362,11 +364,19 @@ def main():
     use_nvls = world > 1 and (args.algo == "nvls" or (args.algo == "auto" and world >= 4))
     symm = []
 
+    runtime_allocs = []
+
     def comm_buffer(numel):
         """A buffer peers touch: plain device memory (peer-mapped by the runtime
-        over CUDA IPC), or torch symmetric memory with a multicast address."""
+        over CUDA IPC), or symmetric memory with an NVSwitch multicast mapping --
+        made by the runtime (cocoMemAlloc, default) or, with --symm torch, by
+        torch's symmetric memory and handed over with cocoRegisterMapped."""
         if not use_nvls:
             return torch.empty(numel, dtype=torch.float16, device=dev)
+        if args.symm == "runtime":
+            t = comm.mem_alloc(numel, torch.float16)
+            runtime_allocs.append(t)
+            return t
         import torch.distributed._symmetric_memory as symm_mem
         t = symm_mem.empty(numel, dtype=torch.float16, device=dev)
         h = symm_mem.rendezvous(t, dist.group.WORLD)
@@ -393,7 +403,9 @@ def main():
     v = torch.zeros(S, device=dev)
     if use_nvls:
         comm.set_algo("nvls")
-        use_nvls = all(int(h.multicast_ptr) != 0 for h in symm)  # else the runtime uses peer-to-peer
+        # without a multicast mapping the runtime falls back to peer-to-peer
+        use_nvls = (all(comm.has_multicast(t) for t in runtime_allocs) if args.symm == "runtime"
+                    else all(int(h.multicast_ptr) != 0 for h in symm))
     else:
         for t in g:
             comm.register(t)
@@ -519,6 +531,9 @@ def main():
             line["cpu_baseline"] = cpu_baseline(1 << 24, 1)
         print(json.dumps(line), flush=True)
 
+    torch.cuda.synchronize()
+    for t in runtime_allocs:
+        comm.mem_free(t)
     comm.destroy()
     if world > 1:
         dist.barrier()

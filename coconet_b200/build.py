@@ -6,7 +6,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcoconet_rt.so")
-SOURCES = ["fused_step.cu", "runtime.cu", "bootstrap.cpp", "no_alloc.cu"]
+SOURCES = ["fused_step.cu", "runtime.cu", "bootstrap.cpp", "no_alloc.cu", "symm_mem.cu"]
 HEADERS = ["fused_step.cuh", "bootstrap.h", os.path.join(ROOT, "include", "coconet_rt.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
@@ -30,7 +30,7 @@ def build_library(force=False, verbose=False):
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     base = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-            "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
+            "-Xcompiler", "-fPIC", "-diag-suppress", "177", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
     if verbose:
         base += ["-Xptxas", "-v"]
     jobs = []
@@ -44,7 +44,7 @@ def build_library(force=False, verbose=False):
         jobs.append((base + ["-c", os.path.join(CSRC, src), "-o", obj], obj))
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
         list(pool.map(lambda j: subprocess.check_call(j[0]), jobs))
-    subprocess.check_call([NVCC, "-shared", "-cudart", "shared", "-o", LIB] + [j[1] for j in jobs])
+    subprocess.check_call([NVCC, "-shared", "-cudart", "shared", "-Wno-deprecated-gpu-targets", "-o", LIB] + [j[1] for j in jobs])
     return LIB
 
 

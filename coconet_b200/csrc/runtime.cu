@@ -12,6 +12,8 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <cmath>
@@ -145,6 +147,7 @@ struct cocoComm {
   FlagPage *peer_flags[kMaxRanks] = {};
   unsigned long long seq = 0;
   unsigned long long launches = 0;
+  unsigned long long session = 0;  // random id shared by the ranks (names of side channels)
   int ctas_per_sm = 0;  // 0 = automatic
   int threads = 512;
   int timeout_ms = 10000;
@@ -543,6 +546,31 @@ void set_denominators(StepArgs *sa, int opt, int step) {
 
 }  // namespace
 
+// What symm_mem.cu needs from a communicator.
+namespace coco {
+int comm_world(cocoComm_t c) { return c->world; }
+int comm_rank(cocoComm_t c) { return c->rank; }
+int comm_device(cocoComm_t c) { return c->device; }
+bool comm_is_group(cocoComm_t c) { return (bool)c->group; }
+unsigned long long comm_session(cocoComm_t c) { return c->session; }
+int comm_all_gather(cocoComm_t c, const void *send, void *recv, size_t bytes) {
+  if (!c->boot) return cocoInvalidUsage;
+  return c->boot->all_gather(send, recv, bytes);
+}
+int comm_add_mapped_region(cocoComm_t c, void *ptr, size_t bytes, void *const *peers, void *mc) {
+  return cocoRegisterMapped(c, ptr, bytes, peers, mc);
+}
+int comm_remove_region(cocoComm_t c, void *ptr) {
+  auto &v = c->regions;
+  for (size_t k = 0; k < v.size(); ++k)
+    if (v[k].base == (char *)ptr) {
+      v.erase(v.begin() + k);
+      return cocoSuccess;
+    }
+  return cocoInvalidArgument;
+}
+}  // namespace coco
+
 // ============================================================================
 // C ABI
 // ============================================================================
@@ -591,6 +619,18 @@ int cocoCommInitRank(cocoComm_t *comm, int world, int rank, const char *bootstra
   c->boot.reset(new Bootstrap);
   const int boot_timeout = env_int("COCO_BOOTSTRAP_TIMEOUT_MS", 120000);
   COCO_TRY(c->boot->init(world, rank, resolve_bootstrap_addr(bootstrap), boot_timeout));
+  {  // a session id all ranks share: rank 0's random number
+    unsigned long long mine = 0;
+    FILE *f = fopen("/dev/urandom", "rb");
+    if (f) {
+      if (fread(&mine, sizeof(mine), 1, f) != 1) mine = 0;
+      fclose(f);
+    }
+    if (!mine) mine = (unsigned long long)getpid() * 2654435761ull + (unsigned long long)time(nullptr);
+    std::vector<unsigned long long> all(world);
+    COCO_TRY(c->boot->all_gather(&mine, all.data(), sizeof(mine)));
+    c->session = all[0];
+  }
   int rc = init_common(c.get());
   // agree on success before anyone maps anything
   std::vector<int> rcs(world);

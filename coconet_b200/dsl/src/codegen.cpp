@@ -608,7 +608,15 @@ struct Emitter {
     os << "  for (int __i = firstLog; __i < lastLog; __i++) {\n";
     os << "    size_t " << N() << " = 1UL << __i;\n";
     os << "    // Inputs\n";
-    std::vector<std::string> frees;
+    // Buffers the fused step lets peers touch come from the runtime's symmetric
+    // allocator (peer mappings + NVSwitch multicast where the node has it).
+    std::set<const Node *> symmetric;
+    for (const Step &st : steps)
+      if (st.kind == Step::Fused) {
+        symmetric.insert(st.fused.grad.get());
+        symmetric.insert(st.fused.weight.get());
+      }
+    std::vector<std::string> frees, symm_frees;
     for (const NodeRef &a : args) {
       const std::string ty = elemTypeName(a->type);
       if (a->kind == NodeKind::Variable) {
@@ -620,9 +628,15 @@ struct Emitter {
         // src/codegen.cpp:139-165)
         const std::string cnt = a->layout == Sliced ? sliceCount() : N();
         os << "    " << ty << "* " << a->name << ";\n";
-        os << "    CUDACHECK(cudaMalloc(&" << a->name << ", " << cnt << " * sizeof(" << ty << ")));\n";
+        if (symmetric.count(a.get())) {
+          os << "    COCOCHECK(cocoMemAlloc(comm, (void**)&" << a->name << ", " << cnt << " * sizeof(" << ty
+             << ")));\n";
+          symm_frees.push_back(a->name);
+        } else {
+          os << "    CUDACHECK(cudaMalloc(&" << a->name << ", " << cnt << " * sizeof(" << ty << ")));\n";
+          frees.push_back(a->name);
+        }
         os << "    cudaMemRandInt(" << a->name << ", " << cnt << ");\n";
-        frees.push_back(a->name);
       }
     }
     os << "\n    // Intermediates\n";
@@ -639,15 +653,6 @@ struct Emitter {
         frees.push_back(b + "_acc");
       }
     }
-    // buffers the fused step lets peers touch are mapped before the timed loop
-    for (const Step &st : steps)
-      if (st.kind == Step::Fused) {
-        const FusedUpdate &fu = st.fused;
-        os << "    COCOCHECK(cocoRegister(comm, " << fu.grad->name << ", " << N() << " * sizeof("
-           << elemTypeName(fu.grad->type) << ")));\n";
-        os << "    COCOCHECK(cocoRegister(comm, " << fu.weight->name << ", " << N() << " * sizeof("
-           << elemTypeName(fu.weight->type) << ")));\n";
-      }
     for (const std::string &l : labels) os << "    float elapsedTime" << l << " = 0;\n";
     if (all_float) {
       os << "    if (check) {  // one step, compared with the host evaluation of the same pipeline\n";
@@ -688,12 +693,8 @@ struct Emitter {
     os << ");\n    }\n";
     os << "    CUDACHECK(cudaStreamSynchronize(stream));\n";
     os << "    coconetCheckStatus(comm, rank);\n";
-    for (const Step &st : steps)
-      if (st.kind == Step::Fused) {
-        os << "    COCOCHECK(cocoDeregister(comm, " << st.fused.grad->name << "));\n";
-        os << "    COCOCHECK(cocoDeregister(comm, " << st.fused.weight->name << "));\n";
-      }
     os << "    COCOCHECK(cocoBarrier(comm));\n";
+    for (const std::string &f : symm_frees) os << "    COCOCHECK(cocoMemFree(comm, " << f << "));\n";
     for (const std::string &f : frees) os << "    CUDACHECK(cudaFree(" << f << "));\n";
     os << "    if (rank == 0)\n      printf(\"{SZ: %ld, Epochs: %d";
     for (const std::string &l : labels) os << ", " << l << ": %f";

@@ -55,6 +55,9 @@ _SIGNATURES = {
     "cocoRegisterMapped": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p),
                                      C.c_void_p]),
     "cocoSetAlgo": (C.c_int, [C.c_void_p, C.c_int]),
+    "cocoMemAlloc": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t]),
+    "cocoMemFree": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "cocoMemHasMulticast": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "cocoFusedSGD": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                C.c_size_t, C.c_float, C.c_float, C.c_void_p]),
     "cocoFusedAdam": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
@@ -222,6 +225,38 @@ class Communicator:
         arr = (C.c_void_p * self.world)(*peer_ptrs)
         _check(lib().cocoRegisterMapped(self._h, _ptr(t), t.numel() * t.element_size(), arr,
                                         C.c_void_p(multicast_ptr or None)), "cocoRegisterMapped")
+
+    def mem_alloc(self, numel, dtype):
+        """Collective: a torch tensor over runtime-made symmetric memory (peer
+        mappings and, where supported, an NVSwitch multicast mapping).  Free it
+        with mem_free before destroying the communicator."""
+        import torch
+        esize = torch.empty(0, dtype=dtype).element_size()
+        p = C.c_void_p()
+        _check(lib().cocoMemAlloc(self._h, C.byref(p), numel * esize), "cocoMemAlloc")
+        typestr = {torch.float32: "<f4", torch.float16: "<f2", torch.uint8: "|u1"}.get(dtype)
+        view_dtype = dtype
+        if typestr is None:  # e.g. bfloat16: expose as 16-bit integers, then reinterpret
+            typestr, view_dtype = "<i2", torch.int16
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (numel,), "typestr": typestr,
+                                        "data": (p.value, False), "version": 2}
+        t = torch.as_tensor(_Raw(), device=torch.device("cuda", torch.cuda.current_device()))
+        if view_dtype != dtype:
+            t = t.view(dtype)
+        self._allocs = getattr(self, "_allocs", {})
+        self._allocs[t.data_ptr()] = p.value
+        return t
+
+    def mem_free(self, t):
+        base = getattr(self, "_allocs", {}).pop(t.data_ptr())
+        _check(lib().cocoMemFree(self._h, C.c_void_p(base)), "cocoMemFree")
+
+    def has_multicast(self, t):
+        yes = C.c_int()
+        _check(lib().cocoMemHasMulticast(self._h, _ptr(t), C.byref(yes)), "cocoMemHasMulticast")
+        return bool(yes.value)
 
     def set_algo(self, algo):
         """0 / False / "p2p", 1 / True / "nvls", 2 / "auto"."""

@@ -166,6 +166,19 @@ int cocoDeregister(cocoComm_t comm, void *ptr);
  * all_reduce_computation.h:262-316, left as assert(false) there). */
 int cocoRegisterMapped(cocoComm_t comm, void *ptr, size_t bytes, void *const *peer_ptrs,
                        void *multicast_ptr);
+/* Collective.  Symmetric device memory made by the runtime (the counterpart of
+ * ncclMemAlloc + registration): `bytes` on every rank, each rank's buffer
+ * mapped into every other rank (cuMemCreate, POSIX-fd exchange, cuMemMap) and,
+ * where all devices support it, an NVSwitch multicast mapping over the R
+ * buffers (cuMulticastCreate / BindMem).  The buffer is registered with the
+ * communicator; put the gradients and the gathered weights in such buffers to
+ * get the NVLS path without any other library.  At world size 1 this is
+ * cudaMalloc.  COCO_NO_MULTICAST=1 skips the multicast mapping.  Free with
+ * cocoMemFree (collective) before destroying the communicator. */
+int cocoMemAlloc(cocoComm_t comm, void **ptr, size_t bytes);
+int cocoMemFree(cocoComm_t comm, void *ptr);
+int cocoMemHasMulticast(cocoComm_t comm, const void *ptr, int *yes);
+
 /* 0: peer-to-peer loads and stores, gradients summed in fixed rank order
  * (results reproducible bit for bit).  1: NVLS wherever both buffers have a
  * multicast address (in-switch summation order; 16-bit sums delivered rounded

@@ -158,6 +158,60 @@ def case_nvls(comm):
             print(f"ok {name} R={R} n={n}", flush=True)
 
 
+def case_symm(comm):
+    """Symmetric memory made by the runtime itself (cuMemCreate + fd exchange +
+    cuMulticast): the peer-to-peer path on it is bit-exact as on IPC-mapped
+    memory, the NVSwitch path within tolerance; then everything is freed."""
+    R, rank = comm.world, comm.rank
+    n = 1 << 22
+    h = K.HYPER
+    g = comm.mem_alloc(n, torch.float16)
+    w_lp = comm.mem_alloc(n, torch.float16)
+    mc = comm.has_multicast(g) and comm.has_multicast(w_lp)
+    S = (n + R - 1) // R
+    lo, hi = K.slice_bounds(n, R, rank)
+    for algo, exact in (("p2p", True), ("nvls", False)):
+        if algo == "nvls" and not mc:
+            if rank == 0:
+                print("skip symm nvls: no multicast support", flush=True)
+            continue
+        comm.set_algo(algo)
+        ora = K.OracleState(K.ADAM, n, seed=66, lp=True)
+        w = torch.from_numpy(ora.w.copy()).cuda()
+        m, v = torch.zeros(S, device="cuda"), torch.zeros(S, device="cuda")
+        for step in range(2):
+            grads = K.make_grads(R, n, 66, step, dtype=np.float16, loss_scale=1024.0)
+            g.copy_(torch.from_numpy(grads[rank]))
+            torch.cuda.synchronize()
+            comm.barrier()
+            comm.fused_adam(g, w, m, v, h["lr"], h["beta1"], h["beta2"], h["eps"], step, w_lp=w_lp,
+                            grad_scale=1 / 1024.0)
+            torch.cuda.synchronize()
+            assert comm.status()["code"] == 0
+            ora.step(grads, step, inv_scale=1 / 1024.0)
+            if exact:
+                assert np.array_equal(w.cpu().numpy()[lo:hi], ora.w[lo:hi])
+                assert np.array_equal(w_lp.cpu().numpy().view(np.uint16), ora.w_lp.view(np.uint16))
+                assert np.array_equal(m.cpu().numpy()[: hi - lo], ora.m[lo:hi])
+            else:
+                K.assert_close_most(w.cpu().numpy()[lo:hi], ora.w[lo:hi], 2e-3, "symm nvls master", rtol_all=4e-3)
+                K.assert_close(w_lp.float().cpu().numpy(), ora.w_lp.astype(np.float32), 4e-3, "symm nvls w_lp")
+            comm.barrier()
+        if rank == 0:
+            print(f"ok symm_{algo} R={R} multicast={mc}", flush=True)
+    comm.set_algo("auto")
+    comm.mem_free(g)
+    comm.mem_free(w_lp)
+    # a second allocation after a free reuses the side channel names
+    t = comm.mem_alloc(1000, torch.float32)
+    t.fill_(float(rank))
+    torch.cuda.synchronize()
+    comm.barrier()
+    comm.mem_free(t)
+    if rank == 0:
+        print("ok symm_free_realloc", flush=True)
+
+
 def case_timeout(comm):
     """Rank 1 skips one fused call: the others' bounded start wait must give
     up with a status, leave the weights untouched and keep the context alive."""
@@ -194,7 +248,7 @@ if __name__ == "__main__":
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     comm = coco.Communicator.init_rank(world, rank)
     try:
-        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls}[sys.argv[1]](comm)
+        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls, "symm": case_symm}[sys.argv[1]](comm)
     except Exception:  # keep this rank alive until its peers are done with its memory
         import traceback
         print("WORKER FAILURE rank %d\n%s" % (rank, traceback.format_exc()), flush=True)

@@ -80,3 +80,11 @@ def test_emitted_program_multi_rank(tmp_path, opt, schedule):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
     assert r.stdout.count("PASSED") == 8 * world and "FAILED" not in r.stdout
     assert "{SZ: 524288, Epochs: 3" in r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_runtime_symmetric_memory_and_multicast():
+    world = min(_ngpu(), 8)
+    r = _launch("symm", world)
+    assert r.returncode == 0, _why(r)
+    assert "ok symm_p2p" in r.stdout and "ok symm_free_realloc" in r.stdout, r.stdout
