@@ -7,7 +7,9 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcoconet_rt.so")
 SOURCES = ["fused_step.cu", "runtime.cu", "bootstrap.cpp", "no_alloc.cu", "symm_mem.cu"]
-HEADERS = ["fused_step.cuh", "bootstrap.h", os.path.join(ROOT, "include", "coconet_rt.h")]
+HEADERS = ["fused_step.cuh", "bootstrap.h", os.path.join(ROOT, "include", "coconet_rt.h"),
+           os.path.join(ROOT, "include", "coconet_device.h"),
+           os.path.join(ROOT, "include", "coconet_fused_generic.cuh")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 

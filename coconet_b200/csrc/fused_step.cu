@@ -1104,12 +1104,12 @@ __global__ void __launch_bounds__(512, 2)
   // done with direct loads.
   TilePlan tp;
   const size_t T = (size_t)kTileElemsPerThread * blockDim.x;
-  tp.stages = (PATH == kPathTiles && ra.pad) ? sa.pipe_stages : 0;
+  tp.stages = (PATH == kPathTiles && ra.aligned16) ? sa.pipe_stages : 0;
   tp.g_bytes = (unsigned)(T * sizeof(GT));
   tp.stage_bytes = (unsigned)(R * tp.g_bytes + (OPT == kSGD ? 1 : 3) * T * 4);
   tp.ntiles = tp.stages > 0 ? L / T : 0;
   const size_t piped = tp.ntiles * T;  // elements covered by the pipeline
-  const size_t nvec_rest = ra.pad ? (L - piped) / VEC : 0;
+  const size_t nvec_rest = ra.aligned16 ? (L - piped) / VEC : 0;
   unsigned iter = 0;
 
   double sum_w2 = 0.0, sum_r2 = 0.0;
@@ -1124,7 +1124,7 @@ __global__ void __launch_bounds__(512, 2)
   // NVLS: whole 16-byte units of the slice go through the switch; the rest
   // (and everything when unaligned) falls through to the peer-to-peer code.
   constexpr int NV = Multimem<GT>::kN;
-  const bool nvls = PATH == kPathNvls && (sa.flags & kFlagNvls) && ra.pad && ra.mc_g &&
+  const bool nvls = PATH == kPathNvls && (sa.flags & kFlagNvls) && ra.aligned16 && ra.mc_g &&
                     ra.mc_out && sa.variant != cocoVariantNccl;
   const size_t nvls_units = nvls ? L / NV : 0;
   if constexpr (PATH == kPathNvls) {

@@ -109,7 +109,7 @@ extern "C" int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *
   ra.w = w, ra.m = m, ra.v = v;
   ra.rank = 0;
   auto al16 = [](const void *p) { return (((uintptr_t)p) & 15u) == 0; };
-  ra.pad = (al16(g) && al16(w) && al16(m) && al16(v) && al16(ra.out[0])) ? 1 : 0;
+  ra.aligned16 = (al16(g) && al16(w) && al16(m) && al16(v) && al16(ra.out[0])) ? 1 : 0;
 
   LaunchConfig cfg = {};
   cfg.threads = 512;

@@ -25,6 +25,7 @@
 
 #include "bootstrap.h"
 #include "coconet_rt.h"
+#include "coconet_fused_generic.cuh"
 #include "fused_step.cuh"
 
 using namespace coco;
@@ -388,7 +389,7 @@ void fill_rank_args(RankArgs *ra, int rank, int world, char *const g_views[], ch
   const size_t vec = 8;  // 16 bytes of the narrowest element type
   size_t lo = (size_t)rank * S;
   if (lo > pc.sa.count) lo = pc.sa.count;
-  ra->pad = (ok16 && (lo % vec) == 0) ? 1 : 0;
+  ra->aligned16 = (ok16 && (lo % vec) == 0) ? 1 : 0;
 }
 
 // Launch of one rank that owns its device alone (process mode, or a
@@ -947,6 +948,41 @@ int cocoFusedLAMB(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *
   set_denominators(&pc.sa, kLAMB, step);
   pc.stream = (cudaStream_t)stream;
   return enqueue(comm, pc);
+}
+
+int cocoFusedGenericPlan(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w,
+                         size_t count, float grad_scale, cocoStream_t stream,
+                         cocoGenericPlan *plan) {
+  (void)stream;
+  if (!comm || !g || !w || !plan) return cocoInvalidArgument;
+  if (g_type != cocoFloat32 && g_type != cocoFloat16) return cocoInvalidArgument;
+  if (comm->group) return cocoInvalidUsage;  // one process per GPU (or world size 1)
+  memset(plan, 0, sizeof(*plan));
+  plan->sa.count = count;
+  plan->sa.world = comm->world;
+  plan->sa.grad_scale = grad_scale;
+  plan->sa.timeout_ns = (unsigned long long)comm->timeout_ms * 1000000ull;
+  if (count == 0) return cocoSuccess;
+  plan->sa.seq = ++comm->seq;
+  DeviceGuard guard(comm->device);
+  if (!guard.ok) return cocoCudaError;
+  char *g_views[kMaxRanks] = {}, *out_views[kMaxRanks] = {};
+  char *mc_g = nullptr, *mc_out = nullptr;
+  COCO_TRY(peer_views(comm, g, count * dtype_size(g_type), g_views, &mc_g));
+  COCO_TRY(peer_views(comm, w, count * sizeof(float), out_views, &mc_out));
+  PendingCall pc;
+  pc.opt = kSGD;  // no m, v of the library's own: the functor owns its state
+  pc.g = g, pc.g_type = g_type, pc.w = w;
+  pc.sa = plan->sa;
+  fill_rank_args(&plan->ra, comm->rank, comm->world, g_views, out_views, comm->peer_flags, pc);
+  const size_t slice = (count + comm->world - 1) / comm->world;
+  const int threads = 512;
+  long ctas = 2L * comm->sm_count;
+  const long need = (long)std::max<size_t>(1, (slice + 4 * (size_t)threads - 1) / (4 * (size_t)threads));
+  plan->ctas = (int)std::max(1L, std::min(ctas, need));
+  plan->threads = threads;
+  comm->launches++;
+  return cocoSuccess;
 }
 
 int cocoLastLambNorms(cocoComm_t comm, double out[2]) {

@@ -61,12 +61,14 @@ std::string fmtConst(double v, TensorElemType t) {
 
 // One launch of the emitted step function.
 struct Step {
-  enum Kind { Fused, Collective, Kernel, NormReduce } kind;
+  enum Kind { Fused, FusedGeneric, Collective, Kernel, NormReduce } kind;
   std::string label;                 // timer name
   std::vector<NodeRef> stages;       // Kernel: stages computed; else one stage
   FusedUpdate fused;
   NodeRef coll;                      // Collective: the collective node
   int kernel_id = -1;
+  // FusedGeneric: the gradient, the gathered weight tensor and the value gathered into it
+  NodeRef ggrad, gweight, gvalue, greduce;
 };
 
 struct Emitter {
@@ -123,13 +125,21 @@ struct Emitter {
         st.kind = Step::Fused;
         st.stages = group;
         st.fused = p.classify(group);
-        if (st.fused.rule == FusedUpdate::Unknown) {
-          std::string names;
-          for (const NodeRef &s : group) names += " " + s->name;
-          fail("fused group {" + names + " } of pipeline '" + p.name() +
-               "' is not a ReduceScatter -> SGD | Adam | LAMB update -> AllGather step");
-        }
         st.label = "FusedAllReduce";
+        if (st.fused.rule == FusedUpdate::Unknown) {
+          // not one of the rules the library ships a kernel for: compile the
+          // group's arithmetic into a device functor for the generic fused kernel
+          std::string why;
+          if (!genericFusable(group, &st, &why)) {
+            std::string names;
+            for (const NodeRef &s : group) names += " " + s->name;
+            fail("fused group {" + names + " } of pipeline '" + p.name() +
+                 "' is not a ReduceScatter -> SGD | Adam | LAMB update -> AllGather step, and cannot "
+                 "be compiled into a generic fused step either: " + why);
+          }
+          st.kind = Step::FusedGeneric;
+          st.kernel_id = kernel_id++;
+        }
         steps.push_back(st);
         continue;
       }
@@ -190,6 +200,136 @@ struct Emitter {
     for (const NodeRef &s : p.stages())
       if (in_memory.count(s.get()) && s->kind != NodeKind::Update && !isCollective(s->kind))
         buffer[s.get()] = s->name;
+  }
+
+  // ---- generic fused groups ------------------------------------------------------
+  // ReduceScatter(sum) of one Local tensor, any pointwise arithmetic (no Norm),
+  // Updates of Sliced tensors, and exactly one Replicated tensor updated with
+  // an AllGather of a Sliced value.
+  bool genericFusable(const std::vector<NodeRef> &group, Step *st, std::string *why) const {
+    std::vector<NodeRef> nodes;
+    for (const NodeRef &s : group) ownedNodes(s, true, &nodes);
+    for (const NodeRef &n : nodes) {
+      if (n->kind == NodeKind::Norm) return *why = "it contains a Norm", false;
+      if (n->kind == NodeKind::AllReduce || n->kind == NodeKind::Broadcast)
+        return *why = "only ReduceScatter ... AllGather groups fuse", false;
+      if (n->kind == NodeKind::ReduceScatter) {
+        if (st->greduce && st->greduce != n) return *why = "more than one ReduceScatter", false;
+        if (n->red != Summation || n->in[0]->kind != NodeKind::Tensor)
+          return *why = "the ReduceScatter must sum a Local tensor", false;
+        st->greduce = n;
+        st->ggrad = n->in[0];
+      }
+      if (n->kind == NodeKind::Update && n->in[0]->layout == Replicated) {
+        if (st->gweight) return *why = "more than one Replicated tensor is updated", false;
+        if (n->in[1]->kind != NodeKind::AllGather) return *why = "the Replicated update is not an AllGather", false;
+        st->gweight = n->in[0];
+        st->gvalue = n->in[1]->in[0];
+      }
+      if (n->kind == NodeKind::Tensor && n->layout == Replicated && n->type != Float32)
+        return *why = "Replicated tensors must be Float32", false;
+    }
+    if (!st->greduce) return *why = "no ReduceScatter", false;
+    if (!st->gweight) return *why = "no AllGather into a Replicated tensor", false;
+    if (st->ggrad->type != Float32 && st->ggrad->type != Float16)
+      return *why = "gradients must be Float32 or Float16", false;
+    return true;
+  }
+
+  // Expression inside the functor: i0 = index in the slice, gi = global index,
+  // gsum = the reduced gradient element, w_old = the weight element.
+  std::string fexpr(const Step &st, const NodeRef &n, const std::set<const Node *> &done) const {
+    if (n.get() == st.greduce.get()) return "gsum";
+    if (n->stage_id >= 0 && done.count(n.get())) {
+      if (n->kind == NodeKind::Update) return n->in[0]->name + "[i0]";
+      return n->name;
+    }
+    switch (n->kind) {
+      case NodeKind::Const: return fmtConst(n->value, n->type);
+      case NodeKind::Variable: return n->name;
+      case NodeKind::Tensor:
+        if (n.get() == st.gweight.get()) return "w_old";
+        return n->layout == Sliced ? n->name + "[i0]" : n->name + "[gi]";
+      case NodeKind::Binary:
+        return "(" + fexpr(st, n->in[0], done) + " " + n->op + " " + fexpr(st, n->in[1], done) + ")";
+      case NodeKind::Sqrt: return "sqrtf(" + fexpr(st, n->in[0], done) + ")";
+      case NodeKind::Cast:
+        return "((" + std::string(elemTypeName(n->type)) + ")" + fexpr(st, n->in[0], done) + ")";
+      case NodeKind::Scatter:
+      case NodeKind::AllGather: return fexpr(st, n->in[0], done);
+      case NodeKind::Update: return n->in[0]->name + "[i0]";
+      default: fail("cannot emit node inside a fused functor");
+    }
+  }
+
+  // Members of the functor: Sliced tensors, other Replicated tensors, Variables.
+  void functorMembers(const Step &st, std::vector<std::string> *decl, std::vector<std::string> *init) const {
+    std::set<std::string> seen;
+    std::function<void(const NodeRef &, bool)> walk = [&](const NodeRef &n, bool root) {
+      if (!root && n->stage_id >= 0) {
+        bool member = false;
+        for (const NodeRef &s : st.stages) member = member || s.get() == n.get();
+        if (!member) fail("a fused group reads stage " + n->name + " computed outside it");
+        return;
+      }
+      if (n->kind == NodeKind::Variable && seen.insert(n->name).second) {
+        decl->push_back(std::string(elemTypeName(n->type)) + " " + n->name);
+        init->push_back(n->name);
+      }
+      if (n->kind == NodeKind::Tensor && n.get() != st.ggrad.get() && n.get() != st.gweight.get() &&
+          seen.insert(n->name).second) {
+        decl->push_back(std::string(elemTypeName(n->type)) + "* " + n->name);
+        init->push_back(n->name);
+      }
+      for (const NodeRef &c : n->in) walk(c, false);
+    };
+    for (const NodeRef &s : st.stages) walk(s, true);
+  }
+
+  void emitFunctor(const Step &st) {
+    std::vector<std::string> decl, init;
+    functorMembers(st, &decl, &init);
+    kernels << "// The arithmetic of the fused group, applied to one element of this rank's slice.\n";
+    kernels << "struct " << p.name() << "Fused" << st.kernel_id << " {\n";
+    for (const std::string &d : decl) kernels << "  " << d << ";\n";
+    kernels << "  __device__ __forceinline__ float operator()(size_t i0, size_t gi, float gsum, float w_old) const {\n";
+    kernels << "    (void)i0; (void)gi; (void)gsum; (void)w_old;\n";
+    std::set<const Node *> done;
+    std::string result = "w_old";
+    for (const NodeRef &s : st.stages) {
+      if (s.get() == st.greduce.get()) {
+        done.insert(s.get());
+        continue;
+      }
+      if (s->kind == NodeKind::Update) {
+        if (s->in[0].get() == st.gweight.get()) {
+          result = fexpr(st, s->in[1], done);
+        } else {
+          kernels << "    " << s->in[0]->name << "[i0] = " << fexpr(st, s->in[1], done) << ";\n";
+        }
+      } else {
+        NodeRef tmp = std::make_shared<Node>(*s);
+        tmp->stage_id = -1;
+        kernels << "    " << elemTypeName(s->type) << " " << s->name << " = " << fexpr(st, tmp, done) << ";\n";
+      }
+      done.insert(s.get());
+    }
+    kernels << "    return " << result << ";\n  }\n};\n\n";
+  }
+
+  std::string genericCall(const Step &st) const {
+    std::vector<std::string> decl, init;
+    functorMembers(st, &decl, &init);
+    std::ostringstream o;
+    const std::string gt = st.ggrad->type == Float16 ? "__half" : "float";
+    o << "  {\n    cocoGenericPlan plan;\n";
+    o << "    COCOCHECK(cocoFusedGenericPlan(comm, " << st.ggrad->name << ", " << cocoType(st.ggrad->type)
+      << ", " << st.gweight->name << ", " << N() << ", 1.0f, stream, &plan));\n";
+    o << "    " << p.name() << "Fused" << st.kernel_id << " f = {";
+    for (size_t k = 0; k < init.size(); ++k) o << (k ? ", " : "") << init[k];
+    o << "};\n";
+    o << "    COCOCHECK(cocoLaunchGenericFused<" << gt << ">(plan, f, stream));\n  }\n";
+    return o.str();
   }
 
   // ---- expressions inside a generated kernel ----------------------------------
@@ -496,13 +636,20 @@ struct Emitter {
     // Norm results need a buffer even when only read in the next kernel
     for (const Step &st : steps)
       if (st.kind == Step::NormReduce) buffer[st.stages[0].get()] = st.stages[0]->name;
-    for (const Step &st : steps)
+    bool has_generic = false;
+    for (const Step &st : steps) {
       if (st.kind == Step::Kernel) emitKernel(st);
+      if (st.kind == Step::FusedGeneric) {
+        emitFunctor(st);
+        has_generic = true;
+      }
+    }
 
     os << "// Generated by the coconet-b200 DSL emitter from pipeline '" << p.name() << "'.\n";
     if (needs_nccl) os << "#define COCONET_USE_NCCL 1\n";
-    os << "#include \"header.h\"\n\n";
-    os << kernels.str();
+    os << "#include \"header.h\"\n";
+    if (has_generic) os << "#include \"coconet_fused_generic.cuh\"\n";
+    os << "\n" << kernels.str();
 
     // signature
     std::vector<std::string> decl, call;
@@ -563,6 +710,9 @@ struct Emitter {
         case Step::Fused:
           body << "  COCOCHECK(" << fusedCall(st.fused) << ");\n";
           break;
+        case Step::FusedGeneric:
+          body << genericCall(st);
+          break;
         case Step::Collective:
           body << collectiveCall(st);
           break;
@@ -611,11 +761,16 @@ struct Emitter {
     // Buffers the fused step lets peers touch come from the runtime's symmetric
     // allocator (peer mappings + NVSwitch multicast where the node has it).
     std::set<const Node *> symmetric;
-    for (const Step &st : steps)
+    for (const Step &st : steps) {
       if (st.kind == Step::Fused) {
         symmetric.insert(st.fused.grad.get());
         symmetric.insert(st.fused.weight.get());
       }
+      if (st.kind == Step::FusedGeneric) {
+        symmetric.insert(st.ggrad.get());
+        symmetric.insert(st.gweight.get());
+      }
+    }
     std::vector<std::string> frees, symm_frees;
     for (const NodeRef &a : args) {
       const std::string ty = elemTypeName(a->type);

@@ -71,6 +71,8 @@ _SIGNATURES = {
                                       C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
                                       C.c_float, C.c_float, C.c_float, C.c_int, C.c_float,
                                       C.c_void_p]),
+    "cocoFusedGenericPlan": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t,
+                                       C.c_float, C.c_void_p, C.c_void_p]),
     "cocoLastLambNorms": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "cocoGetStatus": (C.c_int, [C.c_void_p, C.POINTER(_Status)]),
     "cocoSliceBounds": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_size_t),
@@ -142,6 +144,23 @@ def _stream(stream):
     return C.c_void_p(s.cuda_stream)
 
 
+def rendezvous_address(pg=None):
+    """"host:port" for the runtime's TCP rendezvous, agreed through an
+    initialised torch.distributed group (any backend): rank 0 picks a free port
+    and broadcasts it."""
+    import socket
+    import torch.distributed as dist
+    box = [None]
+    if dist.get_rank(pg) == 0:
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        box[0] = s.getsockname()[1]
+        s.close()
+    dist.broadcast_object_list(box, src=0, group=pg)
+    host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    return f"{host}:{box[0]}"
+
+
 class HostBootstrap:
     """The runtime's TCP rendezvous on its own (no GPU needed)."""
 
@@ -192,20 +211,9 @@ class Communicator:
 
     @classmethod
     def from_torch_distributed(cls, pg=None):
-        """Rendezvous through an initialised torch.distributed group: rank 0
-        picks a free port and broadcasts it."""
-        import socket
+        """Rendezvous through an initialised torch.distributed group."""
         import torch.distributed as dist
-        world, rank = dist.get_world_size(pg), dist.get_rank(pg)
-        box = [None]
-        if rank == 0:
-            s = socket.socket()
-            s.bind(("127.0.0.1", 0))
-            box[0] = s.getsockname()[1]
-            s.close()
-        dist.broadcast_object_list(box, src=0, group=pg)
-        host = os.environ.get("MASTER_ADDR", "127.0.0.1")
-        return cls.init_rank(world, rank, f"{host}:{box[0]}")
+        return cls.init_rank(dist.get_world_size(pg), dist.get_rank(pg), rendezvous_address(pg))
 
     def destroy(self):
         if self._h:

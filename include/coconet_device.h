@@ -1,0 +1,74 @@
+// Device-side ABI of the fused step: the argument blocks a kernel receives and
+// the peer-visible flag page.  Shared by the runtime library and by kernels
+// that programs instantiate themselves (coconet_fused_generic.cuh).  CUDA C++.
+#ifndef COCONET_DEVICE_H_
+#define COCONET_DEVICE_H_
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "coconet_rt.h"
+
+namespace coco {
+
+constexpr int kMaxRanks = COCO_MAX_RANKS;
+constexpr int kMaxCtasPerRank = 2048;  // rows of the per-CTA partial-norm table
+
+enum Opt : int { kSGD = 0, kAdam = 1, kLAMB = 2 };
+
+// Phases recorded in the status word when a bounded wait gives up.
+enum Phase : int { kPhaseStart = 1, kPhaseNorm = 2, kPhaseEnd = 3, kPhaseCopy = 4 };
+
+// One per rank, in device memory, mapped into every peer.  Zero at creation;
+// every flag only ever grows (it holds the sequence number of a fused call),
+// so nothing is reset between steps and a late reader can never miss a value.
+struct FlagPage {
+  // --- written by peers (slot = writer's rank), polled locally -------------
+  unsigned long long arrive[kMaxRanks];     // "my kernel for call seq has started"
+  unsigned long long done[kMaxRanks];       // "all my reads/writes of call seq are complete"
+  unsigned long long norm_flag[kMaxRanks];  // "norm_part[slot] of call seq is valid"
+  double norm_part[kMaxRanks][2];           // per-rank partial sums {sum w^2, sum r^2}
+  // --- local only ---------------------------------------------------------
+  unsigned int done_count;  // CTAs of this rank that finished their data phase
+  unsigned int norm_count;  // CTAs of this rank that posted their partial norms
+  int status[8];            // cocoStatus_t image: code, rank, phase, peer, seq lo/hi
+  double last_norms[2];     // {||w||, ||r||} of the last LAMB step
+  double cta_part[kMaxCtasPerRank][2];
+};
+
+// Per-rank pointers of one fused call.  Indexed tables hold the view THIS
+// rank has of every peer's buffer (entry [rank] is the rank's own buffer).
+struct RankArgs {
+  const void *g[kMaxRanks];   // gradients of each peer, element 0
+  void *out[kMaxRanks];       // gathered output of each peer (fp32 w, or w_lp), element 0
+  FlagPage *flags[kMaxRanks]; // flag page of each peer
+  float *w;                   // own fp32 weights, element 0 (N elements)
+  float *m;                   // own first moment, slice-local (S elements)
+  float *v;                   // own second moment, slice-local
+  const void *mc_g;           // NVLS multicast address of the gradient buffers, or null
+  void *mc_out;               // NVLS multicast address of the gathered output, or null
+  int rank;
+  int aligned16;              // non-zero: slice start and all pointers are 16-byte aligned
+};
+
+// Internal StepArgs::flags bit (public flags use the low byte).
+constexpr unsigned kFlagNvls = 0x100u;  // reduce / gather through NVSwitch multicast
+
+// Scalars of one fused call, identical on every rank.
+struct StepArgs {
+  unsigned long long count;   // N
+  unsigned long long seq;     // sequence number of this call on the communicator (>= 1)
+  unsigned long long timeout_ns;
+  int world;
+  int variant;                // cocoVariant_t
+  unsigned flags;
+  float lr, beta1, beta2, eps, weight_decay, grad_scale;
+  float d1, d2;               // denominators of m^ = m/d1, v^ = v/d2 ...
+  double d1d, d2d;            // ... in double for the bias-corrected form
+  int pipe_stages;            // stages of the bulk-copy tile pipeline, 0 = off
+  int pad;
+};
+
+}  // namespace coco
+
+#endif  // COCONET_DEVICE_H_

@@ -238,6 +238,17 @@ int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *w, void *w_
                         float beta1, float beta2, float eps, float weight_decay, int step,
                         float grad_scale, cocoStream_t stream);
 
+/* Prepares one fused step whose update the CALLER supplies as a device
+ * functor (include/coconet_fused_generic.cuh: cocoLaunchGenericFused): peer
+ * views of g and w, flag pages, sequence number and launch shape.  Collective
+ * like the fused calls; call it once per step, then launch.  The counterpart
+ * of the template-filling generator the reference left unreachable
+ * (src/codegen.cpp:1948-3929). */
+struct cocoGenericPlan;
+int cocoFusedGenericPlan(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w,
+                         size_t count, float grad_scale, cocoStream_t stream,
+                         struct cocoGenericPlan *plan);
+
 /* Norms of the last LAMB step on this communicator: out[0] = ||w||,
  * out[1] = ||r|| as used for the trust ratio.  Synchronise the stream first. */
 int cocoLastLambNorms(cocoComm_t comm, double out[2]);

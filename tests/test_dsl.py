@@ -106,6 +106,20 @@ def test_emitted_programs_compile_for_sm100a(dsl_build, tmp_path, opt, schedule)
                            "-o", str(tmp_path / "x.o")])
 
 
+def test_other_update_rules_compile_into_a_device_functor(dsl_build, tmp_path):
+    text = _gen(dsl_build, "nesterov", "fuse_RS_C_AG", tmp_path)
+    assert '#include "coconet_fused_generic.cuh"' in text
+    assert "struct nesterovFused0 {" in text
+    assert "mom[i0] = ((mu * mom[i0]) + gsum);" in text
+    assert "(w_old - (lr * (gsum + (mu * mom[i0]))))" in text
+    assert "cocoFusedGenericPlan(comm, g, cocoFloat32, w, N, 1.0f, stream, &plan)" in text
+    assert "cocoLaunchGenericFused<float>(plan, f, stream)" in text
+    assert "cocoMemAlloc(comm, (void**)&g" in text and "cocoMemAlloc(comm, (void**)&w" in text
+    subprocess.check_call([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                           os.path.join(DSL, "rt"), "-I", os.path.join(ROOT, "include"), "-c",
+                           str(tmp_path / "nesterov-fuse_RS_C_AG.cu"), "-o", str(tmp_path / "n.o")])
+
+
 def test_unrecognised_fused_group_is_an_error(dsl_build, tmp_path):
     prog = tmp_path / "bad.cpp"
     prog.write_text('''
@@ -116,10 +130,11 @@ int main() {
   Variable N(Int32, "N"); Variable lr(Float32, "lr");
   Tensor g(Float32, N, Local, "g"); Tensor w(Float32, N, Replicated, "w");
   Stage gs = ReduceScatter(Summation, g);
-  Stage ws = Scatter(w) * gs;              // not an optimizer step
+  Stage nrm = Norm(gs);                    // a global norm that is not LAMB's
+  Stage ws = Scatter(w) - lr * gs / nrm;
   Stage wn = Update(w, AllGather(ws));
   Pipeline p("odd", {g, w, lr}, {wn});
-  p.fuse({gs, ws, wn});
+  p.fuse({gs, nrm, ws, wn});
   p.codegen("odd.cu");
 }''')
     exe = str(tmp_path / "bad")
@@ -127,3 +142,4 @@ int main() {
                            os.path.join(dsl_build, "libcoconet_dsl.a"), "-o", exe])
     r = subprocess.run([exe], cwd=tmp_path, capture_output=True, text=True)
     assert r.returncode == 2 and "is not a ReduceScatter -> SGD | Adam | LAMB" in r.stderr
+    assert "it contains a Norm" in r.stderr

@@ -122,3 +122,37 @@ def test_bootstrap_times_out_when_a_rank_never_joins():
     assert res[2] == "skipped"
     assert res[0] == "error 5"  # rank 0 gives up in accept()
     assert res[1].startswith("error")  # connected, then the root went away
+
+
+# ---- world-size-2 host path under torch.distributed (gloo, CPU) --------------
+
+def _gloo_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        addr = coco.rendezvous_address()           # rank 0 picks a port, everyone learns it
+        bs = coco.HostBootstrap(world, rank, addr, timeout_ms=20000)
+        # every rank computes every rank's slice; the shards must tile [0, count)
+        count = 334_000_000
+        mine = "%d:%d" % coco.slice_bounds(count, world, rank)
+        got = [b.decode().rstrip("\0") for b in bs.all_gather(mine.encode().ljust(32, b"\0"))]
+        bs.barrier()
+        bs.close()
+        q.put((rank, addr, got))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gloo_world_2_rendezvous_and_sharding():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_gloo_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in ps)
+    for p in ps:
+        p.join(timeout=30)
+    assert res[0][1] == res[1][1]                      # the same address on both ranks
+    assert res[0][2] == res[1][2] == ["0:167000000", "167000000:334000000"]
