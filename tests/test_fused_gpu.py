@@ -469,3 +469,84 @@ def test_host_side_usage_errors():
     finally:
         for c in comms:
             c.destroy()
+
+
+# ---- edge cases: empty, tiny and very large inputs ---------------------------------
+
+@pytest.mark.parametrize("R", [1, 2, 8])
+def test_empty_and_tiny_counts(R):
+    # count 0: nothing is launched; count < R: some ranks own an empty slice
+    comms = coco.Communicator.init_all(R, [0] * R)
+    try:
+        before = sum(c.launch_count() for c in comms)
+        z = torch.zeros(8, device="cuda")
+        with coco.group():
+            for c in comms:
+                coco.runtime._check(coco.lib().cocoFusedSGD(
+                    c._h, z.data_ptr(), 7, z.data_ptr(), None, 6, 0, 0.1, 1.0, None), "count 0")
+        assert sum(c.launch_count() for c in comms) == before
+        for n in (1, 2, 3, 5):
+            ranks = Ranks(K.ADAM, R, n, seed=40 + n)
+            ora = K.OracleState(K.ADAM, n, seed=40 + n)
+            try:
+                grads = K.make_grads(R, n, 40 + n, 0)
+                ranks.step(grads, 0)
+                ora.step(grads, 0)
+                _check_against(ranks, ora, exact_w=True)
+            finally:
+                ranks.close()
+    finally:
+        for c in comms:
+            c.destroy()
+
+
+def test_more_than_2_to_the_31_elements():
+    # Index and byte-offset arithmetic beyond 32 bits: 2^31 + 2^20 + 24 elements,
+    # two ranks (slice starts at byte offset > 2^32 in the fp32 arrays).  Checked
+    # through a size-independent property: the two-rank fused SGD step equals the
+    # one-rank step on the pre-summed gradient, bit for bit, everywhere.
+    n = (1 << 31) + (1 << 20) + 24
+    free, _ = torch.cuda.mem_get_info()
+    if free < 70 * (1 << 30):
+        pytest.skip("needs about 60 GB of free device memory")
+    R = 2
+    gen = torch.Generator(device="cuda").manual_seed(99)
+
+    def big_randn(scale, dtype):
+        t = torch.empty(n, dtype=dtype, device="cuda")
+        step = 1 << 28
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            t[a:b] = (torch.randn(b - a, device="cuda", generator=gen) * scale).to(dtype)
+        return t
+
+    g = [big_randn(1.0, torch.float16) for _ in range(R)]
+    w0 = big_randn(0.02, torch.float32)
+    comms = coco.Communicator.init_all(R, [0] * R)
+    one = coco.Communicator.init_all(1, [0])[0]
+    try:
+        w = [w0.clone() for _ in range(R)]
+        with coco.group():
+            for r, c in enumerate(comms):
+                c.fused_sgd(g[r], w[r], 0.01)
+        torch.cuda.synchronize()
+        for c in comms:
+            assert c.status()["code"] == 0
+        assert torch.equal(w[0], w[1])
+        w1 = w[1]
+        del w[1]
+        del w1
+        gs = torch.empty(n, dtype=torch.float32, device="cuda")
+        step = 1 << 28
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            gs[a:b] = g[0][a:b].float() + g[1][a:b].float()
+        del g
+        one.fused_sgd(gs, w0, 0.01)
+        torch.cuda.synchronize()
+        assert torch.equal(w[0], w0)
+        # the last elements (past 2^31) did change and are finite
+        assert bool(torch.isfinite(w0[-64:]).all())
+    finally:
+        for c in comms + [one]:
+            c.destroy()
