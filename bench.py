@@ -290,6 +290,39 @@ def run_sweep(args, rank, world, local_rank):
             print(f"# {opt:5s} {gt} n={n:>11d} fused {ms:9.4f} ms  bus {p['bus_gbs']:7.1f} GB/s  "
                   f"hbm {p['hbm_gbs']:7.1f} GB/s  roof {p['roof_frac']:.3f}  stock {base:9.4f} ms  "
                   f"x{p['speedup']:.2f}" + (f"  back-to-back {b2b * 1e3:7.1f} us" if b2b else ""), flush=True)
+    # ---- a list of tensors shaped like BERT-large (24 layers, hidden 1024, FFN 4096,
+    # vocabulary 30522, 512 positions: 391 tensors, 335 M elements) through the scattered
+    # call, next to the flat call on the same number of elements
+    shapes = [30522 * 1024, 512 * 1024, 2 * 1024, 1024, 1024]
+    for _ in range(24):
+        shapes += [1024 * 1024, 1024] * 4 + [1024, 1024]
+        shapes += [1024 * 4096, 4096, 4096 * 1024, 1024, 1024, 1024]
+    shapes += [1024 * 1024, 1024, 1024 * 1024, 1024, 1024, 1024, 30522, 2 * 1024, 2]
+    tot = sum(shapes)
+    if tot <= max_n and not use_nvls:
+        gl, wl, at = [], [], 0
+        for c in shapes:
+            gl.append(g32[at:at + c])
+            wl.append(w32[at:at + c])
+            at += (c + 7) // 8 * 8       # keep every tensor 16-byte aligned inside the big buffers
+        if at <= max_n:
+            Ssc = coco.scattered_slice_elems(shapes, R)
+            msc, vsc = torch.zeros(Ssc, device=dev), torch.zeros(Ssc, device=dev)
+
+            def scattered(i):
+                comm.fused_adam_scattered(gl, wl, msc, vsc, HYPER["lr"], HYPER["beta1"],
+                                          HYPER["beta2"], HYPER["eps"], i)
+
+            def flat(i):
+                comm.fused_adam(g32[:tot], w32[:tot], m[:(tot + R - 1) // R], v[:(tot + R - 1) // R],
+                                HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"], i)
+
+            ms_sc, ms_fl = time_ms(scattered, 5, 3), time_ms(flat, 5, 3)
+            out.append({"opt": "adam", "grad": "f32", "count": tot, "world": R, "tensors": len(shapes),
+                        "scattered_ms": ms_sc, "flat_ms": ms_fl})
+            if rank == 0:
+                print(f"# adam  f32 scattered over {len(shapes)} BERT-large-shaped tensors, {tot} elements: "
+                      f"{ms_sc:.4f} ms  (flat call on as many elements: {ms_fl:.4f} ms)", flush=True)
     st = comm.status()
     if rank == 0:
         line = {"sweep": out, "n_gpus": R, "status": st["code"],

@@ -1036,9 +1036,10 @@ __device__ __forceinline__ bool run_tiles(const RankArgs &ra, const StepArgs &sa
 // allocation of its own (with all three in one kernel the peer-to-peer loop
 // spilled 376 bytes and lost 6 %): kPathDirect = register-staged peer loads
 // and stores for world sizes 2..8, kPathLocal = the same for world size 1
-// (wider units), kPathNvls = NVSwitch multimem, kPathTiles = bulk-copy pipeline.
+// (wider units), kPathNvls = NVSwitch multimem, kPathTiles = bulk-copy pipeline,
+// kPathSegments = peer-to-peer over a list of tensors (scattered calls).
 // Every path ends with the same scalar loop for what it does not cover.
-enum : int { kPathDirect = 0, kPathNvls = 1, kPathTiles = 2, kPathLocal = 3 };
+enum : int { kPathDirect = 0, kPathNvls = 1, kPathTiles = 2, kPathLocal = 3, kPathSegments = 4 };
 
 template <int OPT, typename GT, typename LPT, int PATH>
 __global__ void __launch_bounds__(512, 2)
@@ -1087,6 +1088,7 @@ __global__ void __launch_bounds__(512, 2)
     __syncthreads();
   }
   bool ok = s_ok != 0;
+  const bool started_ok = ok;
 
   // ---- slice of this rank (same arithmetic as cocoSliceBounds) -------------
   const size_t N = sa.count;
@@ -1098,6 +1100,45 @@ __global__ void __launch_bounds__(512, 2)
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nth = (size_t)gridDim.x * blockDim.x;
   const Hyper h = make_hyper<OPT>(sa);
+
+  if constexpr (PATH == kPathSegments) {
+    // Scattered call: the slice is a sequence of pieces of different tensors.
+    // The whole grid walks them one after the other; for each, the piece's
+    // pointers replace the flat call's in the shared RankArgs and the ordinary
+    // peer-to-peer loops run on it.  (SGD and Adam: elementwise, no norms.)
+    __shared__ unsigned long long s_seg[2];
+    const Segment *segs = ra.segs;
+    const int nseg = ra.nseg;
+    double unused_w2 = 0.0, unused_r2 = 0.0;
+    for (int sidx = 0; sidx < nseg && ok; ++sidx) {
+      __syncthreads();  // everyone is done with the previous piece's pointers
+      if (threadIdx.x < kMaxRanks) {
+        ra.g[threadIdx.x] = segs[sidx].g[threadIdx.x];
+        ra.out[threadIdx.x] = segs[sidx].out[threadIdx.x];
+      }
+      if (threadIdx.x == 32) {
+        ra.w = segs[sidx].w, ra.m = segs[sidx].m, ra.v = segs[sidx].v;
+        ra.aligned16 = segs[sidx].aligned16;
+        s_seg[0] = segs[sidx].begin, s_seg[1] = segs[sidx].len;
+      }
+      __syncthreads();
+      const size_t seg_lo = s_seg[0], seg_len = s_seg[1];
+      const size_t nv = ra.aligned16 ? seg_len / VEC : 0;
+      if (R == 1)
+        direct_step<OPT, GT, LPT, 1>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid, nth, unused_w2, unused_r2);
+      else if (R == 2)
+        direct_step<OPT, GT, LPT, 2>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid, nth, unused_w2, unused_r2);
+      else if (R <= 4)
+        direct_step<OPT, GT, LPT, 4>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid, nth, unused_w2, unused_r2);
+      else
+        direct_step<OPT, GT, LPT, 8>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid, nth, unused_w2, unused_r2);
+      for (size_t j = nv * VEC + tid; j < seg_len; j += nth)
+        step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, seg_lo, seg_lo + j, unused_w2, unused_r2);
+    }
+    ok = false;  // nothing is left for the flat-slice code below
+    __syncthreads();
+  }
+  const bool seg_done = PATH == kPathSegments;
 
   // Full tiles go through the bulk-copy pipeline; what is left of the slice
   // (and everything, when the slice or a pointer is not 16-byte aligned) is
@@ -1248,6 +1289,8 @@ __global__ void __launch_bounds__(512, 2)
     }
   }
 
+  if (seg_done) ok = started_ok;
+
   // ---- end barrier ----------------------------------------------------------
   if (R > 1) {
     __threadfence_system();  // this thread's peer stores before the "done" signal
@@ -1283,6 +1326,9 @@ template <int OPT, typename GT, typename LPT> KernelPtr pick_path(int path) {
     case kPathNvls: return fused_step_kernel<OPT, GT, LPT, kPathNvls>;
     case kPathTiles: return fused_step_kernel<OPT, GT, LPT, kPathTiles>;
     case kPathLocal: return fused_step_kernel<OPT, GT, LPT, kPathLocal>;
+    case kPathSegments:
+      if constexpr (OPT == kLAMB) return nullptr;  // per-tensor norms: not built
+      else return fused_step_kernel<OPT, GT, LPT, kPathSegments>;
     default: return fused_step_kernel<OPT, GT, LPT, kPathDirect>;
   }
 }
@@ -1337,7 +1383,9 @@ KernelPtr pick(int opt, cocoDataType_t g, bool has_lp, cocoDataType_t lp, int pa
 
 // The path a launch takes: NVLS when the call carries multicast addresses,
 // the tile pipeline when it was given stages, else the register-staged path.
-int path_of(const StepArgs &sa) {
+int path_of(const StepArgs &sa, const RankArgs &ra) {
+  (void)ra;
+  if (sa.flags & kFlagScattered) return kPathSegments;
   if (sa.flags & kFlagNvls) return kPathNvls;
   if (sa.pipe_stages > 0) return kPathTiles;
   return sa.world == 1 ? kPathLocal : kPathDirect;
@@ -1348,7 +1396,7 @@ int path_of(const StepArgs &sa) {
 cudaError_t launch_fused_step(int opt, cocoDataType_t g_type, bool has_lp, cocoDataType_t lp_type,
                               const StepArgs &sa, const RankArgs &one, const RankArgs *table,
                               const LaunchConfig &cfg, cudaStream_t stream) {
-  KernelPtr k = pick(opt, g_type, has_lp, lp_type, path_of(sa));
+  KernelPtr k = pick(opt, g_type, has_lp, lp_type, path_of(sa, one));
   if (!k) return cudaErrorInvalidValue;
   const dim3 grid(cfg.ctas, cfg.nvirt > 1 ? cfg.nvirt : 1, 1);
   const dim3 block(cfg.threads, 1, 1);

@@ -125,7 +125,33 @@ struct PendingCall {
   float *m = nullptr, *v = nullptr;
   StepArgs sa = {};
   cudaStream_t stream = nullptr;
+  // scattered calls: the parameters are lists of tensors
+  std::vector<const void *> sg;
+  std::vector<float *> sw;
+  std::vector<size_t> scounts;
 };
+
+// Flat layout of a list of tensors: each tensor starts at a multiple of 8
+// elements of a virtual flat buffer that is sliced over the ranks like a
+// single tensor (slice length a multiple of 8 too), so that every piece keeps
+// 16-byte alignment in the moments whatever the tensors' sizes.
+struct FlatLayout {
+  std::vector<size_t> off;
+  size_t total = 0;
+  size_t slice = 0;
+};
+FlatLayout flat_layout(const size_t *counts, size_t n, int world) {
+  FlatLayout L;
+  L.off.resize(n);
+  size_t at = 0;
+  for (size_t b = 0; b < n; ++b) {
+    L.off[b] = at;
+    at += (counts[b] + 7) / 8 * 8;
+  }
+  L.total = at;
+  L.slice = ((at + world - 1) / world + 7) / 8 * 8;
+  return L;
+}
 
 struct LocalGroup;  // ranks that live in one process
 
@@ -149,6 +175,9 @@ struct cocoComm {
   unsigned long long seq = 0;
   unsigned long long launches = 0;
   unsigned long long session = 0;  // random id shared by the ranks (names of side channels)
+  std::vector<Segment> seg_host;   // last segment table uploaded
+  Segment *seg_dev = nullptr;
+  size_t seg_cap = 0;
   int ctas_per_sm = 0;  // 0 = automatic
   int threads = 512;
   int timeout_ms = 10000;
@@ -330,7 +359,7 @@ int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
       (size_t)world * tile * dtype_size(g_type) + (opt == kSGD ? 1 : 3) * tile * 4;
   const size_t budget = (size_t)c->smem_budget_kb * 1024 / want_per_sm;
   int stages = (int)std::min<size_t>(4, budget / stage_bytes);
-  if (stages < 2 || slice < tile || !c->pipeline) stages = 0;
+  if (stages < 2 || slice < tile || !c->pipeline || (sa->flags & kFlagScattered)) stages = 0;
   sa->pipe_stages = stages;
   cfg->smem_bytes = (size_t)stages * stage_bytes;
 
@@ -354,7 +383,14 @@ int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
 }
 
 int validate(const cocoComm *c, const PendingCall &pc) {
-  if (!c || !pc.g || !pc.w) return cocoInvalidArgument;
+  if (!c) return cocoInvalidArgument;
+  if (!pc.scounts.empty()) {
+    if (pc.opt == kLAMB || pc.w_lp) return cocoInvalidArgument;  // per-tensor norms / copies: not built
+    for (size_t b = 0; b < pc.scounts.size(); ++b)
+      if (!pc.sg[b] || !pc.sw[b]) return cocoInvalidArgument;
+  } else if (!pc.g || !pc.w) {
+    return cocoInvalidArgument;
+  }
   if (dtype_size(pc.g_type) == 0) return cocoInvalidArgument;
   if (pc.w_lp && pc.lp_type != cocoFloat16 && pc.lp_type != cocoBfloat16)
     return cocoInvalidArgument;
@@ -392,6 +428,70 @@ void fill_rank_args(RankArgs *ra, int rank, int world, char *const g_views[], ch
   ra->aligned16 = (ok16 && (lo % vec) == 0) ? 1 : 0;
 }
 
+// This rank's pieces of a list of tensors.  views_g[b][p] / views_w[b][p]: rank
+// p's copy of tensor b as this rank addresses it.
+std::vector<Segment> build_segments(int rank, int world, const FlatLayout &L,
+                                    const std::vector<size_t> &counts,
+                                    const std::vector<std::vector<char *>> &views_g,
+                                    const std::vector<std::vector<char *>> &views_w, float *m,
+                                    float *v, size_t gsize) {
+  std::vector<Segment> out;
+  const size_t lo = std::min(L.total, (size_t)rank * L.slice);
+  const size_t hi = std::min(L.total, lo + L.slice);
+  for (size_t b = 0; b < counts.size(); ++b) {
+    const size_t t0 = L.off[b], t1 = L.off[b] + counts[b];
+    const size_t s0 = std::max(t0, lo), s1 = std::min(t1, hi);
+    if (s0 >= s1) continue;
+    Segment sg;
+    memset(&sg, 0, sizeof(sg));
+    bool al = true;
+    for (int p = 0; p < world; ++p) {
+      sg.g[p] = views_g[b][p];
+      sg.out[p] = views_w[b][p];
+      al = al && aligned16(views_g[b][p]) && aligned16(views_w[b][p]);
+    }
+    sg.w = (float *)views_w[b][rank];
+    sg.begin = s0 - t0;
+    sg.len = s1 - s0;
+    // element i of the tensor lives at flat index t0 + i, i.e. at m[(t0 + i) - lo];
+    // the kernel indexes m[i - begin]
+    sg.m = m ? m + (s0 - lo) : nullptr;
+    sg.v = v ? v + (s0 - lo) : nullptr;
+    al = al && (sg.begin % 8 == 0) && aligned16(sg.m) && aligned16(sg.v) && gsize != 0;
+    sg.aligned16 = al ? 1 : 0;
+    sg.tensor = (int)b;
+    out.push_back(sg);
+  }
+  return out;
+}
+
+// Puts `segs` into the communicator's device table (re-uploading only when it
+// changed) and returns the device pointer.
+int upload_segments(cocoComm *c, const std::vector<Segment> &segs, cudaStream_t stream,
+                    const Segment **dev) {
+  *dev = nullptr;
+  if (segs.empty()) return cocoSuccess;
+  if (segs.size() > c->seg_cap) {
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    if (c->seg_dev) CUDA_TRY(cudaFree(c->seg_dev));
+    c->seg_dev = nullptr;
+    c->seg_cap = std::max<size_t>(64, segs.size() * 2);
+    CUDA_TRY(cudaMalloc((void **)&c->seg_dev, c->seg_cap * sizeof(Segment)));
+    c->seg_host.clear();
+  }
+  const bool same = c->seg_host.size() == segs.size() &&
+                    memcmp(c->seg_host.data(), segs.data(), segs.size() * sizeof(Segment)) == 0;
+  if (!same) {
+    c->seg_host = segs;
+    // pageable source: staged before the call returns; ordered on the stream
+    // after the previous step's kernel, which may still be reading the table
+    CUDA_TRY(cudaMemcpyAsync(c->seg_dev, c->seg_host.data(), segs.size() * sizeof(Segment),
+                             cudaMemcpyHostToDevice, stream));
+  }
+  *dev = c->seg_dev;
+  return cocoSuccess;
+}
+
 // Launch of one rank that owns its device alone (process mode, or a
 // single-process rank with a device of its own).
 int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
@@ -400,6 +500,23 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
   fill_rank_args(&ra, c->rank, c->world, g_views, out_views, c->peer_flags, pc);
   LaunchConfig cfg;
   StepArgs sa = pc.sa;
+  if (!pc.scounts.empty()) {  // scattered: peer views per tensor, pieces of this rank's slice
+    const FlatLayout L = flat_layout(pc.scounts.data(), pc.scounts.size(), c->world);
+    std::vector<std::vector<char *>> vg(pc.scounts.size()), vw(pc.scounts.size());
+    for (size_t b = 0; b < pc.scounts.size(); ++b) {
+      vg[b].resize(kMaxRanks);
+      vw[b].resize(kMaxRanks);
+      char *mc = nullptr;
+      COCO_TRY(peer_views(c, pc.sg[b], pc.scounts[b] * dtype_size(pc.g_type), vg[b].data(), &mc));
+      COCO_TRY(peer_views(c, pc.sw[b], pc.scounts[b] * sizeof(float), vw[b].data(), &mc));
+    }
+    const std::vector<Segment> segs = build_segments(c->rank, c->world, L, pc.scounts, vg, vw, pc.m,
+                                                     pc.v, dtype_size(pc.g_type));
+    COCO_TRY(upload_segments(c, segs, pc.stream, &ra.segs));
+    ra.nseg = (int)segs.size();
+    sa.flags |= kFlagScattered;
+    mc_g = mc_out = nullptr;
+  }
   // NVLS moves (1 + 1/R) N s bytes per direction, peer-to-peer 2 (R-1)/R N s:
   // the switch wins from R = 4 on ("auto").  It needs multicast addresses for
   // both buffers, i.e. buffers registered with cocoRegisterMapped.
@@ -455,8 +572,45 @@ int flush_group(LocalGroup *grp) {
     for (size_t k = 0; k < ranks.size(); ++k)
       fill_rank_args(&host[k], ranks[k], R, g_views, out_views, flags,
                      grp->comms[ranks[k]]->pending);
+    const bool scattered = !pc0.scounts.empty();
+    if (scattered) {  // one address space: every rank's tensors are addressed directly
+      const size_t nb = pc0.scounts.size();
+      const FlatLayout L = flat_layout(pc0.scounts.data(), nb, R);
+      std::vector<std::vector<char *>> vg(nb), vw(nb);
+      bool same = true;
+      for (size_t b = 0; b < nb; ++b) {
+        vg[b].resize(kMaxRanks);
+        vw[b].resize(kMaxRanks);
+        for (int r = 0; r < R; ++r) {
+          const PendingCall &pr = grp->comms[r]->pending;
+          same = same && pr.scounts.size() == nb && pr.scounts[b] == pc0.scounts[b];
+          if (!same) break;
+          vg[b][r] = (char *)pr.sg[b];
+          vw[b][r] = (char *)pr.sw[b];
+        }
+      }
+      if (!same) {
+        result = cocoInvalidUsage;
+        break;
+      }
+      bool failed = false;
+      for (size_t k = 0; k < ranks.size() && !failed; ++k) {
+        cocoComm *ck = grp->comms[ranks[k]];
+        const std::vector<Segment> segs = build_segments(ranks[k], R, L, pc0.scounts, vg, vw,
+                                                         ck->pending.m, ck->pending.v,
+                                                         dtype_size(pc0.g_type));
+        int rc2 = upload_segments(ck, segs, pc0.stream, &host[k].segs);
+        host[k].nseg = (int)segs.size();
+        if (rc2 != cocoSuccess) {
+          result = rc2;
+          failed = true;
+        }
+      }
+      if (failed) break;
+    }
     LaunchConfig cfg;
     StepArgs sa = pc0.sa;
+    if (scattered) sa.flags |= kFlagScattered;
     int rc = pick_launch(lead, pc0.opt, pc0.g_type, pc0.w_lp != nullptr, pc0.lp_type,
                          pc0.sa.count, R, (int)ranks.size(), &sa, &cfg);
     if (rc != cocoSuccess) {
@@ -517,6 +671,7 @@ int enqueue(cocoComm *c, PendingCall &pc) {
   if (!guard.ok) return cocoCudaError;
   char *g_views[kMaxRanks] = {}, *out_views[kMaxRanks] = {};
   char *mc_g = nullptr, *mc_out = nullptr;
+  if (!pc.scounts.empty()) return launch_single(c, pc, g_views, out_views, nullptr, nullptr);
   COCO_TRY(peer_views(c, pc.g, pc.sa.count * dtype_size(pc.g_type), g_views, &mc_g));
   if (pc.w_lp)
     COCO_TRY(peer_views(c, pc.w_lp, pc.sa.count * dtype_size(pc.lp_type), out_views, &mc_out));
@@ -731,6 +886,7 @@ int cocoCommDestroy(cocoComm_t comm) {
       }
   }
   if (comm->flags) cudaFree(comm->flags);
+  if (comm->seg_dev) cudaFree(comm->seg_dev);
   (void)cudaGetLastError();
   delete comm;
   return cocoSuccess;
@@ -983,6 +1139,55 @@ int cocoFusedGenericPlan(cocoComm_t comm, const void *g, cocoDataType_t g_type, 
   plan->threads = threads;
   comm->launches++;
   return cocoSuccess;
+}
+
+int cocoScatteredSliceElems(size_t nbuff, const size_t *counts, int world, size_t *slice_elems) {
+  if (!counts || !slice_elems || world < 1 || world > kMaxRanks) return cocoInvalidArgument;
+  *slice_elems = flat_layout(counts, nbuff, world).slice;
+  return cocoSuccess;
+}
+
+static int enqueue_scattered(cocoComm_t comm, int opt, size_t nbuff, const void *const *g,
+                             cocoDataType_t g_type, float *const *w, const size_t *counts,
+                             float *m, float *v, PendingCall &pc, cocoStream_t stream) {
+  if (!comm || !g || !w || !counts || nbuff == 0) return cocoInvalidArgument;
+  pc.opt = opt;
+  pc.g_type = g_type;
+  pc.m = m, pc.v = v;
+  pc.sg.assign(g, g + nbuff);
+  pc.sw.assign(w, w + nbuff);
+  pc.scounts.assign(counts, counts + nbuff);
+  pc.g = g[0];
+  pc.w = w[0];
+  pc.sa.count = flat_layout(counts, nbuff, comm->world).total;
+  pc.stream = (cudaStream_t)stream;
+  return enqueue(comm, pc);
+}
+
+int cocoFusedSGDScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
+                          cocoDataType_t g_type, float *const *w, const size_t *counts, float lr,
+                          float grad_scale, cocoStream_t stream) {
+  PendingCall pc;
+  pc.sa.lr = lr;
+  pc.sa.grad_scale = grad_scale;
+  pc.sa.variant = cocoVariantOverlap;
+  pc.sa.d1 = pc.sa.d2 = 1.f;
+  pc.sa.d1d = pc.sa.d2d = 1.0;
+  return enqueue_scattered(comm, kSGD, nbuff, g, g_type, w, counts, nullptr, nullptr, pc, stream);
+}
+
+int cocoFusedAdamScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
+                           cocoDataType_t g_type, float *const *w, const size_t *counts, float *m,
+                           float *v, float lr, float beta1, float beta2, float eps, int step,
+                           float grad_scale, cocoVariant_t variant, cocoStream_t stream) {
+  if (step < 0 || variant == cocoVariantNccl || !m || !v) return cocoInvalidArgument;
+  PendingCall pc;
+  pc.sa.lr = lr, pc.sa.beta1 = beta1, pc.sa.beta2 = beta2;
+  pc.sa.eps = variant == cocoVariantOverlap ? eps : 0.f;
+  pc.sa.grad_scale = grad_scale;
+  pc.sa.variant = (int)variant;
+  set_denominators(&pc.sa, kAdam, step);
+  return enqueue_scattered(comm, kAdam, nbuff, g, g_type, w, counts, m, v, pc, stream);
 }
 
 int cocoLastLambNorms(cocoComm_t comm, double out[2]) {

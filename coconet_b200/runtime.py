@@ -71,6 +71,15 @@ _SIGNATURES = {
                                       C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
                                       C.c_float, C.c_float, C.c_float, C.c_int, C.c_float,
                                       C.c_void_p]),
+    "cocoScatteredSliceElems": (C.c_int, [C.c_size_t, C.POINTER(C.c_size_t), C.c_int,
+                                          C.POINTER(C.c_size_t)]),
+    "cocoFusedSGDScattered": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_int,
+                                        C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_float,
+                                        C.c_float, C.c_void_p]),
+    "cocoFusedAdamScattered": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_int,
+                                         C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_void_p,
+                                         C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_float,
+                                         C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "cocoFusedGenericPlan": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t,
                                        C.c_float, C.c_void_p, C.c_void_p]),
     "cocoLastLambNorms": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
@@ -110,6 +119,14 @@ def error_string(code):
 def _check(code, what):
     if code != 0:
         raise CocoError(code, what)
+
+
+def scattered_slice_elems(counts, world):
+    """Elements of m / v each rank holds for a list of tensors of these sizes."""
+    arr = (C.c_size_t * len(counts))(*counts)
+    out = C.c_size_t()
+    _check(lib().cocoScatteredSliceElems(len(counts), arr, world, C.byref(out)), "cocoScatteredSliceElems")
+    return out.value
 
 
 def slice_bounds(count, world, rank):
@@ -296,6 +313,27 @@ class Communicator:
         _check(lib().cocoFusedLAMB(self._h, _ptr(g), _dtype_code(g), _ptr(w), lp, lpt, _ptr(m),
                                    _ptr(v), w.numel(), lr, beta1, beta2, eps, weight_decay, step,
                                    grad_scale, variant, flags, _stream(stream)), "cocoFusedLAMB")
+
+    # ---- lists of tensors ----
+    @staticmethod
+    def _lists(gs, ws):
+        n = len(gs)
+        ga = (C.c_void_p * n)(*[t.data_ptr() for t in gs])
+        wa = (C.c_void_p * n)(*[t.data_ptr() for t in ws])
+        ca = (C.c_size_t * n)(*[t.numel() for t in ws])
+        return n, ga, wa, ca
+
+    def fused_sgd_scattered(self, gs, ws, lr, grad_scale=1.0, stream=None):
+        n, ga, wa, ca = self._lists(gs, ws)
+        _check(lib().cocoFusedSGDScattered(self._h, n, ga, _dtype_code(gs[0]), wa, ca, lr,
+                                           grad_scale, _stream(stream)), "cocoFusedSGDScattered")
+
+    def fused_adam_scattered(self, gs, ws, m, v, lr, beta1, beta2, eps, step, grad_scale=1.0,
+                             variant=VARIANT_OVERLAP, stream=None):
+        n, ga, wa, ca = self._lists(gs, ws)
+        _check(lib().cocoFusedAdamScattered(self._h, n, ga, _dtype_code(gs[0]), wa, ca, _ptr(m),
+                                            _ptr(v), lr, beta1, beta2, eps, step, grad_scale,
+                                            variant, _stream(stream)), "cocoFusedAdamScattered")
 
     # ---- introspection ----
     def status(self):

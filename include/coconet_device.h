@@ -36,6 +36,20 @@ struct FlagPage {
   double cta_part[kMaxCtasPerRank][2];
 };
 
+// One piece of a rank's slice when the parameters are a LIST of tensors
+// (scattered calls): the part of one tensor that falls into the slice.
+struct Segment {
+  const void *g[kMaxRanks];   // that tensor's gradient on every rank, element 0
+  void *out[kMaxRanks];       // that tensor's weights on every rank, element 0
+  float *w;                   // own weights of the tensor, element 0
+  float *m;                   // own moments, positioned so that [i - begin] is element i's
+  float *v;
+  unsigned long long begin;   // first element of the tensor inside the slice
+  unsigned long long len;     // number of elements
+  int aligned16;
+  int tensor;
+};
+
 // Per-rank pointers of one fused call.  Indexed tables hold the view THIS
 // rank has of every peer's buffer (entry [rank] is the rank's own buffer).
 struct RankArgs {
@@ -49,10 +63,14 @@ struct RankArgs {
   void *mc_out;               // NVLS multicast address of the gathered output, or null
   int rank;
   int aligned16;              // non-zero: slice start and all pointers are 16-byte aligned
+  const Segment *segs;        // scattered calls: this rank's segments (device memory)
+  int nseg;
+  int pad;
 };
 
 // Internal StepArgs::flags bit (public flags use the low byte).
 constexpr unsigned kFlagNvls = 0x100u;  // reduce / gather through NVSwitch multicast
+constexpr unsigned kFlagScattered = 0x200u;  // the parameters are a list of tensors (RankArgs::segs)
 
 // Scalars of one fused call, identical on every rank.
 struct StepArgs {

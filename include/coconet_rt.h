@@ -238,6 +238,28 @@ int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *w, void *w_
                         float beta1, float beta2, float eps, float weight_decay, int step,
                         float grad_scale, cocoStream_t stream);
 
+/* ---- lists of tensors ("scattered" calls) -----------------------------------
+ * Replace ncclAllReduceScatteredWeights / ...Adam of the reference's second
+ * NCCL fork (nccl-overlap/src/collectives/all_reduce.cc:21-59; kernel
+ * nccl-overlap/src/collectives/device/all_reduce_scattered.h:15-105): the
+ * parameters are nbuff separate tensors (g[b], w[b] of counts[b] elements,
+ * e.g. one per layer) instead of one flat buffer; ONE kernel per step still.
+ * The tensors form a virtual flat buffer in which tensor b starts at the next
+ * multiple of 8 elements; that buffer is sliced over the ranks like a single
+ * tensor with slices of cocoScatteredSliceElems elements, and m, v are
+ * slice-local arrays of that many fp32 elements.  Every rank passes the same
+ * list in the same order; each tensor is peer-mapped on first use.  fp32
+ * weights are gathered (no low-precision copy); peer-to-peer path.  Per-tensor
+ * LAMB (all_reduce_scattered.h:106-282) is not built. */
+int cocoScatteredSliceElems(size_t nbuff, const size_t *counts, int world, size_t *slice_elems);
+int cocoFusedSGDScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
+                          cocoDataType_t g_type, float *const *w, const size_t *counts, float lr,
+                          float grad_scale, cocoStream_t stream);
+int cocoFusedAdamScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
+                           cocoDataType_t g_type, float *const *w, const size_t *counts, float *m,
+                           float *v, float lr, float beta1, float beta2, float eps, int step,
+                           float grad_scale, cocoVariant_t variant, cocoStream_t stream);
+
 /* Prepares one fused step whose update the CALLER supplies as a device
  * functor (include/coconet_fused_generic.cuh: cocoLaunchGenericFused): peer
  * views of g and w, flag pages, sequence number and launch shape.  Collective

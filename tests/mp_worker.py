@@ -212,6 +212,50 @@ def case_symm(comm):
         print("ok symm_free_realloc", flush=True)
 
 
+def case_scattered(comm):
+    """Lists of tensors across processes: every tensor is peer-mapped over CUDA
+    IPC on first use; results per tensor against the oracle, bit for bit."""
+    R, rank = comm.world, comm.rank
+    counts = [1000, 8, 3, 4096, 70001, 2, (1 << 20) + 5, 24]
+    S = coco.scattered_slice_elems(counts, R)
+    h = K.HYPER
+    w0 = [K.make_weights(c, 800 + b) for b, c in enumerate(counts)]
+    w = [torch.from_numpy(x.copy()).cuda() for x in w0]
+    g = [torch.zeros(c, device="cuda") for c in counts]
+    m, v = torch.zeros(S, device="cuda"), torch.zeros(S, device="cuda")
+    ow = [x.copy() for x in w0]
+    om = [np.zeros(c, np.float32) for c in counts]
+    ov = [np.zeros(c, np.float32) for c in counts]
+    off, at = [], 0
+    for c in counts:
+        off.append(at)
+        at += (c + 7) // 8 * 8
+    for step in range(3):
+        grads = [K.make_grads(R, c, 900 + b, step) for b, c in enumerate(counts)]
+        for b in range(len(counts)):
+            g[b].copy_(torch.from_numpy(grads[b][rank]))
+        torch.cuda.synchronize()
+        comm.barrier()
+        comm.fused_adam_scattered(g, w, m, v, h["lr"], h["beta1"], h["beta2"], h["eps"], step)
+        torch.cuda.synchronize()
+        assert comm.status()["code"] == 0
+        mh, vh = m.cpu().numpy(), v.cpu().numpy()
+        for b, cnt in enumerate(counts):
+            O_ = __import__("oracle_lib")
+            O_.adam(ow[b], om[b], ov[b], O_.reduce_f32(grads[b]), h["lr"], h["beta1"], h["beta2"],
+                    h["eps"], step)
+            assert np.array_equal(w[b].cpu().numpy(), ow[b]), f"scattered w tensor {b} step {step}"
+            # the part of this tensor's moments that lives on this rank
+            lo, hi = rank * S, (rank + 1) * S
+            a, z = max(off[b], lo), min(off[b] + cnt, hi)
+            if a < z:
+                assert np.array_equal(mh[a - lo:z - lo], om[b][a - off[b]:z - off[b]])
+                assert np.array_equal(vh[a - lo:z - lo], ov[b][a - off[b]:z - off[b]])
+        comm.barrier()
+    if rank == 0:
+        print(f"ok scattered R={R} tensors={len(counts)}", flush=True)
+
+
 def case_timeout(comm):
     """Rank 1 skips one fused call: the others' bounded start wait must give
     up with a status, leave the weights untouched and keep the context alive."""
@@ -248,7 +292,7 @@ if __name__ == "__main__":
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     comm = coco.Communicator.init_rank(world, rank)
     try:
-        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls, "symm": case_symm}[sys.argv[1]](comm)
+        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls, "symm": case_symm, "scattered": case_scattered}[sys.argv[1]](comm)
     except Exception:  # keep this rank alive until its peers are done with its memory
         import traceback
         print("WORKER FAILURE rank %d\n%s" % (rank, traceback.format_exc()), flush=True)

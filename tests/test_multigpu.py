@@ -88,3 +88,10 @@ def test_runtime_symmetric_memory_and_multicast():
     r = _launch("symm", world)
     assert r.returncode == 0, _why(r)
     assert "ok symm_p2p" in r.stdout and "ok symm_free_realloc" in r.stdout, r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_scattered_tensor_lists_across_processes():
+    r = _launch("scattered", min(_ngpu(), 8))
+    assert r.returncode == 0, _why(r)
+    assert "ok scattered" in r.stdout, r.stdout

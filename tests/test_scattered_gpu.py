@@ -1,0 +1,117 @@
+"""Lists of tensors ("scattered" calls): one fused kernel over per-layer
+gradient and weight tensors, with flat Sliced moments.  Virtual ranks on one
+GPU; every tensor is checked against the CPU oracle run on that tensor alone,
+bit for bit (the arithmetic is the flat path's)."""
+import numpy as np
+import pytest
+import torch
+
+import cases as K
+import oracle_lib as O
+
+pytestmark = pytest.mark.gpu
+
+import coconet_b200 as coco  # noqa: E402
+
+# sizes that are not multiples of 8, tiny tensors, and one larger than a slice
+SIZES = [1000, 8, 3, 4096, 70001, 2, 1, (1 << 19) + 5, 24]
+
+
+def _layout(counts, R):
+    off, at = [], 0
+    for c in counts:
+        off.append(at)
+        at += (c + 7) // 8 * 8
+    S = ((at + R - 1) // R + 7) // 8 * 8
+    return off, at, S
+
+
+@pytest.mark.parametrize("R", [1, 2, 3, 8])
+@pytest.mark.parametrize("opt", ["sgd", "adam"])
+def test_scattered_matches_per_tensor_oracle(R, opt):
+    counts = SIZES
+    off, total, S = _layout(counts, R)
+    assert coco.scattered_slice_elems(counts, R) == S
+    comms = coco.Communicator.init_all(R, [0] * R)
+    h = K.HYPER
+    try:
+        w0 = [K.make_weights(c, 500 + b) for b, c in enumerate(counts)]
+        w = [[torch.from_numpy(x.copy()).cuda() for x in w0] for _ in range(R)]
+        m = [torch.zeros(S, device="cuda") for _ in range(R)]
+        v = [torch.zeros(S, device="cuda") for _ in range(R)]
+        ow = [x.copy() for x in w0]
+        om = [np.zeros(c, np.float32) for c in counts]
+        ov = [np.zeros(c, np.float32) for c in counts]
+        for step in range(3):
+            grads = [[K.make_grads(R, c, 600 + b, step)[r] for b, c in enumerate(counts)]
+                     for r in range(R)]
+            g = [[torch.from_numpy(x).cuda() for x in grads[r]] for r in range(R)]
+            with coco.group():
+                for r, c in enumerate(comms):
+                    if opt == "sgd":
+                        c.fused_sgd_scattered(g[r], w[r], 0.01)
+                    else:
+                        c.fused_adam_scattered(g[r], w[r], m[r], v[r], h["lr"], h["beta1"],
+                                               h["beta2"], h["eps"], step)
+            torch.cuda.synchronize()
+            for c in comms:
+                assert c.status()["code"] == 0
+            for b, cnt in enumerate(counts):
+                gsum = O.reduce_f32([grads[r][b] for r in range(R)])
+                if opt == "sgd":
+                    O.sgd(ow[b], gsum, 0.01)
+                else:
+                    O.adam(ow[b], om[b], ov[b], gsum, h["lr"], h["beta1"], h["beta2"], h["eps"], step)
+                for r in range(R):
+                    assert np.array_equal(w[r][b].cpu().numpy(), ow[b]), (step, b, r)
+            if opt == "adam":
+                flat_m = np.concatenate([x.cpu().numpy() for x in m])[:total]
+                flat_v = np.concatenate([x.cpu().numpy() for x in v])[:total]
+                for b, cnt in enumerate(counts):
+                    assert np.array_equal(flat_m[off[b]:off[b] + cnt], om[b]), (step, b)
+                    assert np.array_equal(flat_v[off[b]:off[b] + cnt], ov[b]), (step, b)
+    finally:
+        for c in comms:
+            c.destroy()
+
+
+def test_scattered_equals_flat_call_on_one_tensor():
+    # a list with a single tensor of a multiple-of-8R size is the flat call
+    R, n = 4, 1 << 18
+    comms = coco.Communicator.init_all(R, [0] * R)
+    h = K.HYPER
+    try:
+        w0 = K.make_weights(n, 7)
+        grads = K.make_grads(R, n, 7, 0)
+        g = [torch.from_numpy(x).cuda() for x in grads]
+        wa = [torch.from_numpy(w0.copy()).cuda() for _ in range(R)]
+        wb = [torch.from_numpy(w0.copy()).cuda() for _ in range(R)]
+        S = n // R
+        ma, va, mb, vb = ([torch.zeros(S, device="cuda") for _ in range(R)] for _ in range(4))
+        with coco.group():
+            for r, c in enumerate(comms):
+                c.fused_adam(g[r], wa[r], ma[r], va[r], h["lr"], h["beta1"], h["beta2"], h["eps"], 0)
+        with coco.group():
+            for r, c in enumerate(comms):
+                c.fused_adam_scattered([g[r]], [wb[r]], mb[r], vb[r], h["lr"], h["beta1"],
+                                       h["beta2"], h["eps"], 0)
+        torch.cuda.synchronize()
+        for r in range(R):
+            assert torch.equal(wa[r], wb[r]) and torch.equal(ma[r], mb[r]) and torch.equal(va[r], vb[r])
+    finally:
+        for c in comms:
+            c.destroy()
+
+
+def test_scattered_rejects_what_is_not_built():
+    c = coco.Communicator.init_all(1, [0])[0]
+    try:
+        g = [torch.zeros(16, device="cuda")]
+        w = [torch.zeros(16, device="cuda")]
+        with pytest.raises(coco.CocoError):     # moments are required
+            c.fused_adam_scattered(g, w, None, None, 1e-3, 0.9, 0.999, 1e-6, 0)
+        with pytest.raises(coco.CocoError):     # the forked-NCCL formulation is flat-only
+            c.fused_adam_scattered(g, w, w[0], w[0], 1e-3, 0.9, 0.999, 1e-6, 0,
+                                   variant=coco.VARIANT_NCCL)
+    finally:
+        c.destroy()
