@@ -162,7 +162,7 @@ def run_sweep(args, rank, world, local_rank):
     local = coco.Communicator.init_all(1, [local_rank])[0]
     R = world
     use_nvls = world > 1 and (args.algo == "nvls" or (args.algo == "auto" and world >= 4))
-    max_n = max(1 << args.sweep_max_log, COUNT)
+    max_n = max(1 << args.sweep_max_log, COUNT, 340_000_000)  # also holds the BERT-large-shaped list
     keep = []
 
     def comm_buffer(numel, dtype):
@@ -291,7 +291,7 @@ def run_sweep(args, rank, world, local_rank):
                   f"hbm {p['hbm_gbs']:7.1f} GB/s  roof {p['roof_frac']:.3f}  stock {base:9.4f} ms  "
                   f"x{p['speedup']:.2f}" + (f"  back-to-back {b2b * 1e3:7.1f} us" if b2b else ""), flush=True)
     # ---- a list of tensors shaped like BERT-large (24 layers, hidden 1024, FFN 4096,
-    # vocabulary 30522, 512 positions: 391 tensors, 335 M elements) through the scattered
+    # vocabulary 30522, 512 positions: 398 tensors, 336 M elements) through the scattered
     # call, next to the flat call on the same number of elements
     shapes = [30522 * 1024, 512 * 1024, 2 * 1024, 1024, 1024]
     for _ in range(24):
@@ -313,8 +313,10 @@ def run_sweep(args, rank, world, local_rank):
                 comm.fused_adam_scattered(gl, wl, msc, vsc, HYPER["lr"], HYPER["beta1"],
                                           HYPER["beta2"], HYPER["eps"], i)
 
+            tot_f = tot // (8 * R) * (8 * R)   # keeps every rank's flat slice 16-byte aligned
+
             def flat(i):
-                comm.fused_adam(g32[:tot], w32[:tot], m[:(tot + R - 1) // R], v[:(tot + R - 1) // R],
+                comm.fused_adam(g32[:tot_f], w32[:tot_f], m[:tot_f // R], v[:tot_f // R],
                                 HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"], i)
 
             ms_sc, ms_fl = time_ms(scattered, 5, 3), time_ms(flat, 5, 3)

@@ -1110,7 +1110,18 @@ __global__ void __launch_bounds__(512, 2)
     const Segment *segs = ra.segs;
     const int nseg = ra.nseg;
     double unused_w2 = 0.0, unused_r2 = 0.0;
+    // Small pieces (biases, layer norms) are taken by ONE CTA each, round robin,
+    // so that they proceed side by side instead of every CTA walking every
+    // tiny piece; large pieces are shared by the whole grid.
+    const unsigned long long small = 64ull * blockDim.x;
     for (int sidx = 0; sidx < nseg && ok; ++sidx) {
+      const bool solo = segs[sidx].len < small;
+      if (solo && (unsigned)sidx % gridDim.x != blockIdx.x) continue;  // uniform per CTA
+      // Shared pieces start at a different CTA each time: a piece rarely is a whole
+      // number of grid passes, and without the rotation the same CTAs would always
+      // get the extra pass.
+      const size_t tid_s = solo ? threadIdx.x : (tid + (size_t)sidx * 37u * blockDim.x) % nth;
+      const size_t nth_s = solo ? blockDim.x : nth;
       __syncthreads();  // everyone is done with the previous piece's pointers
       if (threadIdx.x < kMaxRanks) {
         ra.g[threadIdx.x] = segs[sidx].g[threadIdx.x];
@@ -1125,14 +1136,14 @@ __global__ void __launch_bounds__(512, 2)
       const size_t seg_lo = s_seg[0], seg_len = s_seg[1];
       const size_t nv = ra.aligned16 ? seg_len / VEC : 0;
       if (R == 1)
-        direct_step<OPT, GT, LPT, 1>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid, nth, unused_w2, unused_r2);
+        direct_step<OPT, GT, LPT, 1>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, unused_w2, unused_r2);
       else if (R == 2)
-        direct_step<OPT, GT, LPT, 2>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid, nth, unused_w2, unused_r2);
+        direct_step<OPT, GT, LPT, 2>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, unused_w2, unused_r2);
       else if (R <= 4)
-        direct_step<OPT, GT, LPT, 4>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid, nth, unused_w2, unused_r2);
+        direct_step<OPT, GT, LPT, 4>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, unused_w2, unused_r2);
       else
-        direct_step<OPT, GT, LPT, 8>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid, nth, unused_w2, unused_r2);
-      for (size_t j = nv * VEC + tid; j < seg_len; j += nth)
+        direct_step<OPT, GT, LPT, 8>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, unused_w2, unused_r2);
+      for (size_t j = nv * VEC + tid_s; j < seg_len; j += nth_s)
         step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, seg_lo, seg_lo + j, unused_w2, unused_r2);
     }
     ok = false;  // nothing is left for the flat-slice code below
