@@ -166,6 +166,24 @@ template <class T> static __global__ void coconetFinishNorm(const double *acc, T
   *out = (T)(float)sqrt(*acc);
 }
 
+// *acc (a device double) becomes the sum of the ranks' values: 8 bytes per rank
+// through the runtime's host all-gather.  Used by Norm over a Sliced operand in
+// the unfused schedules.
+static inline void coconetSumOverRanks(cocoComm_t comm, double *acc, cudaStream_t stream) {
+  int world = 1;
+  COCOCHECK(cocoCommCount(comm, &world));
+  if (world == 1) return;
+  double mine = 0.0;
+  CUDACHECK(cudaMemcpyAsync(&mine, acc, sizeof(double), cudaMemcpyDeviceToHost, stream));
+  CUDACHECK(cudaStreamSynchronize(stream));
+  std::vector<double> all(world);
+  COCOCHECK(cocoAllGatherHost(comm, &mine, all.data(), sizeof(double)));
+  double sum = 0.0;
+  for (int r = 0; r < world; r++) sum += all[r];
+  CUDACHECK(cudaMemcpyAsync(acc, &sum, sizeof(double), cudaMemcpyHostToDevice, stream));
+  CUDACHECK(cudaStreamSynchronize(stream));
+}
+
 // Device-side failures (a bounded wait that expired) surface here.
 static inline void coconetCheckStatus(cocoComm_t comm, int rank) {
   cocoStatus_t st;

@@ -80,6 +80,9 @@ _SIGNATURES = {
                                          C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_void_p,
                                          C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_float,
                                          C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "cocoAllReduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cocoReduceScatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cocoAllGather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cocoFusedGenericPlan": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t,
                                        C.c_float, C.c_void_p, C.c_void_p]),
     "cocoLastLambNorms": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
@@ -313,6 +316,18 @@ class Communicator:
         _check(lib().cocoFusedLAMB(self._h, _ptr(g), _dtype_code(g), _ptr(w), lp, lpt, _ptr(m),
                                    _ptr(v), w.numel(), lr, beta1, beta2, eps, weight_decay, step,
                                    grad_scale, variant, flags, _stream(stream)), "cocoFusedLAMB")
+
+    # ---- stand-alone collectives (fp32 sum; count = total elements) ----
+    def all_reduce(self, buf, stream=None):
+        _check(lib().cocoAllReduce(self._h, _ptr(buf), buf.numel(), _stream(stream)), "cocoAllReduce")
+
+    def reduce_scatter(self, send, recv, stream=None):
+        _check(lib().cocoReduceScatter(self._h, _ptr(send), _ptr(recv), send.numel(), _stream(stream)),
+               "cocoReduceScatter")
+
+    def all_gather(self, send, recv, stream=None):
+        _check(lib().cocoAllGather(self._h, _ptr(send), _ptr(recv), recv.numel(), _stream(stream)),
+               "cocoAllGather")
 
     # ---- lists of tensors ----
     @staticmethod

@@ -71,6 +71,8 @@ struct RankArgs {
 // Internal StepArgs::flags bit (public flags use the low byte).
 constexpr unsigned kFlagNvls = 0x100u;  // reduce / gather through NVSwitch multicast
 constexpr unsigned kFlagScattered = 0x200u;  // the parameters are a list of tensors (RankArgs::segs)
+constexpr unsigned kFlagNoGather = 0x400u;   // generic kernel: do not store the result to the ranks
+constexpr unsigned kFlagNoReduce = 0x800u;   // generic kernel: do not read the ranks' gradients
 
 // Scalars of one fused call, identical on every rank.
 struct StepArgs {

@@ -88,7 +88,7 @@ __device__ __forceinline__ void st_sys_f(float *p, float v) {
 }
 
 // false if the flag did not reach seq within the time limit (or 2^28 probes)
-__device__ __noinline__ bool wait_flag(const unsigned long long *flag, unsigned long long seq,
+static __device__ __noinline__ bool wait_flag(const unsigned long long *flag, unsigned long long seq,
                                        unsigned long long timeout_ns) {
   if (ld_acquire(flag) >= seq) return true;
   const unsigned long long t0 = timer_ns();
@@ -102,7 +102,7 @@ __device__ __noinline__ bool wait_flag(const unsigned long long *flag, unsigned 
   return false;
 }
 
-__device__ __noinline__ void record(coco::FlagPage *me, int code, int rank, int phase, int peer,
+static __device__ __noinline__ void record(coco::FlagPage *me, int code, int rank, int phase, int peer,
                                     unsigned long long seq) {
   if (atomicCAS(&me->status[0], 0, code) == 0) {
     me->status[1] = rank;
@@ -186,16 +186,22 @@ __global__ void __launch_bounds__(512, 2)
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nth = (size_t)gridDim.x * blockDim.x;
   const size_t nvec = ra.aligned16 ? L / 4 : 0;
+  // The stand-alone collectives of the library are this kernel with one half
+  // switched off: a reduce-scatter does not store to the ranks, an all-gather
+  // does not read from them.
+  const bool reduce = (sa.flags & coco::kFlagNoReduce) == 0;
+  const bool gather = (sa.flags & coco::kFlagNoGather) == 0;
+  const int Rr = reduce ? R : 0, Rw = gather ? R : 0;
   if (ok) {
     for (size_t u = tid; u < nvec; u += nth) {
       const size_t j = u * 4, gi = lo + j;
       float g[4] = {0.f, 0.f, 0.f, 0.f}, x[coco::kMaxRanks][4];
 #pragma unroll
       for (int p = 0; p < coco::kMaxRanks; ++p)
-        if (p < R) Grad<GT>::load4(ra.g[p], gi, x[p]);
+        if (p < Rr) Grad<GT>::load4(ra.g[p], gi, x[p]);
 #pragma unroll
       for (int p = 0; p < coco::kMaxRanks; ++p)
-        if (p < R) {
+        if (p < Rr) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) g[e] = p == 0 ? x[0][e] : __fadd_rn(g[e], x[p][e]);
         }
@@ -207,17 +213,17 @@ __global__ void __launch_bounds__(512, 2)
       o.w = f(j + 3, gi + 3, __fmul_rn(g[3], sa.grad_scale), w4.w);
 #pragma unroll
       for (int p = 0; p < coco::kMaxRanks; ++p)
-        if (p < R) st_sys_f4((float *)ra.out[p] + gi, o);
+        if (p < Rw) st_sys_f4((float *)ra.out[p] + gi, o);
     }
     for (size_t j = nvec * 4 + tid; j < L; j += nth) {
       const size_t gi = lo + j;
       float g = 0.f;
-      for (int p = 0; p < R; ++p) {
+      for (int p = 0; p < Rr; ++p) {
         const float x = Grad<GT>::load1(ra.g[p], gi);
         g = p == 0 ? x : __fadd_rn(g, x);
       }
       const float o = f(j, gi, __fmul_rn(g, sa.grad_scale), ra.w[gi]);
-      for (int p = 0; p < R; ++p) st_sys_f((float *)ra.out[p] + gi, o);
+      for (int p = 0; p < Rw; ++p) st_sys_f((float *)ra.out[p] + gi, o);
     }
   }
 

@@ -260,6 +260,22 @@ int cocoFusedAdamScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
                            float *v, float lr, float beta1, float beta2, float eps, int step,
                            float grad_scale, cocoVariant_t variant, cocoStream_t stream);
 
+/* ---- stand-alone collectives (fp32, sum) ------------------------------------
+ * What the unfused schedules of a generated program call where the reference
+ * emits ncclAllReduce / ncclReduceScatter / ncclAllGather
+ * (src/codegen.cpp:4146-4189), on the runtime's own peer memory: `count` is the
+ * TOTAL element count N; slices are those of cocoSliceBounds.
+ *   cocoAllReduce      buf[0..N) on every rank becomes the sum over ranks
+ *   cocoReduceScatter  recv[0..S_r) = sum over ranks of send[lo_r .. hi_r)
+ *   cocoAllGather      recv[lo_r .. hi_r) on every rank = rank r's send[0..S_r)
+ * Buffers that peers touch (buf; send of a reduce-scatter; recv of an
+ * all-gather) are peer-mapped on first use like the fused calls' buffers. */
+int cocoAllReduce(cocoComm_t comm, float *buf, size_t count, cocoStream_t stream);
+int cocoReduceScatter(cocoComm_t comm, const float *send, float *recv, size_t count,
+                      cocoStream_t stream);
+int cocoAllGather(cocoComm_t comm, const float *send, float *recv, size_t count,
+                  cocoStream_t stream);
+
 /* Prepares one fused step whose update the CALLER supplies as a device
  * functor (include/coconet_fused_generic.cuh: cocoLaunchGenericFused): peer
  * views of g and w, flag pages, sequence number and launch shape.  Collective

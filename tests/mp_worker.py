@@ -256,6 +256,38 @@ def case_scattered(comm):
         print(f"ok scattered R={R} tensors={len(counts)}", flush=True)
 
 
+def case_collectives(comm):
+    """cocoAllReduce / cocoReduceScatter / cocoAllGather against numpy, sums in
+    rank order (bit-exact), aligned and ragged sizes."""
+    R, rank = comm.world, comm.rank
+    for n in (1 << 20, 100003, 5):
+        xs = [np.random.default_rng((n, r)).standard_normal(n).astype(np.float32) for r in range(R)]
+        want = xs[0].copy()
+        for r in range(1, R):
+            want = want + xs[r]
+        lo, hi = K.slice_bounds(n, R, rank)
+        S = (n + R - 1) // R
+        buf = torch.from_numpy(xs[rank].copy()).cuda()
+        comm.all_reduce(buf)
+        torch.cuda.synchronize()
+        assert np.array_equal(buf.cpu().numpy(), want), f"all_reduce n={n}"
+        send = torch.from_numpy(xs[rank].copy()).cuda()
+        recv = torch.zeros(S, device="cuda")
+        comm.barrier()
+        comm.reduce_scatter(send, recv)
+        torch.cuda.synchronize()
+        assert np.array_equal(recv.cpu().numpy()[: hi - lo], want[lo:hi]), f"reduce_scatter n={n}"
+        full = torch.zeros(n, device="cuda")
+        comm.barrier()
+        comm.all_gather(recv, full)
+        torch.cuda.synchronize()
+        assert np.array_equal(full.cpu().numpy(), want), f"all_gather n={n}"
+        assert comm.status()["code"] == 0
+        comm.barrier()
+    if rank == 0:
+        print(f"ok collectives R={R}", flush=True)
+
+
 def case_timeout(comm):
     """Rank 1 skips one fused call: the others' bounded start wait must give
     up with a status, leave the weights untouched and keep the context alive."""
@@ -292,7 +324,7 @@ if __name__ == "__main__":
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     comm = coco.Communicator.init_rank(world, rank)
     try:
-        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls, "symm": case_symm, "scattered": case_scattered}[sys.argv[1]](comm)
+        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls, "symm": case_symm, "scattered": case_scattered, "collectives": case_collectives}[sys.argv[1]](comm)
     except Exception:  # keep this rank alive until its peers are done with its memory
         import traceback
         print("WORKER FAILURE rank %d\n%s" % (rank, traceback.format_exc()), flush=True)

@@ -48,11 +48,12 @@ def test_unfused_schedules_emit_stock_collectives_and_kernels(dsl_build, tmp_pat
     text = _gen(dsl_build, opt, schedule, tmp_path)
     assert "cocoFused" not in text
     assert "__global__ void binOpFunc0" in text
+    assert "nccl" not in text                      # the runtime's own collectives: no NCCL, no MPI
     if schedule == "AR_C":
-        assert "ncclAllReduce(g, g, N, ncclFloat32, ncclSum, nccl, stream)" in text
+        assert "cocoAllReduce(comm, g, N, stream)" in text
     else:
-        assert "ncclReduceScatter(g, g + (size_t)DIVUP(N, comm_size) * rank" in text
-        assert "ncclAllGather(" in text
+        assert "cocoReduceScatter(comm, g, g + (size_t)DIVUP(N, comm_size) * rank, N, stream)" in text
+        assert "cocoAllGather(comm, " in text
         assert "m[i0]" in text or opt == "sgd"     # Sliced state is indexed from the slice start
     if opt == "lamb":
         assert text.count("coconetSumSquares<<<") == 2

@@ -28,3 +28,15 @@ def test_emitted_program_runs_and_checks_world_1(tmp_path, opt, schedule):
     assert [int(a) for a, _ in lines] == [1 << k for k in range(10, 17)]
     if schedule == "fuse_RS_C_AG":
         assert "FusedAllReduce:" in r.stdout
+
+
+def test_measuring_autotuner_ranks_the_schedules():
+    from coconet_b200.dsl.autotune import autotune
+    res = autotune("adam", gpus=1, log2=22, epochs=5,
+                   scalars={"beta1": 0.9, "beta2": 0.999, "lr": 0.01})
+    assert [r["schedule"] for r in res["results"]] == ["AR_C", "RS_C_AG", "fuse_RS_C_AG"]
+    assert all(r["ms_per_step"] > 0 for r in res["results"])
+    assert res["best"] in ("AR_C", "RS_C_AG", "fuse_RS_C_AG")
+    # the fused schedule is one stage; the unfused ones report their collectives too
+    assert list(res["results"][2]["stages_ms"]) == ["FusedAllReduce"]
+    assert "AllReduce" in res["results"][0]["stages_ms"]

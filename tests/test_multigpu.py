@@ -62,7 +62,8 @@ def test_nvls_multicast_path():
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
 @pytest.mark.parametrize("opt,schedule", [("adam", "fuse_RS_C_AG"), ("lamb", "fuse_RS_C_AG"),
-                                          ("sgd", "RS_C_AG"), ("nesterov", "fuse_RS_C_AG")])
+                                          ("sgd", "RS_C_AG"), ("nesterov", "fuse_RS_C_AG"),
+                                          ("lamb", "RS_C_AG"), ("adam", "AR_C")])
 def test_emitted_program_multi_rank(tmp_path, opt, schedule):
     """A DSL-emitted C++ program, one process per GPU, started without MPI."""
     import dsl_build_util as B
@@ -95,3 +96,10 @@ def test_scattered_tensor_lists_across_processes():
     r = _launch("scattered", min(_ngpu(), 8))
     assert r.returncode == 0, _why(r)
     assert "ok scattered" in r.stdout, r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_stand_alone_collectives():
+    r = _launch("collectives", min(_ngpu(), 8))
+    assert r.returncode == 0, _why(r)
+    assert "ok collectives" in r.stdout, r.stdout
