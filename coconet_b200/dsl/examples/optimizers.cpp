@@ -96,6 +96,50 @@ static void lamb(const std::string &schedule, const std::string &out) {
   pipeline.codegen(out);
 }
 
+// Adam written ONCE, as AllReduce + update on every element, and then scheduled
+// with CoCoNet's transformations instead of being rewritten by hand:
+//   split    AllReduce -> ReduceScatter + AllGather
+//   reorder  the update moves below the AllGather and runs on the slice
+//   asSlice  the moments are kept as Sliced tensors
+//   fuse     everything into one kernel
+// `schedule` selects how far the derivation goes.
+static void adam_derived(const std::string &schedule, const std::string &out) {
+  Variable N(Int32, "N");
+  Variable lr(Float32, "lr"), beta1(Float32, "beta1"), beta2(Float32, "beta2");
+  Tensor g(Float32, N, Local, "g");
+  Tensor w(Float32, N, Replicated, "w");
+  Tensor m(Float32, N, Replicated, "m");
+  Tensor v(Float32, N, Replicated, "v");
+  Stage gsum = AllReduce(Summation, g);
+  Stage mnew = Update(m, beta1 * m + (1 - beta1) * gsum);
+  Stage vnew = Update(v, beta2 * v + (1 - beta2) * gsum * gsum);
+  Stage mhat = mnew / beta1;
+  Stage vhat = vnew / beta2;
+  Stage wnew = Update(w, w - lr * mhat / vhat);
+  Pipeline pipeline("adam", {g, w, m, v, lr, beta1, beta2}, {mnew, vnew, wnew});
+  if (schedule == "AR_C") {
+    pipeline.fuse({mnew, vnew, mhat, vhat, wnew});
+    pipeline.codegen(out);
+    return;
+  }
+  std::pair<Stage, Stage> rsag = pipeline.split(gsum, AllReduceRSAG);
+  ReorderedStages re = pipeline.reorder({mnew, vnew, mhat, vhat, wnew}, rsag.second);
+  pipeline.asSlice({m, v});
+  if (schedule == "fuse_RS_C_AG") {
+    std::vector<Stage> all = {rsag.first};
+    all.insert(all.end(), re.compStages.begin(), re.compStages.end());
+    all.insert(all.end(), re.allGatherStages.begin(), re.allGatherStages.end());
+    pipeline.fuse(all);
+  } else {
+    // after asSlice the two moment updates are plain slice computations again
+    std::vector<Stage> comp = re.compStages;
+    comp.push_back(mnew);
+    comp.push_back(vnew);
+    pipeline.fuse(comp);
+  }
+  pipeline.codegen(out);
+}
+
 // SGD with Nesterov momentum: not one of the rules the runtime ships a kernel
 // for, so the fused schedule compiles its arithmetic into a device functor for
 // the generic fused kernel (include/coconet_fused_generic.cuh).
@@ -142,6 +186,7 @@ int main(int argc, char **argv) {
   else if (opt == "adam") adam(schedule, out);
   else if (opt == "lamb") lamb(schedule, out);
   else if (opt == "nesterov") nesterov(schedule, out);
+  else if (opt == "adam_derived") adam_derived(schedule, out);
   else { std::cout << "Invalid optimizer" << std::endl; return 1; }
   return 0;
 }

@@ -107,4 +107,13 @@ Expression Broadcast(const Expression &x, int root);
 // tensor implies an AllGather (reference: src/ast.hpp:966-968).
 Expression Update(const Tensor &target, const Expression &value);
 
+namespace detail {
+// Recomputes type-independent attributes (layout, scalar) of a node from its
+// operands after a schedule transformation rewired them.
+void relayout(Node &n);
+// A fresh stage node (gets the next S<k> name).
+NodeRef makeStage(NodeKind kind, const std::vector<NodeRef> &in, TensorElemType type,
+                  TensorLayout layout);
+}  // namespace detail
+
 }  // namespace ACCCDSL

@@ -21,6 +21,14 @@ struct FusedUpdate {
   std::string lr, beta1, beta2, decay;        // Variable names
 };
 
+// Schedule transformations (surface of the reference's src/pipeline.hpp:51-54,
+// 76-79, 552-558).
+enum SplitType { AllReduceRSAG, AllReduceBR };
+struct ReorderedStages {
+  std::vector<Stage> compStages;       // the computations, now on slices
+  std::vector<Stage> allGatherStages;  // one AllGather per Replicated tensor they update
+};
+
 class Pipeline {
  public:
   Pipeline(const std::string &name, std::initializer_list<Expression> args,
@@ -32,8 +40,23 @@ class Pipeline {
   // group contains ReduceScatter/AllGather).  Aborts with a message if the
   // stages are not part of the pipeline or the fusion would create a cycle.
   void fuse(std::initializer_list<Stage> stages);
+  void fuse(const std::vector<Stage> &stages);
   // Non-aborting form of the same check.
   bool canFuse(const std::vector<NodeRef> &stages, std::string *why = nullptr) const;
+
+  // ---- schedule transformations: AR_C -> RS_C_AG -> fused, without rewriting the program ----
+  // split(AllReduceRSAG): the AllReduce stage becomes ReduceScatter + AllGather.
+  // Returns {reduce-scatter stage, all-gather stage}; the all-gather stage IS
+  // the handle that was passed in (stages that used it keep working).
+  std::pair<Stage, Stage> split(Stage allReduce, SplitType type);
+  // reorder: move `allGather` below the pointwise stages `comps` that consume
+  // it, so that they compute on the rank's slice only; every Replicated tensor
+  // they update gets an AllGather of its own.
+  ReorderedStages reorder(std::vector<Stage> comps, Stage allGather);
+  // asSlice: keep a Replicated tensor (optimizer state) as a Sliced one; the
+  // AllGather that fed its Update disappears.
+  void asSlice(Tensor replicated);
+  void asSlice(std::vector<Tensor> replicated);
 
   // Emit the CUDA host program.
   void codegen(const std::string &filename);
@@ -54,6 +77,7 @@ class Pipeline {
   std::vector<NodeRef> outputs_;
   std::vector<NodeRef> stages_;
   std::vector<std::set<const Node *>> fused_;
+  void rediscover();  // recompute stages_ after a transformation
 };
 
 }  // namespace ACCCDSL

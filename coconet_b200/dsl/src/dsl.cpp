@@ -244,4 +244,38 @@ Expression Update(const Tensor &target, const Expression &value) {
   return Expression(n);
 }
 
+namespace detail {
+
+void relayout(Node &n) {
+  switch (n.kind) {
+    case NodeKind::Binary:
+      n.scalar = n.in[0]->scalar && n.in[1]->scalar;
+      n.layout = combine(*n.in[0], *n.in[1]);
+      break;
+    case NodeKind::Sqrt:
+    case NodeKind::Cast:
+      n.scalar = n.in[0]->scalar;
+      n.layout = n.in[0]->layout;
+      break;
+    case NodeKind::Update:
+      n.layout = n.in[0]->layout;
+      break;
+    default:
+      break;
+  }
+}
+
+NodeRef makeStage(NodeKind kind, const std::vector<NodeRef> &in, TensorElemType type,
+                  TensorLayout layout) {
+  NodeRef n = make(kind);
+  n->in = in;
+  n->type = type;
+  n->layout = layout;
+  n->stage_id = g_next_stage++;
+  n->name = "S" + std::to_string(n->stage_id);
+  return n;
+}
+
+}  // namespace detail
+
 }  // namespace ACCCDSL

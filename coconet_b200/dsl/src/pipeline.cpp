@@ -50,6 +50,11 @@ Pipeline::Pipeline(const std::string &name, std::initializer_list<Expression> ar
   for (const Stage &s : outputs) outputs_.push_back(s.node());
   if (outputs_.empty()) fail("pipeline '" + name + "' has no outputs");
 
+  rediscover();
+}
+
+void Pipeline::rediscover() {
+  stages_.clear();
   // post-order DFS from the outputs = a topological order of the stages
   std::set<const Node *> seen;
   std::function<void(const NodeRef &)> visit = [&](const NodeRef &n) {
@@ -111,7 +116,9 @@ bool Pipeline::canFuse(const std::vector<NodeRef> &stages, std::string *why) con
   return true;
 }
 
-void Pipeline::fuse(std::initializer_list<Stage> stages) {
+void Pipeline::fuse(std::initializer_list<Stage> stages) { fuse(std::vector<Stage>(stages)); }
+
+void Pipeline::fuse(const std::vector<Stage> &stages) {
   std::vector<NodeRef> v;
   for (const Stage &s : stages) v.push_back(s.node());
   std::string why;
@@ -352,6 +359,146 @@ FusedUpdate Pipeline::classify(const std::vector<NodeRef> &group) const {
       }
   }
   return fu;
+}
+
+// ---------------------------------------------------------------------------
+// Schedule transformations.  Nodes are rewired IN PLACE, so the Stage handles
+// the program holds stay valid.  (Reference: src/pipeline.cpp:851-902 split,
+// 661-843 reorder, 471-587 asSlice.)
+// ---------------------------------------------------------------------------
+std::pair<Stage, Stage> Pipeline::split(Stage allReduce, SplitType type) {
+  NodeRef ar = allReduce.node();
+  if (type != AllReduceRSAG) fail("split: only AllReduceRSAG is implemented");
+  if (!ar || ar->kind != NodeKind::AllReduce) fail("split: not an AllReduce stage");
+  if (std::find(stages_.begin(), stages_.end(), ar) == stages_.end())
+    fail("split: stage " + ar->name + " is not part of pipeline '" + name_ + "'");
+  NodeRef rs = detail::makeStage(NodeKind::ReduceScatter, {ar->in[0]}, ar->type, Sliced);
+  rs->red = ar->red;
+  ar->kind = NodeKind::AllGather;  // same node, same handle: now gathers the scattered sum
+  ar->in = {rs};
+  ar->layout = Replicated;
+  rediscover();
+  return {Stage(Expression(rs)), Stage(Expression(ar))};
+}
+
+namespace {
+
+// Replace every use of `from` inside the expression owned by stage `s`.
+void substitute(const NodeRef &n, const NodeRef &from, const NodeRef &to, bool root) {
+  if (!root && n->stage_id >= 0) return;
+  for (NodeRef &c : n->in) {
+    if (c.get() == from.get()) c = to;
+    else substitute(c, from, to, false);
+  }
+  detail::relayout(*n);
+}
+
+}  // namespace
+
+ReorderedStages Pipeline::reorder(std::vector<Stage> comps, Stage allGather) {
+  NodeRef ag = allGather.node();
+  if (!ag || ag->kind != NodeKind::AllGather) fail("reorder: the second argument must be an AllGather stage");
+  const NodeRef sliced = ag->in[0];
+  ReorderedStages out;
+  std::set<const Node *> members;
+  for (const Stage &c : comps) members.insert(c.node().get());
+  // every consumer of the AllGather must move below it, or it would still need the gathered value
+  for (const NodeRef &s : stages_) {
+    if (members.count(s.get()) || s.get() == ag.get()) continue;
+    std::vector<const Node *> d;
+    direct_deps(s, true, &d);
+    if (std::find(d.begin(), d.end(), ag.get()) != d.end())
+      fail("reorder: stage " + s->name + " also uses the AllGather but is not among the reordered stages");
+  }
+  // What the moved stages read instead: the scattered value for the gathered
+  // one, and, for an Update that now gathers, the slice it computed (on the
+  // slice both hold the same numbers).
+  std::vector<std::pair<NodeRef, NodeRef>> subs = {{ag, sliced}};
+  // in topological order, so that a stage sees its producers already sliced
+  for (const NodeRef &s : std::vector<NodeRef>(stages_)) {
+    if (!members.count(s.get())) continue;
+    std::vector<NodeRef> own;
+    ownedNodes(s, true, &own);
+    for (const NodeRef &n : own)
+      if (isCollective(n->kind) || n->kind == NodeKind::Norm)
+        fail("reorder: stage " + s->name + " is not pointwise");
+    for (const auto &sub : subs) substitute(s, sub.first, sub.second, true);
+    if (s->kind == NodeKind::Update && s->in[0]->layout == Replicated && s->in[1]->layout == Sliced) {
+      // Update(w, f(gathered)) -> c = f(slice); Update(w, AllGather(c))
+      NodeRef comp = s->in[1];
+      if (comp->stage_id < 0) {  // an unnamed expression: give the sliced computation a stage of its own
+        NodeRef named = detail::makeStage(comp->kind, comp->in, comp->type, comp->layout);
+        named->op = comp->op, named->value = comp->value, named->scalar = comp->scalar;
+        named->red = comp->red;
+        comp = named;
+      }
+      NodeRef gather = std::make_shared<Node>();
+      gather->kind = NodeKind::AllGather;
+      gather->in = {comp};
+      gather->type = comp->type;
+      gather->layout = Replicated;
+      s->in[1] = gather;
+      s->layout = Replicated;
+      subs.push_back({s, comp});
+      out.compStages.push_back(Stage(Expression(comp)));
+      out.allGatherStages.push_back(Stage(Expression(s)));
+    } else {
+      out.compStages.push_back(Stage(Expression(s)));
+    }
+  }
+  rediscover();
+  return out;
+}
+
+void Pipeline::asSlice(Tensor replicated) { asSlice(std::vector<Tensor>{replicated}); }
+
+void Pipeline::asSlice(std::vector<Tensor> tensors) {
+  for (const Tensor &t : tensors) {
+    NodeRef tn = t.node();
+    if (tn->kind != NodeKind::Tensor || tn->layout != Replicated)
+      fail("asSlice: '" + tn->name + "' is not a Replicated tensor");
+    // every use must already be on slices: a stage that needs the whole tensor forbids it
+    for (const NodeRef &s : stages_) {
+      std::vector<NodeRef> own;
+      ownedNodes(s, true, &own);
+      for (const NodeRef &n : own) {
+        bool uses = false;
+        for (const NodeRef &c : n->in) uses = uses || c.get() == tn.get();
+        if (!uses) continue;
+        if (n->kind == NodeKind::Update && n->in[0].get() == tn.get()) continue;  // handled below
+        if (n->kind == NodeKind::Norm || isCollective(n->kind))
+          fail("asSlice: '" + tn->name + "' is used whole by stage " + s->name);
+        // a Replicated sub-expression inside a stage that works on the slice is
+        // only ever evaluated at the slice's elements: the stage's layout decides
+        if (s->layout != Sliced && !(n->kind == NodeKind::Scatter))
+          fail("asSlice: stage " + s->name + " still computes on all of '" + tn->name +
+               "'; reorder it below the AllGather first");
+      }
+    }
+    tn->layout = Sliced;
+    for (const NodeRef &s : stages_) {
+      std::vector<NodeRef> own;
+      ownedNodes(s, true, &own);
+      for (const NodeRef &n : own) {
+        if (n->kind == NodeKind::Update && n->in[0].get() == tn.get()) {
+          if (n->in[1]->kind == NodeKind::AllGather) n->in[1] = n->in[1]->in[0];  // no gather needed
+          n->layout = Sliced;
+        } else if (n->kind == NodeKind::Scatter && n->in[0].get() == tn.get()) {
+          // Scatter of a tensor that is already Sliced is the tensor itself
+          n->kind = NodeKind::Cast;
+          n->type = tn->type;
+          n->layout = Sliced;
+        } else {
+          detail::relayout(*n);
+          if (n->kind == NodeKind::Update && n->in[0]->layout == Replicated && n->in[1]->layout == Sliced &&
+              n->in[1]->kind != NodeKind::AllGather)
+            fail("asSlice: stage " + s->name + " would update Replicated '" + n->in[0]->name +
+                 "' from a slice without an AllGather; reorder it below the AllGather first");
+        }
+      }
+    }
+  }
+  rediscover();
 }
 
 void Pipeline::print(std::ostream &os) const {

@@ -144,3 +144,85 @@ int main() {
     r = subprocess.run([exe], cwd=tmp_path, capture_output=True, text=True)
     assert r.returncode == 2 and "is not a ReduceScatter -> SGD | Adam | LAMB" in r.stderr
     assert "it contains a Norm" in r.stderr
+
+
+ADAM_CALL = ("cocoFusedAdam(comm, g, cocoFloat32, w, NULL, cocoFloat16, m, v, N, lr, beta1, beta2, "
+             "0.0f, iter, 1.0f, cocoVariantDsl, stream)")
+
+
+def test_schedules_derived_by_split_reorder_asslice(dsl_build, tmp_path):
+    """One Adam program written as AllReduce + computation; the other two
+    schedules are derived from it (reference: src/pipeline.cpp:851-902 split,
+    661-843 reorder, 471-587 asSlice) and must emit what the hand-written
+    schedules emit."""
+    ar = _gen(dsl_build, "adam_derived", "AR_C", tmp_path)
+    assert "cocoAllReduce(comm, g, N, stream)" in ar and "cocoFused" not in ar
+    rs = _gen(dsl_build, "adam_derived", "RS_C_AG", tmp_path)
+    assert "cocoReduceScatter(comm, g, g + (size_t)DIVUP(N, comm_size) * rank, N, stream)" in rs
+    assert "cocoAllGather(comm, " in rs and ", w, N, stream)" in rs
+    assert "m[i0] = " in rs and "v[i0] = " in rs           # asSlice: the moments live on the slice
+    assert "w[DIVUP(N, comm_size) * rank + i0]" in rs      # the weight is still whole
+    assert rs.count("__global__") == 1                     # the slice computation is one kernel
+    fused = _gen(dsl_build, "adam_derived", "fuse_RS_C_AG", tmp_path)
+    assert ADAM_CALL in fused and "__global__" not in fused
+    assert ADAM_CALL in _gen(dsl_build, "adam", "fuse_RS_C_AG", tmp_path)
+    for sched in ("RS_C_AG", "fuse_RS_C_AG"):
+        subprocess.check_call([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                               os.path.join(DSL, "rt"), "-I", os.path.join(ROOT, "include"), "-c",
+                               str(tmp_path / f"adam_derived-{sched}.cu"), "-o", str(tmp_path / "d.o")])
+
+
+def _run_dsl_program(tmp_path, body):
+    prog = tmp_path / "t.cpp"
+    prog.write_text('#include <dsl.hpp>\n#include <pipeline.hpp>\n#include <iostream>\n'
+                    'using namespace ACCCDSL;\nint main() {\n'
+                    '  Variable N(Int32, "N"); Variable lr(Float32, "lr");\n'
+                    '  Tensor g(Float32, N, Local, "g"); Tensor w(Float32, N, Replicated, "w");\n'
+                    '  Tensor m(Float32, N, Replicated, "m");\n' + body + '\n  return 0;\n}\n')
+    exe = str(tmp_path / "t")
+    subprocess.check_call(["g++", "-std=c++17", "-I", os.path.join(DSL, "include"), str(prog),
+                           os.path.join(DSL, "build", "libcoconet_dsl.a"), "-o", exe])
+    return subprocess.run([exe], cwd=tmp_path, capture_output=True, text=True)
+
+
+def test_transformations_refuse_what_would_change_the_result(dsl_build, tmp_path):
+    # split of something that is not an AllReduce
+    out = _run_dsl_program(tmp_path, '''
+  Stage s = AllReduce(Summation, g); Stage wn = Update(w, w - lr * s);
+  Pipeline p("p", {g, w, lr}, {wn});
+  p.split(wn, AllReduceRSAG);''')
+    assert out.returncode != 0 and "not an AllReduce" in out.stderr
+    # reorder that leaves a consumer of the gathered value above the AllGather
+    out = _run_dsl_program(tmp_path, '''
+  Stage s = AllReduce(Summation, g); Stage mn = Update(m, m + s); Stage wn = Update(w, w - lr * s);
+  Pipeline p("p", {g, w, m, lr}, {mn, wn});
+  auto rsag = p.split(s, AllReduceRSAG);
+  p.reorder({wn}, rsag.second);''')
+    assert out.returncode != 0 and "also uses the AllGather" in out.stderr
+    # a stage with a norm is not pointwise
+    out = _run_dsl_program(tmp_path, '''
+  Stage s = AllReduce(Summation, g); Stage wn = Update(w, w - lr * s / Norm(s));
+  Pipeline p("p", {g, w, lr}, {wn});
+  auto rsag = p.split(s, AllReduceRSAG);
+  p.reorder({wn}, rsag.second);''')
+    assert out.returncode != 0 and "not pointwise" in out.stderr
+    # asSlice of a tensor that a stage still computes on whole
+    out = _run_dsl_program(tmp_path, '''
+  Stage s = AllReduce(Summation, g); Stage mn = Update(m, m + s); Stage wn = Update(w, w - lr * mn);
+  Pipeline p("p", {g, w, m, lr}, {mn, wn});
+  p.asSlice(m);''')
+    assert out.returncode != 0 and "reorder it below the AllGather first" in out.stderr
+    # the legal sequence: every stage moves, then the state becomes a slice
+    out = _run_dsl_program(tmp_path, '''
+  Stage s = AllReduce(Summation, g); Stage mn = Update(m, m + s); Stage wn = Update(w, w - lr * mn);
+  Pipeline p("p", {g, w, m, lr}, {mn, wn});
+  auto rsag = p.split(s, AllReduceRSAG);
+  auto re = p.reorder({mn, wn}, rsag.second);
+  p.asSlice(m);
+  std::cout << re.compStages.size() << " " << re.allGatherStages.size() << " "
+            << (m.layout() == Sliced) << (w.layout() == Replicated) << std::endl;
+  p.codegen("seq.cu");''')
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split()[:3] == ["2", "2", "11"]
+    text = (tmp_path / "seq.cu").read_text()
+    assert "cocoReduceScatter(" in text and text.count("cocoAllGather(") == 1

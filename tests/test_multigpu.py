@@ -63,7 +63,9 @@ def test_nvls_multicast_path():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
 @pytest.mark.parametrize("opt,schedule", [("adam", "fuse_RS_C_AG"), ("lamb", "fuse_RS_C_AG"),
                                           ("sgd", "RS_C_AG"), ("nesterov", "fuse_RS_C_AG"),
-                                          ("lamb", "RS_C_AG"), ("adam", "AR_C")])
+                                          ("lamb", "RS_C_AG"), ("adam", "AR_C"),
+                                          ("adam_derived", "RS_C_AG"),
+                                          ("adam_derived", "fuse_RS_C_AG")])
 def test_emitted_program_multi_rank(tmp_path, opt, schedule):
     """A DSL-emitted C++ program, one process per GPU, started without MPI."""
     import dsl_build_util as B
