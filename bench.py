@@ -325,6 +325,23 @@ def run_sweep(args, rank, world, local_rank):
             if rank == 0:
                 print(f"# adam  f32 scattered over {len(shapes)} BERT-large-shaped tensors, {tot} elements: "
                       f"{ms_sc:.4f} ms  (flat call on as many elements: {ms_fl:.4f} ms)", flush=True)
+
+            # LAMB with one trust ratio per tensor, next to the flat call (one ratio overall)
+            def scattered_lamb(i):
+                comm.fused_lamb_scattered(gl, wl, msc, vsc, HYPER["lr"], HYPER["beta1"],
+                                          HYPER["beta2"], HYPER["eps"], 0.01, i)
+
+            def flat_lamb(i):
+                comm.fused_lamb(g32[:tot_f], w32[:tot_f], m[:tot_f // R], v[:tot_f // R],
+                                HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"],
+                                0.01, i)
+
+            ms_sc, ms_fl = time_ms(scattered_lamb, 5, 3), time_ms(flat_lamb, 5, 3)
+            out.append({"opt": "lamb", "grad": "f32", "count": tot, "world": R, "tensors": len(shapes),
+                        "scattered_ms": ms_sc, "flat_ms": ms_fl})
+            if rank == 0:
+                print(f"# lamb  f32 scattered (per-tensor trust ratios) over {len(shapes)} tensors: "
+                      f"{ms_sc:.4f} ms  (flat call on as many elements: {ms_fl:.4f} ms)", flush=True)
     st = comm.status()
     if rank == 0:
         line = {"sweep": out, "n_gpus": R, "status": st["code"],

@@ -437,6 +437,7 @@ struct Hyper {
   double d1d, d2d, r1d, r2d;
   int variant;
   bool square_first;  // (1-b2)*(g*g) instead of ((1-b2)*g)*g
+  float quirk_n;      // COCO_LAMB_REF_QUIRK: the element count r^2 is divided by
 };
 
 template <int OPT> __device__ __forceinline__ Hyper make_hyper(const StepArgs &sa) {
@@ -449,6 +450,7 @@ template <int OPT> __device__ __forceinline__ Hyper make_hyper(const StepArgs &s
   h.variant = sa.variant;
   // test-adam.cu:16 squares first; lamb.cpp:81 multiplies left to right
   h.square_first = OPT == kAdam && sa.variant == cocoVariantDsl;
+  h.quirk_n = (float)sa.count;
   return h;
 }
 
@@ -566,7 +568,7 @@ __device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa
       } else {
         const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
         if (sa.flags & COCO_LAMB_REF_QUIRK) {
-          sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), (float)sa.count);
+          sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), h.quirk_n);
           sum_w2 += (double)__fmul_rn(w[e], w[e]);
         } else {
           sum_r2 += (double)r * (double)r;
@@ -722,7 +724,7 @@ __device__ __forceinline__ void nvls_phase(const RankArgs &ra, const StepArgs &s
           } else {
             const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
             if (sa.flags & COCO_LAMB_REF_QUIRK) {
-              sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), (float)sa.count);
+              sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), h.quirk_n);
               sum_w2 += (double)__fmul_rn(w[e], w[e]);
             } else {
               sum_r2 += (double)r * (double)r;
@@ -931,7 +933,7 @@ __device__ __forceinline__ void tile_math(const RankArgs &ra, const StepArgs &sa
         } else {
           const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
           if (sa.flags & COCO_LAMB_REF_QUIRK) {
-            sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), (float)sa.count);
+            sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), h.quirk_n);
             sum_w2 += (double)__fmul_rn(w[e], w[e]);
           } else {
             sum_r2 += (double)r * (double)r;
@@ -1101,51 +1103,177 @@ __global__ void __launch_bounds__(512, 2)
   const size_t nth = (size_t)gridDim.x * blockDim.x;
   const Hyper h = make_hyper<OPT>(sa);
 
+  bool seg_norm_ok = true;  // scattered LAMB: the norm exchange completed
   if constexpr (PATH == kPathSegments) {
     // Scattered call: the slice is a sequence of pieces of different tensors.
     // The whole grid walks them one after the other; for each, the piece's
     // pointers replace the flat call's in the shared RankArgs and the ordinary
-    // peer-to-peer loops run on it.  (SGD and Adam: elementwise, no norms.)
-    __shared__ unsigned long long s_seg[2];
+    // peer-to-peer loops run on it.  SGD and Adam: one pass.  LAMB: a pass for
+    // the moments and every tensor's partial norms, the exchange of those
+    // between the ranks, and a pass that applies each tensor's own trust ratio.
+    __shared__ unsigned long long s_seg[3];
+    __shared__ int s_last;
     const Segment *segs = ra.segs;
     const int nseg = ra.nseg;
-    double unused_w2 = 0.0, unused_r2 = 0.0;
     // Small pieces (biases, layer norms) are taken by ONE CTA each, round robin,
     // so that they proceed side by side instead of every CTA walking every
     // tiny piece; large pieces are shared by the whole grid.
     const unsigned long long small = 64ull * blockDim.x;
-    for (int sidx = 0; sidx < nseg && ok; ++sidx) {
-      const bool solo = segs[sidx].len < small;
-      if (solo && (unsigned)sidx % gridDim.x != blockIdx.x) continue;  // uniform per CTA
-      // Shared pieces start at a different CTA each time: a piece rarely is a whole
-      // number of grid passes, and without the rotation the same CTAs would always
-      // get the extra pass.
-      const size_t tid_s = solo ? threadIdx.x : (tid + (size_t)sidx * 37u * blockDim.x) % nth;
-      const size_t nth_s = solo ? blockDim.x : nth;
-      __syncthreads();  // everyone is done with the previous piece's pointers
-      if (threadIdx.x < kMaxRanks) {
-        ra.g[threadIdx.x] = segs[sidx].g[threadIdx.x];
-        ra.out[threadIdx.x] = segs[sidx].out[threadIdx.x];
+    constexpr int kPasses = OPT == kLAMB ? 2 : 1;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll 1
+    for (int pass = 0; pass < kPasses; ++pass) {
+#pragma unroll 1
+      for (int sidx = 0; sidx < nseg && ok; ++sidx) {
+        const bool solo = segs[sidx].len < small;
+        if (solo && (unsigned)sidx % gridDim.x != blockIdx.x) continue;  // uniform per CTA
+        // Shared pieces start at a different CTA each time: a piece rarely is a whole
+        // number of grid passes, and without the rotation the same CTAs would always
+        // get the extra pass.
+        const size_t tid_s = solo ? threadIdx.x : (tid + (size_t)sidx * 37u * blockDim.x) % nth;
+        const size_t nth_s = solo ? blockDim.x : nth;
+        __syncthreads();  // everyone is done with the previous piece's pointers
+        if (threadIdx.x < kMaxRanks) {
+          ra.g[threadIdx.x] = segs[sidx].g[threadIdx.x];
+          ra.out[threadIdx.x] = segs[sidx].out[threadIdx.x];
+        }
+        if (threadIdx.x == 32) {
+          ra.w = segs[sidx].w, ra.m = segs[sidx].m, ra.v = segs[sidx].v;
+          ra.aligned16 = segs[sidx].aligned16;
+          s_seg[0] = segs[sidx].begin, s_seg[1] = segs[sidx].len;
+          s_seg[2] = segs[sidx].tensor_len;
+        }
+        if constexpr (OPT == kLAMB) {
+          if (pass == 1 && threadIdx.x == 0) {
+            // this tensor's norms: the partials of the ranks that hold a part of
+            // it, in rank order (thread 0 is the one that waited for them)
+            TensorNorms *tn = tensor_norms_of(me);
+            const int t = segs[sidx].tensor;
+            double w2 = 0.0, r2 = 0.0;
+            for (int p = segs[sidx].first_rank; p <= segs[sidx].last_rank; ++p) {
+              w2 += ld_volatile_f64(&tn->part[p][t][0]);
+              r2 += ld_volatile_f64(&tn->part[p][t][1]);
+            }
+            double wn, rn, sc;
+            if (sa.flags & COCO_LAMB_REF_QUIRK) {  // sample :424-433, per buffer
+              rn = sqrt(r2);
+              wn = sqrt(w2 / (double)segs[sidx].tensor_len);
+              sc = ((wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0) / rn;
+            } else {
+              rn = sqrt(r2);
+              wn = sqrt(w2);
+              sc = (wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0;
+            }
+            s_lr_scale = __fmul_rn(sa.lr, (float)sc);
+          }
+        }
+        __syncthreads();
+        const size_t seg_lo = s_seg[0], seg_len = s_seg[1];
+        const size_t nv = ra.aligned16 ? seg_len / VEC : 0;
+        Hyper hs = h;
+        if constexpr (OPT == kLAMB) hs.quirk_n = (float)s_seg[2];
+        if (pass == 0) {
+          double p_w2 = 0.0, p_r2 = 0.0;
+          if (R == 1)
+            direct_step<OPT, GT, LPT, 1>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
+          else if (R == 2)
+            direct_step<OPT, GT, LPT, 2>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
+          else if (R <= 4)
+            direct_step<OPT, GT, LPT, 4>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
+          else
+            direct_step<OPT, GT, LPT, 8>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
+          for (size_t j = nv * VEC + tid_s; j < seg_len; j += nth_s)
+            step_unit<OPT, GT, LPT, 1, 0>(ra, sa, hs, seg_lo, seg_lo + j, p_w2, p_r2);
+          if constexpr (OPT == kLAMB) {
+            // this CTA's share of the piece: thread -> warp -> CTA, fixed order
+            p_w2 = warp_sum(p_w2);
+            p_r2 = warp_sum(p_r2);
+            if (lane == 0) s_red[0][wid] = p_w2, s_red[1][wid] = p_r2;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+              double a = 0.0, b = 0.0;
+              for (int k = 0; k < nwarp; ++k) a += s_red[0][k], b += s_red[1][k];
+              double *slot = ra.seg_part + ((size_t)sidx * gridDim.x + blockIdx.x) * 2;
+              slot[0] = a;
+              slot[1] = b;
+            }
+          }
+        } else if constexpr (OPT == kLAMB) {
+          const float lr_scale = s_lr_scale;
+          if (R == 1)
+            direct_apply<GT, LPT, 1>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
+          else if (R == 2)
+            direct_apply<GT, LPT, 2>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
+          else if (R <= 4)
+            direct_apply<GT, LPT, 4>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
+          else
+            direct_apply<GT, LPT, 8>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
+          for (size_t j = nv * VEC + tid_s; j < seg_len; j += nth_s)
+            lamb_apply_unit<LPT, 1, 0>(ra, sa, hs, seg_lo, seg_lo + j, lr_scale);
+        }
       }
-      if (threadIdx.x == 32) {
-        ra.w = segs[sidx].w, ra.m = segs[sidx].m, ra.v = segs[sidx].v;
-        ra.aligned16 = segs[sidx].aligned16;
-        s_seg[0] = segs[sidx].begin, s_seg[1] = segs[sidx].len;
+      if constexpr (OPT == kLAMB) {
+        if (pass == 0) {
+          // ---- per-tensor norms: CTA partials -> rank (last CTA, fixed order) -> peers
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            __threadfence();  // this CTA's partial sums before the count
+            const unsigned prev = atomicAdd(&me->norm_count, 1u);
+            s_last = prev == gridDim.x - 1;
+            if (s_last) me->norm_count = 0;
+          }
+          __syncthreads();
+          if (s_last) {
+            __threadfence();
+            for (int sidx = wid; sidx < nseg; sidx += nwarp) {  // one warp per piece
+              double a = 0.0, b = 0.0;
+              if (started_ok) {  // a rank that never started publishes zeros
+                const double *row = ra.seg_part + (size_t)sidx * gridDim.x * 2;
+                if (segs[sidx].len < small) {  // taken by one CTA
+                  if (lane == 0) {
+                    const unsigned c = (unsigned)sidx % gridDim.x;
+                    a = ld_volatile_f64(row + 2 * c), b = ld_volatile_f64(row + 2 * c + 1);
+                  }
+                } else {
+                  for (unsigned c = lane; c < gridDim.x; c += 32) {
+                    a += ld_volatile_f64(row + 2 * c);
+                    b += ld_volatile_f64(row + 2 * c + 1);
+                  }
+                }
+              }
+              a = warp_sum(a);
+              b = warp_sum(b);
+              if (lane == 0) {
+                const int t = segs[sidx].tensor;
+                for (int p = 0; p < R; ++p) {
+                  volatile double *dst = tensor_norms_of(ra.flags[p])->part[rank][t];
+                  dst[0] = a;
+                  dst[1] = b;
+                }
+                __threadfence_system();
+              }
+            }
+            __syncthreads();
+            if ((int)threadIdx.x < R) {
+              __threadfence_system();
+              st_release_sys(&ra.flags[threadIdx.x]->norm_flag[rank], seq);
+            }
+          }
+          // every CTA: wait (bounded) until all ranks' partials are in
+          if (threadIdx.x == 0 && ok) {
+            const int late = wait_all(me->norm_flag, R, -1, seq, sa.timeout_ns);
+            if (late >= 0) {
+              record_status(me, cocoTimeout, rank, kPhaseNorm, late, seq);
+              s_ok = 0;
+            }
+          }
+          __syncthreads();
+          ok = ok && s_ok != 0;
+        }
       }
-      __syncthreads();
-      const size_t seg_lo = s_seg[0], seg_len = s_seg[1];
-      const size_t nv = ra.aligned16 ? seg_len / VEC : 0;
-      if (R == 1)
-        direct_step<OPT, GT, LPT, 1>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, unused_w2, unused_r2);
-      else if (R == 2)
-        direct_step<OPT, GT, LPT, 2>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, unused_w2, unused_r2);
-      else if (R <= 4)
-        direct_step<OPT, GT, LPT, 4>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, unused_w2, unused_r2);
-      else
-        direct_step<OPT, GT, LPT, 8>(ra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, unused_w2, unused_r2);
-      for (size_t j = nv * VEC + tid_s; j < seg_len; j += nth_s)
-        step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, seg_lo, seg_lo + j, unused_w2, unused_r2);
     }
+    seg_norm_ok = ok;
     ok = false;  // nothing is left for the flat-slice code below
     __syncthreads();
   }
@@ -1203,7 +1331,7 @@ __global__ void __launch_bounds__(512, 2)
       step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, lo, lo + j, sum_w2, sum_r2);
   }
 
-  if constexpr (OPT == kLAMB) {
+  if constexpr (OPT == kLAMB && PATH != kPathSegments) {
     // ---- norms: thread -> warp -> CTA -> rank (fixed order) -> all ranks ---
     sum_w2 = warp_sum(sum_w2);
     sum_r2 = warp_sum(sum_r2);
@@ -1300,7 +1428,7 @@ __global__ void __launch_bounds__(512, 2)
     }
   }
 
-  if (seg_done) ok = started_ok;
+  if (seg_done) ok = started_ok && seg_norm_ok;
 
   // ---- end barrier ----------------------------------------------------------
   if (R > 1) {
@@ -1337,9 +1465,7 @@ template <int OPT, typename GT, typename LPT> KernelPtr pick_path(int path) {
     case kPathNvls: return fused_step_kernel<OPT, GT, LPT, kPathNvls>;
     case kPathTiles: return fused_step_kernel<OPT, GT, LPT, kPathTiles>;
     case kPathLocal: return fused_step_kernel<OPT, GT, LPT, kPathLocal>;
-    case kPathSegments:
-      if constexpr (OPT == kLAMB) return nullptr;  // per-tensor norms: not built
-      else return fused_step_kernel<OPT, GT, LPT, kPathSegments>;
+    case kPathSegments: return fused_step_kernel<OPT, GT, LPT, kPathSegments>;
     default: return fused_step_kernel<OPT, GT, LPT, kPathDirect>;
   }
 }

@@ -155,6 +155,8 @@ FlatLayout flat_layout(const size_t *counts, size_t n, int world) {
 
 struct LocalGroup;  // ranks that live in one process
 
+constexpr size_t kCommPageBytes = sizeof(FlagPage) + sizeof(TensorNorms);
+
 }  // namespace
 
 struct cocoComm {
@@ -178,6 +180,8 @@ struct cocoComm {
   std::vector<Segment> seg_host;   // last segment table uploaded
   Segment *seg_dev = nullptr;
   size_t seg_cap = 0;
+  double *seg_part = nullptr;      // scattered LAMB: per-segment, per-CTA partial sums
+  size_t seg_part_cap = 0;         // in doubles
   int ctas_per_sm = 0;  // 0 = automatic
   int threads = 512;
   int timeout_ms = 10000;
@@ -225,8 +229,10 @@ int init_common(cocoComm *c) {
   c->smem_budget_kb = std::max(16, std::min(220, env_int("COCO_SMEM_KB", 200)));
   c->timeout_ms = env_int("COCO_TIMEOUT_MS", 10000);
   if (c->timeout_ms <= 0) c->timeout_ms = 10000;
-  CUDA_TRY(cudaMalloc((void **)&c->flags, sizeof(FlagPage)));
-  CUDA_TRY(cudaMemset(c->flags, 0, sizeof(FlagPage)));
+  // one block: the flag page, and behind it the per-tensor norm table of
+  // scattered LAMB calls (tensor_norms_of)
+  CUDA_TRY(cudaMalloc((void **)&c->flags, kCommPageBytes));
+  CUDA_TRY(cudaMemset(c->flags, 0, kCommPageBytes));
   CUDA_TRY(cudaDeviceSynchronize());
   c->peer_flags[c->rank] = c->flags;
   return cocoSuccess;
@@ -385,7 +391,8 @@ int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
 int validate(const cocoComm *c, const PendingCall &pc) {
   if (!c) return cocoInvalidArgument;
   if (!pc.scounts.empty()) {
-    if (pc.opt == kLAMB || pc.w_lp) return cocoInvalidArgument;  // per-tensor norms / copies: not built
+    if (pc.w_lp) return cocoInvalidArgument;  // low-precision copies of a list: not built
+    if (pc.opt == kLAMB && pc.scounts.size() > (size_t)kMaxLambTensors) return cocoInvalidArgument;
     for (size_t b = 0; b < pc.scounts.size(); ++b)
       if (!pc.sg[b] || !pc.sw[b]) return cocoInvalidArgument;
   } else if (!pc.g || !pc.w) {
@@ -460,6 +467,9 @@ std::vector<Segment> build_segments(int rank, int world, const FlatLayout &L,
     al = al && (sg.begin % 8 == 0) && aligned16(sg.m) && aligned16(sg.v) && gsize != 0;
     sg.aligned16 = al ? 1 : 0;
     sg.tensor = (int)b;
+    sg.tensor_len = counts[b];
+    sg.first_rank = (int)(t0 / L.slice);          // counts[b] > 0 here: t1 - 1 >= t0
+    sg.last_rank = (int)((t1 - 1) / L.slice);
     out.push_back(sg);
   }
   return out;
@@ -489,6 +499,22 @@ int upload_segments(cocoComm *c, const std::vector<Segment> &segs, cudaStream_t 
                              cudaMemcpyHostToDevice, stream));
   }
   *dev = c->seg_dev;
+  return cocoSuccess;
+}
+
+// Scattered LAMB: room for one partial-sum pair per (segment, CTA) of this rank.
+// Nothing is cleared: a step reads only the entries it wrote.
+int ensure_seg_part(cocoComm *c, size_t nseg, int ctas, cudaStream_t stream, double **dev) {
+  const size_t need = nseg * (size_t)ctas * 2;
+  if (need > c->seg_part_cap) {
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    if (c->seg_part) CUDA_TRY(cudaFree(c->seg_part));
+    c->seg_part = nullptr;
+    c->seg_part_cap = 0;
+    CUDA_TRY(cudaMalloc((void **)&c->seg_part, need * sizeof(double)));
+    c->seg_part_cap = need;
+  }
+  *dev = c->seg_part;
   return cocoSuccess;
 }
 
@@ -528,6 +554,8 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
   }
   COCO_TRY(pick_launch(c, pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, pc.sa.count,
                        c->world, 1, &sa, &cfg));
+  if (pc.opt == kLAMB && ra.nseg > 0)
+    COCO_TRY(ensure_seg_part(c, (size_t)ra.nseg, cfg.ctas, pc.stream, &ra.seg_part));
   CUDA_TRY(launch_fused_step(pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, sa, ra, nullptr,
                              cfg, pc.stream));
   c->launches++;
@@ -616,6 +644,16 @@ int flush_group(LocalGroup *grp) {
     if (rc != cocoSuccess) {
       result = rc;
       break;
+    }
+    if (scattered && pc0.opt == kLAMB) {
+      bool failed = false;
+      for (size_t k = 0; k < ranks.size() && !failed; ++k)
+        if (host[k].nseg > 0) {
+          int rc2 = ensure_seg_part(grp->comms[ranks[k]], (size_t)host[k].nseg, cfg.ctas,
+                                    pc0.stream, &host[k].seg_part);
+          if (rc2 != cocoSuccess) result = rc2, failed = true;
+        }
+      if (failed) break;
     }
     RankArgs *table = nullptr;
     if (ranks.size() > 1) {
@@ -795,7 +833,7 @@ int cocoCommInitRank(cocoComm_t *comm, int world, int rank, const char *bootstra
     if (r != cocoSuccess) return r;
   if (world > 1) {
     Region reg;
-    COCO_TRY(map_region_ipc(c.get(), c->flags, sizeof(FlagPage), &reg));
+    COCO_TRY(map_region_ipc(c.get(), c->flags, kCommPageBytes, &reg));
     for (int p = 0; p < world; ++p) c->peer_flags[p] = (FlagPage *)reg.peer[p];
     COCO_TRY(c->boot->barrier());
   }
@@ -885,6 +923,7 @@ int cocoCommDestroy(cocoComm_t comm) {
         cudaFree(kv.second);
       }
   }
+  if (comm->seg_part) cudaFree(comm->seg_part);
   if (comm->flags) cudaFree(comm->flags);
   if (comm->seg_dev) cudaFree(comm->seg_dev);
   (void)cudaGetLastError();
@@ -1188,6 +1227,24 @@ int cocoFusedAdamScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
   pc.sa.variant = (int)variant;
   set_denominators(&pc.sa, kAdam, step);
   return enqueue_scattered(comm, kAdam, nbuff, g, g_type, w, counts, m, v, pc, stream);
+}
+
+int cocoFusedLAMBScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
+                           cocoDataType_t g_type, float *const *w, const size_t *counts, float *m,
+                           float *v, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, int step, float grad_scale, cocoVariant_t variant,
+                           unsigned flags, cocoStream_t stream) {
+  if (step < 0 || variant == cocoVariantNccl || !m || !v) return cocoInvalidArgument;
+  if (nbuff > (size_t)kMaxLambTensors) return cocoInvalidArgument;
+  PendingCall pc;
+  pc.sa.lr = lr, pc.sa.beta1 = beta1, pc.sa.beta2 = beta2;
+  pc.sa.eps = variant == cocoVariantOverlap ? eps : 0.f;
+  pc.sa.weight_decay = weight_decay;
+  pc.sa.grad_scale = grad_scale;
+  pc.sa.variant = (int)variant;
+  pc.sa.flags = flags;
+  set_denominators(&pc.sa, kLAMB, step);
+  return enqueue_scattered(comm, kLAMB, nbuff, g, g_type, w, counts, m, v, pc, stream);
 }
 
 int cocoLastLambNorms(cocoComm_t comm, double out[2]) {

@@ -80,6 +80,11 @@ _SIGNATURES = {
                                          C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_void_p,
                                          C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_float,
                                          C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "cocoFusedLAMBScattered": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_int,
+                                         C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_void_p,
+                                         C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_float,
+                                         C.c_float, C.c_int, C.c_float, C.c_int, C.c_uint,
+                                         C.c_void_p]),
     "cocoAllReduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cocoReduceScatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cocoAllGather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
@@ -244,6 +249,12 @@ class Communicator:
     def barrier(self):
         _check(lib().cocoBarrier(self._h), "cocoBarrier")
 
+    def all_gather_host(self, blob: bytes):
+        """Every rank's `blob` (same length everywhere), in rank order."""
+        recv = C.create_string_buffer(len(blob) * self.world)
+        _check(lib().cocoAllGatherHost(self._h, blob, recv, len(blob)), "cocoAllGatherHost")
+        return [recv.raw[i * len(blob):(i + 1) * len(blob)] for i in range(self.world)]
+
     def register(self, t):
         _check(lib().cocoRegister(self._h, _ptr(t), t.numel() * t.element_size()), "cocoRegister")
 
@@ -349,6 +360,15 @@ class Communicator:
         _check(lib().cocoFusedAdamScattered(self._h, n, ga, _dtype_code(gs[0]), wa, ca, _ptr(m),
                                             _ptr(v), lr, beta1, beta2, eps, step, grad_scale,
                                             variant, _stream(stream)), "cocoFusedAdamScattered")
+
+    def fused_lamb_scattered(self, gs, ws, m, v, lr, beta1, beta2, eps, weight_decay, step,
+                             grad_scale=1.0, variant=VARIANT_OVERLAP, flags=0, stream=None):
+        """LAMB over a list of tensors with one trust ratio PER TENSOR."""
+        n, ga, wa, ca = self._lists(gs, ws)
+        _check(lib().cocoFusedLAMBScattered(self._h, n, ga, _dtype_code(gs[0]), wa, ca, _ptr(m),
+                                            _ptr(v), lr, beta1, beta2, eps, weight_decay, step,
+                                            grad_scale, variant, flags, _stream(stream)),
+               "cocoFusedLAMBScattered")
 
     # ---- introspection ----
     def status(self):

@@ -13,6 +13,7 @@ namespace coco {
 
 constexpr int kMaxRanks = COCO_MAX_RANKS;
 constexpr int kMaxCtasPerRank = 2048;  // rows of the per-CTA partial-norm table
+constexpr int kMaxLambTensors = COCO_MAX_LAMB_TENSORS;  // tensors of one scattered LAMB call
 
 enum Opt : int { kSGD = 0, kAdam = 1, kLAMB = 2 };
 
@@ -36,6 +37,19 @@ struct FlagPage {
   double cta_part[kMaxCtasPerRank][2];
 };
 
+// Per-tensor norm partials of a scattered LAMB call.  A communicator allocates
+// its flag page and this table as ONE peer-mapped block, the table right
+// behind the page (tensor_norms_of); pages made elsewhere have no table.
+struct TensorNorms {
+  // written by peers (first index = writer's rank): {sum w^2, sum r^2} of the
+  // part of tensor b that lies in the writer's slice; valid for call seq once
+  // the writer's norm_flag says so, and only for writers whose slice meets b
+  double part[kMaxRanks][kMaxLambTensors][2];
+};
+__host__ __device__ inline TensorNorms *tensor_norms_of(FlagPage *page) {
+  return reinterpret_cast<TensorNorms *>(page + 1);
+}
+
 // One piece of a rank's slice when the parameters are a LIST of tensors
 // (scattered calls): the part of one tensor that falls into the slice.
 struct Segment {
@@ -48,6 +62,8 @@ struct Segment {
   unsigned long long len;     // number of elements
   int aligned16;
   int tensor;
+  unsigned long long tensor_len;  // elements of the whole tensor
+  int first_rank, last_rank;      // ranks whose slices hold a part of the tensor
 };
 
 // Per-rank pointers of one fused call.  Indexed tables hold the view THIS
@@ -66,6 +82,7 @@ struct RankArgs {
   const Segment *segs;        // scattered calls: this rank's segments (device memory)
   int nseg;
   int pad;
+  double *seg_part;           // scattered LAMB: [segment][CTA][2] partial sums of this rank
 };
 
 // Internal StepArgs::flags bit (public flags use the low byte).

@@ -44,6 +44,7 @@ extern "C" {
 
 #define COCO_VERSION 100
 #define COCO_MAX_RANKS 8
+#define COCO_MAX_LAMB_TENSORS 2048 /* tensors of one cocoFusedLAMBScattered call */
 
 typedef struct cocoComm *cocoComm_t;
 
@@ -249,8 +250,13 @@ int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *w, void *w_
  * tensor with slices of cocoScatteredSliceElems elements, and m, v are
  * slice-local arrays of that many fp32 elements.  Every rank passes the same
  * list in the same order; each tensor is peer-mapped on first use.  fp32
- * weights are gathered (no low-precision copy); peer-to-peer path.  Per-tensor
- * LAMB (all_reduce_scattered.h:106-282) is not built. */
+ * weights are gathered (no low-precision copy); peer-to-peer path.
+ * cocoFusedLAMBScattered replaces ncclAllReduceScatteredLAMB (all_reduce.cc:
+ * 61-75; all_reduce_scattered.h:106-282): the trust ratio is PER TENSOR, from
+ * ||w_b|| and ||r_b|| of tensor b alone (double sums, fixed order: CTA, rank),
+ * exchanged between the ranks whose slices hold parts of b; everything else is
+ * cocoFusedLAMB's arithmetic, `flags` included.  At most COCO_MAX_LAMB_TENSORS
+ * tensors per call. */
 int cocoScatteredSliceElems(size_t nbuff, const size_t *counts, int world, size_t *slice_elems);
 int cocoFusedSGDScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
                           cocoDataType_t g_type, float *const *w, const size_t *counts, float lr,
@@ -259,6 +265,12 @@ int cocoFusedAdamScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
                            cocoDataType_t g_type, float *const *w, const size_t *counts, float *m,
                            float *v, float lr, float beta1, float beta2, float eps, int step,
                            float grad_scale, cocoVariant_t variant, cocoStream_t stream);
+
+int cocoFusedLAMBScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
+                           cocoDataType_t g_type, float *const *w, const size_t *counts, float *m,
+                           float *v, float lr, float beta1, float beta2, float eps,
+                           float weight_decay, int step, float grad_scale, cocoVariant_t variant,
+                           unsigned flags, cocoStream_t stream);
 
 /* ---- stand-alone collectives (fp32, sum) ------------------------------------
  * What the unfused schedules of a generated program call where the reference

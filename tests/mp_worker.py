@@ -252,8 +252,43 @@ def case_scattered(comm):
                 assert np.array_equal(mh[a - lo:z - lo], om[b][a - off[b]:z - off[b]])
                 assert np.array_equal(vh[a - lo:z - lo], ov[b][a - off[b]:z - off[b]])
         comm.barrier()
+    # LAMB with one trust ratio per tensor: the per-tensor norm partials cross
+    # processes through the table behind each rank's flag page
+    O_ = __import__("oracle_lib")
+    lw = [torch.from_numpy(x.copy()).cuda() for x in w0]
+    lm, lv = torch.zeros(S, device="cuda"), torch.zeros(S, device="cuda")
+    low = [x.copy() for x in w0]
+    lom = [np.zeros(c, np.float32) for c in counts]
+    lov = [np.zeros(c, np.float32) for c in counts]
+    for step in range(3):
+        grads = [K.make_grads(R, c, 950 + b, step) for b, c in enumerate(counts)]
+        for b in range(len(counts)):
+            g[b].copy_(torch.from_numpy(grads[b][rank]))
+        torch.cuda.synchronize()
+        comm.barrier()
+        comm.fused_lamb_scattered(g, lw, lm, lv, h["lr"], h["beta1"], h["beta2"], h["eps"],
+                                  h["weight_decay"], step)
+        torch.cuda.synchronize()
+        assert comm.status()["code"] == 0
+        mh = lm.cpu().numpy()
+        for b, cnt in enumerate(counts):
+            O_.lamb(low[b], lom[b], lov[b], O_.reduce_f32(grads[b]), h["lr"], h["beta1"],
+                    h["beta2"], h["eps"], h["weight_decay"], step)
+            got = lw[b].cpu().numpy()
+            K.assert_close(got, low[b], 1e-5, f"scattered lamb w tensor {b} step {step}")
+            low[b] = got.copy()
+            lo, hi = rank * S, (rank + 1) * S
+            a, z = max(off[b], lo), min(off[b] + cnt, hi)
+            if a < z:
+                assert np.array_equal(mh[a - lo:z - lo], lom[b][a - off[b]:z - off[b]])
+        # replicas agree bit for bit: compare a checksum of all weights across ranks
+        digest = np.array([float(np.sum(x.cpu().numpy().astype(np.float64))) for x in lw])
+        all_d = comm.all_gather_host(digest.tobytes())
+        assert all(d == all_d[0] for d in all_d), "scattered lamb: replicas differ"
+        comm.barrier()
     if rank == 0:
         print(f"ok scattered R={R} tensors={len(counts)}", flush=True)
+        print(f"ok scattered_lamb R={R}", flush=True)
 
 
 def case_collectives(comm):

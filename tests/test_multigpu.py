@@ -97,7 +97,7 @@ def test_runtime_symmetric_memory_and_multicast():
 def test_scattered_tensor_lists_across_processes():
     r = _launch("scattered", min(_ngpu(), 8))
     assert r.returncode == 0, _why(r)
-    assert "ok scattered" in r.stdout, r.stdout
+    assert "ok scattered" in r.stdout and "ok scattered_lamb" in r.stdout, r.stdout
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")

@@ -75,6 +75,99 @@ def test_scattered_matches_per_tensor_oracle(R, opt):
             c.destroy()
 
 
+@pytest.mark.parametrize("R", [1, 2, 3, 8])
+@pytest.mark.parametrize("quirk", [False, True])
+def test_scattered_lamb_has_one_trust_ratio_per_tensor(R, quirk):
+    """Every tensor of the list against the oracle's LAMB run on that tensor
+    alone (its own ||w||, ||r||): moments bit for bit, weights to 1e-5 (the
+    norms are summed in another order), replicas bit-identical.  With the
+    quirk flag the step is also replayed through the reference sample's own
+    host checker, tensor by tensor."""
+    counts = SIZES
+    off, total, S = _layout(counts, R)
+    comms = coco.Communicator.init_all(R, [0] * R)
+    h = dict(K.HYPER)
+    flags = coco.LAMB_REF_QUIRK if quirk else 0
+    if quirk:
+        h["weight_decay"] = 1.0
+    try:
+        w0 = [K.make_weights(c, 700 + b) for b, c in enumerate(counts)]
+        w = [[torch.from_numpy(x.copy()).cuda() for x in w0] for _ in range(R)]
+        m = [torch.zeros(S, device="cuda") for _ in range(R)]
+        v = [torch.zeros(S, device="cuda") for _ in range(R)]
+        ow = [x.copy() for x in w0]
+        om = [np.zeros(c, np.float32) for c in counts]
+        ov = [np.zeros(c, np.float32) for c in counts]
+        rm = [np.zeros(c, np.float32) for c in counts]
+        rv = [np.zeros(c, np.float32) for c in counts]
+        for step in range(3):
+            grads = [[K.make_grads(R, c, 800 + b, step)[r] for b, c in enumerate(counts)]
+                     for r in range(R)]
+            g = [[torch.from_numpy(x).cuda() for x in grads[r]] for r in range(R)]
+            w_old = [x.cpu().numpy().copy() for x in w[0]]
+            with coco.group():
+                for r, c in enumerate(comms):
+                    c.fused_lamb_scattered(g[r], w[r], m[r], v[r], h["lr"], h["beta1"], h["beta2"],
+                                           h["eps"], h["weight_decay"], step, flags=flags)
+            torch.cuda.synchronize()
+            for c in comms:
+                assert c.status()["code"] == 0
+            flat_m = np.concatenate([x.cpu().numpy() for x in m])[:total]
+            flat_v = np.concatenate([x.cpu().numpy() for x in v])[:total]
+            for b, cnt in enumerate(counts):
+                gsum = O.reduce_f32([grads[r][b] for r in range(R)])
+                O.lamb(ow[b], om[b], ov[b], gsum, h["lr"], h["beta1"], h["beta2"], h["eps"],
+                       h["weight_decay"], step, flags=O.LAMB_REF_QUIRK if quirk else 0)
+                got = w[0][b].cpu().numpy()
+                K.assert_close(got, ow[b], 1e-5, f"w of tensor {b} at step {step}")
+                for r in range(1, R):
+                    assert np.array_equal(w[r][b].cpu().numpy(), got), (step, b, r)
+                assert np.array_equal(flat_m[off[b]:off[b] + cnt], om[b]), (step, b)
+                assert np.array_equal(flat_v[off[b]:off[b] + cnt], ov[b]), (step, b)
+                if quirk and O.ref_available() and cnt >= 8:
+                    assert O.ref_overlap_check("lamb", [grads[r][b] for r in range(R)], step,
+                                               w_old[b], got, rm[b], rv[b], h["beta1"], h["beta2"],
+                                               h["lr"], h["eps"]), (step, b)
+                # the oracle continues from the device's weights, so that a last-bit
+                # difference of one step is not carried into the next comparison
+                ow[b] = got.copy()
+    finally:
+        for c in comms:
+            c.destroy()
+
+
+def test_scattered_lamb_equals_flat_call_on_one_tensor():
+    R, n = 4, 1 << 18
+    comms = coco.Communicator.init_all(R, [0] * R)
+    h = K.HYPER
+    try:
+        w0 = K.make_weights(n, 17)
+        grads = K.make_grads(R, n, 17, 0)
+        g = [torch.from_numpy(x).cuda() for x in grads]
+        wa = [torch.from_numpy(w0.copy()).cuda() for _ in range(R)]
+        wb = [torch.from_numpy(w0.copy()).cuda() for _ in range(R)]
+        S = n // R
+        ma, va, mb, vb = ([torch.zeros(S, device="cuda") for _ in range(R)] for _ in range(4))
+        with coco.group():
+            for r, c in enumerate(comms):
+                c.fused_lamb(g[r], wa[r], ma[r], va[r], h["lr"], h["beta1"], h["beta2"], h["eps"],
+                             h["weight_decay"], 0)
+        with coco.group():
+            for r, c in enumerate(comms):
+                c.fused_lamb_scattered([g[r]], [wb[r]], mb[r], vb[r], h["lr"], h["beta1"],
+                                       h["beta2"], h["eps"], h["weight_decay"], 0)
+        torch.cuda.synchronize()
+        for r in range(R):
+            assert torch.equal(ma[r], mb[r]) and torch.equal(va[r], vb[r])
+            # the flat call sums its norm partials per CTA over the whole slice, the
+            # list call per piece: same values to the last bits of a double
+            K.assert_close(wb[r].cpu().numpy(), wa[r].cpu().numpy(), 1e-6, "w")
+            assert torch.equal(wb[r], wb[0])
+    finally:
+        for c in comms:
+            c.destroy()
+
+
 def test_scattered_equals_flat_call_on_one_tensor():
     # a list with a single tensor of a multiple-of-8R size is the flat call
     R, n = 4, 1 << 18
@@ -113,5 +206,8 @@ def test_scattered_rejects_what_is_not_built():
         with pytest.raises(coco.CocoError):     # the forked-NCCL formulation is flat-only
             c.fused_adam_scattered(g, w, w[0], w[0], 1e-3, 0.9, 0.999, 1e-6, 0,
                                    variant=coco.VARIANT_NCCL)
+        many = [torch.zeros(8, device="cuda") for _ in range(2049)]   # more tensors than the norm table holds
+        with pytest.raises(coco.CocoError):
+            c.fused_lamb_scattered(many, many, w[0], w[0], 1e-3, 0.9, 0.999, 1e-6, 0.01, 0)
     finally:
         c.destroy()
