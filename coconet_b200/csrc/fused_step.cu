@@ -216,6 +216,23 @@ template <> struct RawUnit<float, 4> {
   }
   __device__ __forceinline__ unsigned short bits(int) const { return 0; }
 };
+template <> struct RawUnit<float, 8> {
+  uint4 q[2];
+  __device__ __forceinline__ void load(const void *base, size_t i) {
+    q[0] = ld_sys_16((const float *)base + i);
+    q[1] = ld_sys_16((const float *)base + i + 4);
+  }
+  template <int HS> __device__ __forceinline__ void load_halves(const void *base, size_t i) {
+    q[0] = ld_sys_16((const float *)base + i);
+    q[1] = ld_sys_16((const float *)base + i + HS);
+  }
+  __device__ __forceinline__ float get(int k) const {
+    const uint4 &h = q[k >> 2];
+    const int j = k & 3;
+    return __uint_as_float(j == 0 ? h.x : j == 1 ? h.y : j == 2 ? h.z : h.w);
+  }
+  __device__ __forceinline__ unsigned short bits(int) const { return 0; }
+};
 template <> struct RawUnit<float, 1> {
   unsigned q;
   __device__ __forceinline__ void load(const void *base, size_t i) {
@@ -239,6 +256,12 @@ template <typename GT> struct RawUnit<GT, 8> {
   uint4 q;
   __device__ __forceinline__ void load(const void *base, size_t i) {
     q = ld_sys_16((const unsigned short *)base + i);
+  }
+  // elements i..i+3 and i+HS..i+HS+3
+  template <int HS> __device__ __forceinline__ void load_halves(const void *base, size_t i) {
+    const uint2 a = ld_sys_8((const unsigned short *)base + i);
+    const uint2 b = ld_sys_8((const unsigned short *)base + i + HS);
+    q = make_uint4(a.x, a.y, b.x, b.y);
   }
   __device__ __forceinline__ unsigned short bits(int k) const {
     const unsigned wd = (k >> 1) == 0 ? q.x : (k >> 1) == 1 ? q.y : (k >> 1) == 2 ? q.z : q.w;
@@ -264,7 +287,7 @@ template <typename GT> struct RawUnit<GT, 1> {
 // thread has up to RB remote requests in flight.  RB = 0 is a plain loop over
 // the R ranks (cold scalar path).
 // ---------------------------------------------------------------------------
-template <typename GT, int VEC, int RB>
+template <typename GT, int VEC, int RB, int HS = 4>
 __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &sa, size_t i,
                                             float (&g)[VEC], float (&gg)[VEC]) {
   const int R = sa.world;
@@ -311,7 +334,10 @@ __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &
       if (kExact || k < R) {
         int p = first + k;
         if (p >= R) p -= R;
-        raw[k].load(ra.g[p], i);
+        if constexpr (VEC == 8 && HS != 4)
+          raw[k].template load_halves<HS>(ra.g[p], i);
+        else
+          raw[k].load(ra.g[p], i);
       }
     }
     if (ring) {
@@ -343,37 +369,44 @@ __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &
 // ---------------------------------------------------------------------------
 // local fp32 state and the gathered output
 // ---------------------------------------------------------------------------
-template <int VEC> __device__ __forceinline__ void load_f32(const float *p, float (&x)[VEC]) {
+// Plain (write-back, normally cached) accesses: the streaming hints ld.cs /
+// st.cs measured 5 % slower for fp32 Adam on one GPU (0.908 -> 0.954 of the
+// copy peak without them) and no faster anywhere else.
+// HS: distance in elements between the first and the second four of an
+// 8-element unit (4 = contiguous).
+template <int VEC, int HS = 4>
+__device__ __forceinline__ void load_f32(const float *p, float (&x)[VEC]) {
   if constexpr (VEC == 1) {
     x[0] = *p;
   } else if constexpr (VEC == 2) {
-    const float2 t = __ldcs(reinterpret_cast<const float2 *>(p));
+    const float2 t = *reinterpret_cast<const float2 *>(p);
     x[0] = t.x, x[1] = t.y;
   } else {
 #pragma unroll
     for (int q = 0; q < VEC / 4; ++q) {
-      const float4 t = __ldcs(reinterpret_cast<const float4 *>(p) + q);
+      const float4 t = *reinterpret_cast<const float4 *>(p + q * HS);
       x[4 * q] = t.x, x[4 * q + 1] = t.y, x[4 * q + 2] = t.z, x[4 * q + 3] = t.w;
     }
   }
 }
-template <int VEC> __device__ __forceinline__ void store_f32(float *p, const float (&x)[VEC]) {
+template <int VEC, int HS = 4>
+__device__ __forceinline__ void store_f32(float *p, const float (&x)[VEC]) {
   if constexpr (VEC == 1) {
     *p = x[0];
   } else if constexpr (VEC == 2) {
-    __stcs(reinterpret_cast<float2 *>(p), make_float2(x[0], x[1]));
+    *reinterpret_cast<float2 *>(p) = make_float2(x[0], x[1]);
   } else {
 #pragma unroll
     for (int q = 0; q < VEC / 4; ++q)
-      __stcs(reinterpret_cast<float4 *>(p) + q,
-             make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]));
+      *reinterpret_cast<float4 *>(p + q * HS) =
+          make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
   }
 }
 
 // Store VEC updated weights at element i of every rank's gathered buffer.
 // RB as in reduce_unit.
 template <int VEC> struct Packed;  // VEC output elements as one store
-template <typename LPT, int VEC, int RB>
+template <typename LPT, int VEC, int RB, int HS = 4>
 __device__ __forceinline__ void gather_unit(const RankArgs &ra, int R, size_t i,
                                             const float (&x)[VEC]) {
   constexpr bool kExact = RB == 1 || RB == 2;
@@ -388,7 +421,7 @@ __device__ __forceinline__ void gather_unit(const RankArgs &ra, int R, size_t i,
       } else {
 #pragma unroll
         for (int j = 0; j < VEC / 4; ++j)
-          st_sys_16(dst + 4 * j,
+          st_sys_16(dst + HS * j,
                     make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
                                __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3])));
       }
@@ -412,9 +445,12 @@ __device__ __forceinline__ void gather_unit(const RankArgs &ra, int R, size_t i,
         st_sys_4(dst, h[0] | ((unsigned)h[1] << 16));
       } else if constexpr (VEC == 4) {
         st_sys_8(dst, make_uint2(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16)));
-      } else {
+      } else if constexpr (HS == 4) {
         st_sys_16(dst, make_uint4(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16),
                                   h[4] | ((unsigned)h[5] << 16), h[6] | ((unsigned)h[7] << 16)));
+      } else {
+        st_sys_8(dst, make_uint2(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16)));
+        st_sys_8(dst + HS, make_uint2(h[4] | ((unsigned)h[5] << 16), h[6] | ((unsigned)h[7] << 16)));
       }
     };
     if constexpr (RB == 0) {
@@ -544,19 +580,19 @@ __device__ __forceinline__ float lamb_r_elem(const Hyper &h, float w, float m_, 
 // one unit of the data phase
 // ---------------------------------------------------------------------------
 // SGD and Adam: whole step.  LAMB phase 1: moments + norm partials only.
-template <int OPT, typename GT, typename LPT, int VEC, int RB>
+template <int OPT, typename GT, typename LPT, int VEC, int RB, int HS = 4>
 __device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
                                           size_t lo, size_t i, double &sum_w2, double &sum_r2) {
   float g[VEC], gg[VEC], w[VEC];
-  reduce_unit<GT, VEC, RB>(ra, sa, i, g, gg);
-  load_f32<VEC>(ra.w + i, w);
+  reduce_unit<GT, VEC, RB, HS>(ra, sa, i, g, gg);
+  load_f32<VEC, HS>(ra.w + i, w);
   if constexpr (OPT == kSGD) {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) w[e] = sgd_elem(h, w[e], g[e]);
   } else {
     float m[VEC], v[VEC];
-    load_f32<VEC>(ra.m + (i - lo), m);
-    load_f32<VEC>(ra.v + (i - lo), v);
+    load_f32<VEC, HS>(ra.m + (i - lo), m);
+    load_f32<VEC, HS>(ra.v + (i - lo), v);
     float m_[VEC], v_[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) moments_elem(h, g[e], gg[e], m[e], v[e]);
@@ -576,24 +612,24 @@ __device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa
         }
       }
     }
-    store_f32<VEC>(ra.m + (i - lo), m);
-    store_f32<VEC>(ra.v + (i - lo), v);
+    store_f32<VEC, HS>(ra.m + (i - lo), m);
+    store_f32<VEC, HS>(ra.v + (i - lo), v);
   }
   if constexpr (OPT != kLAMB) {
-    if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<VEC>(ra.w + i, w);
-    gather_unit<LPT, VEC, RB>(ra, sa.world, i, w);
+    if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<VEC, HS>(ra.w + i, w);
+    gather_unit<LPT, VEC, RB, HS>(ra, sa.world, i, w);
   }
 }
 
 // LAMB phase 2: recompute r from the stored moments, apply the scaled step.
-template <typename LPT, int VEC, int RB>
+template <typename LPT, int VEC, int RB, int HS = 4>
 __device__ __forceinline__ void lamb_apply_unit(const RankArgs &ra, const StepArgs &sa,
                                                 const Hyper &h, size_t lo, size_t i,
                                                 float lr_scale) {
   float w[VEC], m[VEC], v[VEC];
-  load_f32<VEC>(ra.w + i, w);
-  load_f32<VEC>(ra.m + (i - lo), m);
-  load_f32<VEC>(ra.v + (i - lo), v);
+  load_f32<VEC, HS>(ra.w + i, w);
+  load_f32<VEC, HS>(ra.m + (i - lo), m);
+  load_f32<VEC, HS>(ra.v + (i - lo), v);
   float m_[VEC], v_[VEC];
   corrected_moments<VEC>(h, m, v, m_, v_);
 #pragma unroll
@@ -601,8 +637,8 @@ __device__ __forceinline__ void lamb_apply_unit(const RankArgs &ra, const StepAr
     const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
     w[e] = __fsub_rn(w[e], __fmul_rn(lr_scale, r));  // sample :434-435
   }
-  if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<VEC>(ra.w + i, w);
-  gather_unit<LPT, VEC, RB>(ra, sa.world, i, w);
+  if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<VEC, HS>(ra.w + i, w);
+  gather_unit<LPT, VEC, RB, HS>(ra, sa.world, i, w);
 }
 
 // ---------------------------------------------------------------------------
@@ -750,38 +786,64 @@ __device__ __forceinline__ void nvls_phase(const RankArgs &ra, const StepArgs &s
   }
 }
 
-// Grid-stride loops of the direct (register-staged) path over `nunits`
-// 4-element units starting at element `first`.
-// 16-bit gradients on a single rank use 8-element units (16-byte loads and
-// stores: +2 % there); with peers in flight the registers only allow 4
-// (8-element units measured 10 % slower at two ranks).
-template <typename GT, int RB> struct DirectVec {
-  static constexpr int kVec = (GradTraits<GT>::kIs16 && RB == 1) ? 8 : 4;
+// Grid-stride loops of the direct (register-staged) path over the elements
+// [first, first + nelems), nelems a multiple of 4.
+//
+// Unit size: 4 elements per thread and pass, except on a single rank for
+// 16-bit gradients and for SGD, which take 8 (with peers in flight the
+// registers only allow 4: 8 measured 10 % slower at two ranks; fp32 Adam on
+// one rank is 5 % faster with 4).  The 8 elements of a thread are NOT
+// consecutive: a warp's 32 units are 256 consecutive elements, of which lane
+// t takes 4t..4t+3 and 128+4t..128+4t+3, so that every load and store of the
+// warp covers one contiguous run of whole 32-byte sectors (consecutive
+// elements per lane made every fp32 access touch half sectors: 1.3 % slower).
+constexpr int kHalfStride = 128;
+template <int OPT, typename GT, int RB> struct DirectVec {
+  static constexpr int kVec = (RB == 1 && (GradTraits<GT>::kIs16 || OPT == kSGD)) ? 8 : 4;
 };
 
 template <int OPT, typename GT, typename LPT, int RB>
 __device__ __forceinline__ void direct_step(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
                                             size_t lo, size_t first, size_t nelems, size_t tid,
                                             size_t nth, double &sum_w2, double &sum_r2) {
-  constexpr int VEC = DirectVec<GT, RB>::kVec;
+  constexpr int VEC = DirectVec<OPT, GT, RB>::kVec;
   const size_t nunits = nelems / VEC;
-  for (size_t u = tid; u < nunits; u += nth)
-    step_unit<OPT, GT, LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, sum_w2, sum_r2);
-  // up to one 4-element unit may remain (nelems is a multiple of 4)
-  if (VEC == 8 && (nelems & 4) && tid == 0)
-    step_unit<OPT, GT, LPT, 4, RB>(ra, sa, h, lo, first + nunits * VEC, sum_w2, sum_r2);
+  if constexpr (VEC == 8) {
+    // tid and nth are multiples of the warp size apart from the lane, so
+    // u & 31 is the lane and u - lane the warp's first unit
+    const size_t nfull = nunits / 32 * 32;
+    for (size_t u = tid; u < nfull; u += nth)
+      step_unit<OPT, GT, LPT, 8, RB, kHalfStride>(ra, sa, h, lo, first + u * 8 - (u & 31) * 4,
+                                                  sum_w2, sum_r2);
+    for (size_t u = nfull + tid; u < nunits; u += nth)  // last, partial warp: consecutive
+      step_unit<OPT, GT, LPT, 8, RB>(ra, sa, h, lo, first + u * 8, sum_w2, sum_r2);
+    // up to one 4-element unit may remain
+    if ((nelems & 4) && tid == 0)
+      step_unit<OPT, GT, LPT, 4, RB>(ra, sa, h, lo, first + nunits * 8, sum_w2, sum_r2);
+  } else {
+    for (size_t u = tid; u < nunits; u += nth)
+      step_unit<OPT, GT, LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, sum_w2, sum_r2);
+  }
 }
 template <typename GT, typename LPT, int RB>
 __device__ __forceinline__ void direct_apply(const RankArgs &ra, const StepArgs &sa,
                                              const Hyper &h, size_t lo, size_t first,
                                              size_t nelems, size_t tid, size_t nth,
                                              float lr_scale) {
-  constexpr int VEC = DirectVec<GT, RB>::kVec;
+  constexpr int VEC = DirectVec<kLAMB, GT, RB>::kVec;
   const size_t nunits = nelems / VEC;
-  for (size_t u = tid; u < nunits; u += nth)
-    lamb_apply_unit<LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, lr_scale);
-  if (VEC == 8 && (nelems & 4) && tid == 0)
-    lamb_apply_unit<LPT, 4, RB>(ra, sa, h, lo, first + nunits * VEC, lr_scale);
+  if constexpr (VEC == 8) {
+    const size_t nfull = nunits / 32 * 32;
+    for (size_t u = tid; u < nfull; u += nth)
+      lamb_apply_unit<LPT, 8, RB, kHalfStride>(ra, sa, h, lo, first + u * 8 - (u & 31) * 4, lr_scale);
+    for (size_t u = nfull + tid; u < nunits; u += nth)
+      lamb_apply_unit<LPT, 8, RB>(ra, sa, h, lo, first + u * 8, lr_scale);
+    if ((nelems & 4) && tid == 0)
+      lamb_apply_unit<LPT, 4, RB>(ra, sa, h, lo, first + nunits * 8, lr_scale);
+  } else {
+    for (size_t u = tid; u < nunits; u += nth)
+      lamb_apply_unit<LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, lr_scale);
+  }
 }
 
 __device__ __forceinline__ double warp_sum(double x) {
