@@ -554,10 +554,10 @@ def main():
         t = ms * 1e-3
         if R == 1:
             # dram read+write of an ncu capture of this kernel on 64 Mi elements
-            # (profiles/fused_step_adam_mixed_1gpu.md): 1820.4 MB, i.e. 27.126 B per element;
+            # (profiles/fused_step_adam_mixed_1gpu.md): 1830.9 MB, i.e. 27.283 B per element;
             # traffic grows in proportion to the element count
             roof = {"bound": "hbm", "achieved": b_hbm / t / 1e9, "peak": hbm_peak, "unit": "GB/s",
-                    "frac": b_hbm / t / 1e9 / hbm_peak, "traffic": 1820.4e6 / 67108864 * N,
+                    "frac": b_hbm / t / 1e9 / hbm_peak, "traffic": 1830.9e6 / 67108864 * N,
                     "peak_kind": peak_kind, "algorithmic_bytes": b_hbm}
         else:
             # The roof is defined by the peer-to-peer algorithmic bytes per direction,
