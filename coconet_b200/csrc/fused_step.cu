@@ -1101,7 +1101,8 @@ __device__ __forceinline__ bool run_tiles(const RankArgs &ra, const StepArgs &sa
 // spilled 376 bytes and lost 6 %): kPathDirect = register-staged peer loads
 // and stores for world sizes 2..8, kPathLocal = the same for world size 1
 // (wider units), kPathNvls = NVSwitch multimem, kPathTiles = bulk-copy pipeline,
-// kPathSegments = peer-to-peer over a list of tensors (scattered calls).
+// kPathSegments .. kPathSegments + 3 = peer-to-peer over a list of tensors
+// (scattered calls), one kernel per world-size bucket.
 // Every path ends with the same scalar loop for what it does not cover.
 enum : int { kPathDirect = 0, kPathNvls = 1, kPathTiles = 2, kPathLocal = 3, kPathSegments = 4 };
 
@@ -1166,50 +1167,163 @@ __global__ void __launch_bounds__(512, 2)
   const Hyper h = make_hyper<OPT>(sa);
 
   bool seg_norm_ok = true;  // scattered LAMB: the norm exchange completed
-  if constexpr (PATH == kPathSegments) {
+  if constexpr (PATH >= kPathSegments) {
     // Scattered call: the slice is a sequence of pieces of different tensors.
     // The whole grid walks them one after the other; for each, the piece's
     // pointers replace the flat call's in the shared RankArgs and the ordinary
     // peer-to-peer loops run on it.  SGD and Adam: one pass.  LAMB: a pass for
     // the moments and every tensor's partial norms, the exchange of those
     // between the ranks, and a pass that applies each tensor's own trust ratio.
+    //
+    // SRB: the world-size bucket this kernel was built for (1, 2, <= 4, <= 8).
+    // A kernel per bucket, because one kernel holding the loops of all four
+    // spilled 400-550 bytes per thread against 16 and ran 8 % slower.
+    constexpr int SRB = PATH == kPathSegments ? 1 : PATH == kPathSegments + 1 ? 2
+                        : PATH == kPathSegments + 2 ? 4 : 8;
     __shared__ unsigned long long s_seg[3];
     __shared__ int s_last;
+    __shared__ RankArgs s_wra[16];  // LAMB's second pass: one per warp (<= 512 threads per CTA)
     const Segment *segs = ra.segs;
     const int nseg = ra.nseg;
     // Small pieces (biases, layer norms) are taken by ONE CTA each, round robin,
     // so that they proceed side by side instead of every CTA walking every
     // tiny piece; large pieces are shared by the whole grid.
     const unsigned long long small = 64ull * blockDim.x;
-    constexpr int kPasses = OPT == kLAMB ? 2 : 1;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int nwarp = (blockDim.x + 31) >> 5;
+
+    // ---- first (SGD, Adam: only) pass, CTA by CTA -------------------------------
 #pragma unroll 1
-    for (int pass = 0; pass < kPasses; ++pass) {
+    for (int sidx = 0; sidx < nseg && ok; ++sidx) {
+      const bool solo = segs[sidx].len < small;
+      if (solo && (unsigned)sidx % gridDim.x != blockIdx.x) continue;  // uniform per CTA
+      // Shared pieces start at a different CTA each time: a piece rarely is a whole
+      // number of grid passes, and without the rotation the same CTAs would always
+      // get the extra pass.
+      const size_t tid_s = solo ? threadIdx.x : (tid + (size_t)sidx * 37u * blockDim.x) % nth;
+      const size_t nth_s = solo ? blockDim.x : nth;
+      __syncthreads();  // everyone is done with the previous piece's pointers
+      if (threadIdx.x < kMaxRanks) {
+        ra.g[threadIdx.x] = segs[sidx].g[threadIdx.x];
+        ra.out[threadIdx.x] = segs[sidx].out[threadIdx.x];
+      }
+      if (threadIdx.x == 32) {
+        ra.w = segs[sidx].w, ra.m = segs[sidx].m, ra.v = segs[sidx].v;
+        ra.aligned16 = segs[sidx].aligned16;
+        s_seg[0] = segs[sidx].begin, s_seg[1] = segs[sidx].len;
+        s_seg[2] = segs[sidx].tensor_len;
+      }
+      __syncthreads();
+      const size_t seg_lo = s_seg[0], seg_len = s_seg[1];
+      const size_t nv = ra.aligned16 ? seg_len / VEC : 0;
+      Hyper hs = h;
+      if constexpr (OPT == kLAMB) hs.quirk_n = (float)s_seg[2];
+      double p_w2 = 0.0, p_r2 = 0.0;
+      direct_step<OPT, GT, LPT, SRB>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
+      for (size_t j = nv * VEC + tid_s; j < seg_len; j += nth_s)
+        step_unit<OPT, GT, LPT, 1, 0>(ra, sa, hs, seg_lo, seg_lo + j, p_w2, p_r2);
+      if constexpr (OPT == kLAMB) {
+        // this CTA's share of the piece: thread -> warp -> CTA, fixed order
+        p_w2 = warp_sum(p_w2);
+        p_r2 = warp_sum(p_r2);
+        if (lane == 0) s_red[0][wid] = p_w2, s_red[1][wid] = p_r2;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          double a = 0.0, b = 0.0;
+          for (int k = 0; k < nwarp; ++k) a += s_red[0][k], b += s_red[1][k];
+          double *slot = ra.seg_part + ((size_t)sidx * gridDim.x + blockIdx.x) * 2;
+          slot[0] = a;
+          slot[1] = b;
+        }
+      }
+    }
+
+    if constexpr (OPT == kLAMB) {
+      // ---- per-tensor norms: CTA partials -> rank (last CTA, fixed order) -> peers
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();  // this CTA's partial sums before the count
+        const unsigned prev = atomicAdd(&me->norm_count, 1u);
+        s_last = prev == gridDim.x - 1;
+        if (s_last) me->norm_count = 0;
+      }
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        for (int sidx = wid; sidx < nseg; sidx += nwarp) {  // one warp per piece
+          double a = 0.0, b = 0.0;
+          if (started_ok) {  // a rank that never started publishes zeros
+            const double *row = ra.seg_part + (size_t)sidx * gridDim.x * 2;
+            if (segs[sidx].len < small) {  // taken by one CTA
+              if (lane == 0) {
+                const unsigned c = (unsigned)sidx % gridDim.x;
+                a = ld_volatile_f64(row + 2 * c), b = ld_volatile_f64(row + 2 * c + 1);
+              }
+            } else {
+              for (unsigned c = lane; c < gridDim.x; c += 32) {
+                a += ld_volatile_f64(row + 2 * c);
+                b += ld_volatile_f64(row + 2 * c + 1);
+              }
+            }
+          }
+          a = warp_sum(a);
+          b = warp_sum(b);
+          if (lane == 0) {
+            const int t = segs[sidx].tensor;
+            for (int p = 0; p < R; ++p) {
+              volatile double *dst = tensor_norms_of(ra.flags[p])->part[rank][t];
+              dst[0] = a;
+              dst[1] = b;
+            }
+            __threadfence_system();
+          }
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < R) {
+          __threadfence_system();
+          st_release_sys(&ra.flags[threadIdx.x]->norm_flag[rank], seq);
+        }
+      }
+      // every CTA: wait (bounded) until all ranks' partials are in
+      if (threadIdx.x == 0 && ok) {
+        const int late = wait_all(me->norm_flag, R, -1, seq, sa.timeout_ns);
+        if (late >= 0) {
+          record_status(me, cocoTimeout, rank, kPhaseNorm, late, seq);
+          s_ok = 0;
+        }
+      }
+      __syncthreads();
+      ok = ok && s_ok != 0;
+
+      // ---- second pass: every tensor's own trust ratio.  No CTA-wide sum is
+      // needed here, so every WARP walks the pieces on its own, with a private
+      // copy of the pointers in shared memory and no CTA barrier (measured 12 %
+      // faster for this pass; the first pass measured slower that way).
+      if (ok) {
+        RankArgs &wra = s_wra[wid];
+        for (int q = lane; q < (int)(sizeof(RankArgs) / sizeof(int)); q += 32)
+          reinterpret_cast<int *>(&wra)[q] = reinterpret_cast<const int *>(&ra)[q];
+        __syncwarp();
 #pragma unroll 1
-      for (int sidx = 0; sidx < nseg && ok; ++sidx) {
-        const bool solo = segs[sidx].len < small;
-        if (solo && (unsigned)sidx % gridDim.x != blockIdx.x) continue;  // uniform per CTA
-        // Shared pieces start at a different CTA each time: a piece rarely is a whole
-        // number of grid passes, and without the rotation the same CTAs would always
-        // get the extra pass.
-        const size_t tid_s = solo ? threadIdx.x : (tid + (size_t)sidx * 37u * blockDim.x) % nth;
-        const size_t nth_s = solo ? blockDim.x : nth;
-        __syncthreads();  // everyone is done with the previous piece's pointers
-        if (threadIdx.x < kMaxRanks) {
-          ra.g[threadIdx.x] = segs[sidx].g[threadIdx.x];
-          ra.out[threadIdx.x] = segs[sidx].out[threadIdx.x];
-        }
-        if (threadIdx.x == 32) {
-          ra.w = segs[sidx].w, ra.m = segs[sidx].m, ra.v = segs[sidx].v;
-          ra.aligned16 = segs[sidx].aligned16;
-          s_seg[0] = segs[sidx].begin, s_seg[1] = segs[sidx].len;
-          s_seg[2] = segs[sidx].tensor_len;
-        }
-        if constexpr (OPT == kLAMB) {
-          if (pass == 1 && threadIdx.x == 0) {
+        for (int sidx = 0; sidx < nseg; ++sidx) {
+          const unsigned long long seg_len = segs[sidx].len;  // the same address in every lane
+          const bool solo = seg_len < small;
+          if (solo && (unsigned)sidx % gridDim.x != blockIdx.x) continue;
+          const size_t tid_s = solo ? threadIdx.x : (tid + (size_t)sidx * 37u * blockDim.x) % nth;
+          const size_t nth_s = solo ? blockDim.x : nth;
+          __syncwarp();  // every lane is done with the previous piece's pointers
+          if (lane < kMaxRanks) {
+            wra.g[lane] = segs[sidx].g[lane];
+            wra.out[lane] = segs[sidx].out[lane];
+          } else if (lane == kMaxRanks) {
+            wra.w = segs[sidx].w, wra.m = segs[sidx].m, wra.v = segs[sidx].v;
+          }
+          const size_t seg_lo = segs[sidx].begin;
+          const size_t nv = segs[sidx].aligned16 ? seg_len / VEC : 0;
+          float lr_scale = 0.f;
+          if (lane == 0) {
             // this tensor's norms: the partials of the ranks that hold a part of
-            // it, in rank order (thread 0 is the one that waited for them)
+            // it, in rank order, so that every replica computes the same ratio
             TensorNorms *tn = tensor_norms_of(me);
             const int t = segs[sidx].tensor;
             double w2 = 0.0, r2 = 0.0;
@@ -1227,111 +1341,13 @@ __global__ void __launch_bounds__(512, 2)
               wn = sqrt(w2);
               sc = (wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0;
             }
-            s_lr_scale = __fmul_rn(sa.lr, (float)sc);
+            lr_scale = __fmul_rn(sa.lr, (float)sc);
           }
-        }
-        __syncthreads();
-        const size_t seg_lo = s_seg[0], seg_len = s_seg[1];
-        const size_t nv = ra.aligned16 ? seg_len / VEC : 0;
-        Hyper hs = h;
-        if constexpr (OPT == kLAMB) hs.quirk_n = (float)s_seg[2];
-        if (pass == 0) {
-          double p_w2 = 0.0, p_r2 = 0.0;
-          if (R == 1)
-            direct_step<OPT, GT, LPT, 1>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
-          else if (R == 2)
-            direct_step<OPT, GT, LPT, 2>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
-          else if (R <= 4)
-            direct_step<OPT, GT, LPT, 4>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
-          else
-            direct_step<OPT, GT, LPT, 8>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, p_w2, p_r2);
+          lr_scale = __shfl_sync(0xffffffffu, lr_scale, 0);
+          __syncwarp();
+          direct_apply<GT, LPT, SRB>(wra, sa, h, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
           for (size_t j = nv * VEC + tid_s; j < seg_len; j += nth_s)
-            step_unit<OPT, GT, LPT, 1, 0>(ra, sa, hs, seg_lo, seg_lo + j, p_w2, p_r2);
-          if constexpr (OPT == kLAMB) {
-            // this CTA's share of the piece: thread -> warp -> CTA, fixed order
-            p_w2 = warp_sum(p_w2);
-            p_r2 = warp_sum(p_r2);
-            if (lane == 0) s_red[0][wid] = p_w2, s_red[1][wid] = p_r2;
-            __syncthreads();
-            if (threadIdx.x == 0) {
-              double a = 0.0, b = 0.0;
-              for (int k = 0; k < nwarp; ++k) a += s_red[0][k], b += s_red[1][k];
-              double *slot = ra.seg_part + ((size_t)sidx * gridDim.x + blockIdx.x) * 2;
-              slot[0] = a;
-              slot[1] = b;
-            }
-          }
-        } else if constexpr (OPT == kLAMB) {
-          const float lr_scale = s_lr_scale;
-          if (R == 1)
-            direct_apply<GT, LPT, 1>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
-          else if (R == 2)
-            direct_apply<GT, LPT, 2>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
-          else if (R <= 4)
-            direct_apply<GT, LPT, 4>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
-          else
-            direct_apply<GT, LPT, 8>(ra, sa, hs, seg_lo, seg_lo, nv * VEC, tid_s, nth_s, lr_scale);
-          for (size_t j = nv * VEC + tid_s; j < seg_len; j += nth_s)
-            lamb_apply_unit<LPT, 1, 0>(ra, sa, hs, seg_lo, seg_lo + j, lr_scale);
-        }
-      }
-      if constexpr (OPT == kLAMB) {
-        if (pass == 0) {
-          // ---- per-tensor norms: CTA partials -> rank (last CTA, fixed order) -> peers
-          __syncthreads();
-          if (threadIdx.x == 0) {
-            __threadfence();  // this CTA's partial sums before the count
-            const unsigned prev = atomicAdd(&me->norm_count, 1u);
-            s_last = prev == gridDim.x - 1;
-            if (s_last) me->norm_count = 0;
-          }
-          __syncthreads();
-          if (s_last) {
-            __threadfence();
-            for (int sidx = wid; sidx < nseg; sidx += nwarp) {  // one warp per piece
-              double a = 0.0, b = 0.0;
-              if (started_ok) {  // a rank that never started publishes zeros
-                const double *row = ra.seg_part + (size_t)sidx * gridDim.x * 2;
-                if (segs[sidx].len < small) {  // taken by one CTA
-                  if (lane == 0) {
-                    const unsigned c = (unsigned)sidx % gridDim.x;
-                    a = ld_volatile_f64(row + 2 * c), b = ld_volatile_f64(row + 2 * c + 1);
-                  }
-                } else {
-                  for (unsigned c = lane; c < gridDim.x; c += 32) {
-                    a += ld_volatile_f64(row + 2 * c);
-                    b += ld_volatile_f64(row + 2 * c + 1);
-                  }
-                }
-              }
-              a = warp_sum(a);
-              b = warp_sum(b);
-              if (lane == 0) {
-                const int t = segs[sidx].tensor;
-                for (int p = 0; p < R; ++p) {
-                  volatile double *dst = tensor_norms_of(ra.flags[p])->part[rank][t];
-                  dst[0] = a;
-                  dst[1] = b;
-                }
-                __threadfence_system();
-              }
-            }
-            __syncthreads();
-            if ((int)threadIdx.x < R) {
-              __threadfence_system();
-              st_release_sys(&ra.flags[threadIdx.x]->norm_flag[rank], seq);
-            }
-          }
-          // every CTA: wait (bounded) until all ranks' partials are in
-          if (threadIdx.x == 0 && ok) {
-            const int late = wait_all(me->norm_flag, R, -1, seq, sa.timeout_ns);
-            if (late >= 0) {
-              record_status(me, cocoTimeout, rank, kPhaseNorm, late, seq);
-              s_ok = 0;
-            }
-          }
-          __syncthreads();
-          ok = ok && s_ok != 0;
+            lamb_apply_unit<LPT, 1, 0>(wra, sa, h, seg_lo, seg_lo + j, lr_scale);
         }
       }
     }
@@ -1339,7 +1355,7 @@ __global__ void __launch_bounds__(512, 2)
     ok = false;  // nothing is left for the flat-slice code below
     __syncthreads();
   }
-  const bool seg_done = PATH == kPathSegments;
+  const bool seg_done = PATH >= kPathSegments;
 
   // Full tiles go through the bulk-copy pipeline; what is left of the slice
   // (and everything, when the slice or a pointer is not 16-byte aligned) is
@@ -1393,7 +1409,7 @@ __global__ void __launch_bounds__(512, 2)
       step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, lo, lo + j, sum_w2, sum_r2);
   }
 
-  if constexpr (OPT == kLAMB && PATH != kPathSegments) {
+  if constexpr (OPT == kLAMB && PATH < kPathSegments) {
     // ---- norms: thread -> warp -> CTA -> rank (fixed order) -> all ranks ---
     sum_w2 = warp_sum(sum_w2);
     sum_r2 = warp_sum(sum_r2);
@@ -1527,7 +1543,16 @@ template <int OPT, typename GT, typename LPT> KernelPtr pick_path(int path) {
     case kPathNvls: return fused_step_kernel<OPT, GT, LPT, kPathNvls>;
     case kPathTiles: return fused_step_kernel<OPT, GT, LPT, kPathTiles>;
     case kPathLocal: return fused_step_kernel<OPT, GT, LPT, kPathLocal>;
-    case kPathSegments: return fused_step_kernel<OPT, GT, LPT, kPathSegments>;
+    case kPathSegments:
+    case kPathSegments + 1:
+    case kPathSegments + 2:
+    case kPathSegments + 3:
+      // lists of tensors gather fp32 weights only: no low-precision variants
+      if constexpr (!std::is_same<LPT, NoLp>::value) return nullptr;
+      else if (path == kPathSegments) return fused_step_kernel<OPT, GT, LPT, kPathSegments>;
+      else if (path == kPathSegments + 1) return fused_step_kernel<OPT, GT, LPT, kPathSegments + 1>;
+      else if (path == kPathSegments + 2) return fused_step_kernel<OPT, GT, LPT, kPathSegments + 2>;
+      else return fused_step_kernel<OPT, GT, LPT, kPathSegments + 3>;
     default: return fused_step_kernel<OPT, GT, LPT, kPathDirect>;
   }
 }
@@ -1584,7 +1609,8 @@ KernelPtr pick(int opt, cocoDataType_t g, bool has_lp, cocoDataType_t lp, int pa
 // the tile pipeline when it was given stages, else the register-staged path.
 int path_of(const StepArgs &sa, const RankArgs &ra) {
   (void)ra;
-  if (sa.flags & kFlagScattered) return kPathSegments;
+  if (sa.flags & kFlagScattered)  // one kernel per world-size bucket: 1, 2, <= 4, <= 8
+    return kPathSegments + (sa.world == 1 ? 0 : sa.world == 2 ? 1 : sa.world <= 4 ? 2 : 3);
   if (sa.flags & kFlagNvls) return kPathNvls;
   if (sa.pipe_stages > 0) return kPathTiles;
   return sa.world == 1 ? kPathLocal : kPathDirect;
