@@ -20,10 +20,12 @@ from .runtime import (  # noqa: F401
     library_path,
     rendezvous_address,
     scattered_slice_elems,
+    scattered_tensor_place,
     slice_bounds,
 )
 
 __all__ = [
     "CocoError", "Communicator", "HostBootstrap", "VARIANT_DSL", "VARIANT_NCCL", "VARIANT_OVERLAP",
-    "LAMB_REF_QUIRK", "group", "lib", "library_path", "rendezvous_address", "scattered_slice_elems", "slice_bounds",
+    "LAMB_REF_QUIRK", "group", "lib", "library_path", "rendezvous_address", "scattered_slice_elems", "scattered_tensor_place",
+    "slice_bounds",
 ]

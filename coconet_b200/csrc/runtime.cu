@@ -1186,6 +1186,22 @@ int cocoScatteredSliceElems(size_t nbuff, const size_t *counts, int world, size_
   return cocoSuccess;
 }
 
+int cocoScatteredTensorPlace(size_t nbuff, const size_t *counts, int world, size_t tensor,
+                             size_t *flat_offset, int *first_rank, int *last_rank) {
+  if (!counts || !flat_offset || !first_rank || !last_rank || world < 1 || world > kMaxRanks ||
+      tensor >= nbuff)
+    return cocoInvalidArgument;
+  const FlatLayout L = flat_layout(counts, nbuff, world);
+  *flat_offset = L.off[tensor];
+  if (counts[tensor] == 0) {
+    *first_rank = *last_rank = -1;
+  } else {  // the same arithmetic as build_segments
+    *first_rank = (int)(L.off[tensor] / L.slice);
+    *last_rank = (int)((L.off[tensor] + counts[tensor] - 1) / L.slice);
+  }
+  return cocoSuccess;
+}
+
 static int enqueue_scattered(cocoComm_t comm, int opt, size_t nbuff, const void *const *g,
                              cocoDataType_t g_type, float *const *w, const size_t *counts,
                              float *m, float *v, PendingCall &pc, cocoStream_t stream) {

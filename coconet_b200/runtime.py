@@ -73,6 +73,9 @@ _SIGNATURES = {
                                       C.c_void_p]),
     "cocoScatteredSliceElems": (C.c_int, [C.c_size_t, C.POINTER(C.c_size_t), C.c_int,
                                           C.POINTER(C.c_size_t)]),
+    "cocoScatteredTensorPlace": (C.c_int, [C.c_size_t, C.POINTER(C.c_size_t), C.c_int, C.c_size_t,
+                                           C.POINTER(C.c_size_t), C.POINTER(C.c_int),
+                                           C.POINTER(C.c_int)]),
     "cocoFusedSGDScattered": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_int,
                                         C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_float,
                                         C.c_float, C.c_void_p]),
@@ -127,6 +130,16 @@ def error_string(code):
 def _check(code, what):
     if code != 0:
         raise CocoError(code, what)
+
+
+def scattered_tensor_place(counts, world, tensor):
+    """(flat_offset, first_rank, last_rank) of one tensor of a list in the flat
+    Sliced moments of the scattered calls."""
+    arr = (C.c_size_t * len(counts))(*counts)
+    off, r0, r1 = C.c_size_t(), C.c_int(), C.c_int()
+    _check(lib().cocoScatteredTensorPlace(len(counts), arr, world, tensor, C.byref(off),
+                                          C.byref(r0), C.byref(r1)), "cocoScatteredTensorPlace")
+    return off.value, r0.value, r1.value
 
 
 def scattered_slice_elems(counts, world):

@@ -258,6 +258,15 @@ int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *w, void *w_
  * cocoFusedLAMB's arithmetic, `flags` included.  At most COCO_MAX_LAMB_TENSORS
  * tensors per call. */
 int cocoScatteredSliceElems(size_t nbuff, const size_t *counts, int world, size_t *slice_elems);
+/* Where tensor `tensor` of such a list lives in the flat Sliced moments (host
+ * only, no GPU needed; e.g. to save or reload the optimizer state of one layer):
+ * element e of the tensor is element flat_offset + e of the virtual flat buffer,
+ * i.e. element (flat_offset + e) % slice_elems of m / v on rank
+ * (flat_offset + e) / slice_elems; first_rank..last_rank are the ranks that hold
+ * a part of it (first_rank = last_rank = -1 for an empty tensor).  No reference
+ * counterpart: the fork indexes full-size moment arrays by global element. */
+int cocoScatteredTensorPlace(size_t nbuff, const size_t *counts, int world, size_t tensor,
+                             size_t *flat_offset, int *first_rank, int *last_rank);
 int cocoFusedSGDScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
                           cocoDataType_t g_type, float *const *w, const size_t *counts, float lr,
                           float grad_scale, cocoStream_t stream);

@@ -49,6 +49,29 @@ def test_slice_bounds_partition(n, R):
         coco.slice_bounds(n, R, R)
 
 
+@pytest.mark.parametrize("R", [1, 2, 3, 8])
+def test_scattered_layout_places_every_tensor(R):
+    # the flat layout of a list of tensors: 8-element alignment per tensor, slices a
+    # multiple of 8, every element of every tensor on exactly one rank
+    counts = [1000, 8, 3, 0, 4096, 70001, 2, 1, (1 << 19) + 5, 24]
+    S = coco.scattered_slice_elems(counts, R)
+    at = 0
+    owned = [0] * R
+    for b, c in enumerate(counts):
+        off, r0, r1 = coco.scattered_tensor_place(counts, R, b)
+        assert off == at and off % 8 == 0
+        if c == 0:
+            assert (r0, r1) == (-1, -1)
+        else:
+            assert (r0, r1) == (off // S, (off + c - 1) // S) and 0 <= r0 <= r1 < R
+            for r in range(r0, r1 + 1):
+                owned[r] += max(0, min(off + c, (r + 1) * S) - max(off, r * S))
+        at += (c + 7) // 8 * 8
+    assert S % 8 == 0 and S * R >= at and sum(owned) == sum(counts) and max(owned) <= S
+    with pytest.raises(coco.CocoError):
+        coco.scattered_tensor_place(counts, R, len(counts))
+
+
 def test_null_handles_are_rejected_not_dereferenced():
     import ctypes as C
     L = coco.lib()
