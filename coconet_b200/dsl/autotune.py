@@ -7,6 +7,11 @@ each schedule, runs it on the GPUs of this node and reports the fastest:
 
     python -m coconet_b200.dsl.autotune adam --gpus 8 --log2 26 --epochs 20
 
+With --derive the three programs come from ONE DSL program written with
+AllReduce: the C++ `Autotuner` (pipeline.hpp) derives RS_C_AG and fuse_RS_C_AG
+from it with split / reorder / asSlice / fuse and emits all three; without it
+each schedule is the hand-written variant in dsl/examples/optimizers.cpp.
+
 Every schedule runs as plain C++ processes (one per GPU, started by
 torch.distributed.run --no-python); times are the programs' own CUDA-event
 totals from their "{SZ: .., Total: ..}" report line.
@@ -26,10 +31,14 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 SCHEDULES = ["AR_C", "RS_C_AG", "fuse_RS_C_AG"]
 
 
-def build(opt, schedule, workdir):
+def build(opt, schedule, workdir, derive=False):
     subprocess.check_call(["make", "-C", HERE, "-s"])
     src = os.path.join(workdir, f"{opt}-{schedule}.cu")
-    subprocess.check_call([os.path.join(HERE, "build", "optimizers"), opt, schedule, src])
+    if not derive:
+        subprocess.check_call([os.path.join(HERE, "build", "optimizers"), opt, schedule, src])
+    elif not os.path.exists(src):   # one call emits all three schedules
+        subprocess.check_call([os.path.join(HERE, "build", "optimizers"), opt, "autotune", workdir],
+                              stdout=subprocess.DEVNULL)
     exe = os.path.join(workdir, f"{opt}-{schedule}")
     libdir = os.path.join(ROOT, "coconet_b200")
     libs = ["-lcoconet_rt", "-lcurand"] + (["-lnccl"] if "COCONET_USE_NCCL" in open(src).read() else [])
@@ -57,19 +66,19 @@ def run(exe, gpus, log2, epochs, env):
     return float(m.group(4)), stages
 
 
-def autotune(opt, gpus, log2, epochs, scalars=None):
+def autotune(opt, gpus, log2, epochs, scalars=None, derive=False):
     env = dict(os.environ)
     env.update({f"COCONET_SCALAR_{k}": str(v) for k, v in (scalars or {}).items()})
     results = []
     with tempfile.TemporaryDirectory() as work:
         for schedule in SCHEDULES:
-            exe = build(opt, schedule, work)
+            exe = build(opt, schedule, work, derive)
             run(exe, gpus, log2, 2, env)                       # warm-up: first-call costs
             total, stages = run(exe, gpus, log2, epochs, env)
             results.append({"schedule": schedule, "ms_per_step": total / epochs, "stages_ms": stages})
     best = min(results, key=lambda r: r["ms_per_step"])
     return {"program": opt, "gpus": gpus, "elements": 1 << log2, "epochs": epochs, "results": results,
-            "best": best["schedule"]}
+            "best": best["schedule"], "schedules": "derived" if derive else "hand-written"}
 
 
 if __name__ == "__main__":
@@ -78,6 +87,9 @@ if __name__ == "__main__":
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--log2", type=int, default=24, help="log2 of the element count")
     ap.add_argument("--epochs", type=int, default=20)
+    ap.add_argument("--derive", action="store_true",
+                    help="derive the schedules from the AllReduce program with the C++ Autotuner")
     a = ap.parse_args()
     print(json.dumps(autotune(a.program, a.gpus, a.log2, a.epochs,
-                              {"beta1": 0.9, "beta2": 0.999, "lr": 0.01, "decay": 0.01, "mu": 0.9})))
+                              {"beta1": 0.9, "beta2": 0.999, "lr": 0.01, "decay": 0.01, "mu": 0.9},
+                              derive=a.derive)))

@@ -4,6 +4,8 @@
 //   RS_C_AG       ReduceScatter, update of the rank's slice, AllGather
 //   fuse_RS_C_AG  the same, fused into one kernel (the B200 runtime's path)
 // usage: optimizers <sgd|adam|lamb|nesterov> <AR_C|RS_C_AG|fuse_RS_C_AG> [output.cu]
+//        optimizers <sgd|adam|lamb|nesterov> autotune [output directory]
+//          (the program written once with AllReduce; the three schedules are derived)
 #include <dsl.hpp>
 #include <pipeline.hpp>
 
@@ -12,15 +14,25 @@
 
 using namespace ACCCDSL;
 
+// `autotune`: the program as written with AllReduce; the Autotuner derives and
+// emits the three schedules into the directory `dir`.
+static void derive_all(Pipeline &pipeline, std::vector<Tensor> state, const std::string &dir) {
+  Autotuner tuner;
+  tuner.setOutputDir(dir);
+  tuner.autotune(pipeline, state);
+  for (const std::string &f : tuner.emitted()) std::cout << f << std::endl;
+}
+
 static void sgd(const std::string &schedule, const std::string &out) {
   Variable N(Int32, "N");
   Variable lr(Float32, "lr");
   Tensor g(Float32, N, Local, "g");
   Tensor w(Float32, N, Replicated, "w");
-  if (schedule == "AR_C") {
+  if (schedule == "AR_C" || schedule == "autotune") {
     Stage gsum = AllReduce(Summation, g);
     Stage wnew = Update(w, w - lr * gsum);
     Pipeline pipeline("sgd", {g, w, lr}, {wnew});
+    if (schedule == "autotune") return derive_all(pipeline, {}, out);
     pipeline.codegen(out);
     return;
   }
@@ -37,7 +49,7 @@ static void adam(const std::string &schedule, const std::string &out) {
   Variable lr(Float32, "lr"), beta1(Float32, "beta1"), beta2(Float32, "beta2");
   Tensor g(Float32, N, Local, "g");
   Tensor w(Float32, N, Replicated, "w");
-  const bool sliced = schedule != "AR_C";
+  const bool sliced = schedule != "AR_C" && schedule != "autotune";
   Tensor m(Float32, N, sliced ? Sliced : Replicated, "m");
   Tensor v(Float32, N, sliced ? Sliced : Replicated, "v");
   Stage gred = sliced ? Stage(ReduceScatter(Summation, g)) : Stage(AllReduce(Summation, g));
@@ -48,6 +60,7 @@ static void adam(const std::string &schedule, const std::string &out) {
   if (!sliced) {
     Stage wnew = Update(w, w - lr * mhat / vhat);
     Pipeline pipeline("adam", {g, w, m, v, lr, beta1, beta2}, {mnew, vnew, wnew});
+    if (schedule == "autotune") return derive_all(pipeline, {m, v}, out);
     pipeline.fuse({mnew, vnew, mhat, vhat, wnew});
     pipeline.codegen(out);
     return;
@@ -68,7 +81,7 @@ static void lamb(const std::string &schedule, const std::string &out) {
   Variable decay(Float32, "decay");
   Tensor g(Float32, N, Local, "g");
   Tensor w(Float32, N, Replicated, "w");
-  const bool sliced = schedule != "AR_C";
+  const bool sliced = schedule != "AR_C" && schedule != "autotune";
   Tensor m(Float32, N, sliced ? Sliced : Replicated, "m");
   Tensor v(Float32, N, sliced ? Sliced : Replicated, "v");
   Stage gred = sliced ? Stage(ReduceScatter(Summation, g)) : Stage(AllReduce(Summation, g));
@@ -83,6 +96,7 @@ static void lamb(const std::string &schedule, const std::string &out) {
   if (!sliced) {
     Stage wnew = Update(w, wstep);
     Pipeline pipeline("lamb", {g, w, m, v, lr, beta1, beta2, decay}, {wnew});
+    if (schedule == "autotune") return derive_all(pipeline, {m, v}, out);
     pipeline.fuse({mnew, vnew, mhat, vhat, r, rnorm, wnorm, wstep, wnew});
     pipeline.codegen(out);
     return;
@@ -148,13 +162,14 @@ static void nesterov(const std::string &schedule, const std::string &out) {
   Variable lr(Float32, "lr"), mu(Float32, "mu");
   Tensor g(Float32, N, Local, "g");
   Tensor w(Float32, N, Replicated, "w");
-  const bool sliced = schedule != "AR_C";
+  const bool sliced = schedule != "AR_C" && schedule != "autotune";
   Tensor mom(Float32, N, sliced ? Sliced : Replicated, "mom");
   if (!sliced) {
     Stage gsum = AllReduce(Summation, g);
     Stage mnew = Update(mom, mu * mom + gsum);
     Stage wnew = Update(w, w - lr * (gsum + mu * mnew));
     Pipeline pipeline("nesterov", {g, w, mom, lr, mu}, {mnew, wnew});
+    if (schedule == "autotune") return derive_all(pipeline, {mom}, out);
     pipeline.fuse({mnew, wnew});
     pipeline.codegen(out);
     return;
@@ -177,11 +192,12 @@ int main(int argc, char **argv) {
     return 1;
   }
   const std::string opt = argv[1], schedule = argv[2];
-  if (schedule != "AR_C" && schedule != "RS_C_AG" && schedule != "fuse_RS_C_AG") {
+  if (schedule != "AR_C" && schedule != "RS_C_AG" && schedule != "fuse_RS_C_AG" && schedule != "autotune") {
     std::cout << "Invalid schedule" << std::endl;
     return 1;
   }
-  const std::string out = argc > 3 ? argv[3] : opt + "-" + schedule + ".cu";
+  // for `autotune` the third argument is the output DIRECTORY (default: the current one)
+  const std::string out = argc > 3 ? argv[3] : schedule == "autotune" ? "." : opt + "-" + schedule + ".cu";
   if (opt == "sgd") sgd(schedule, out);
   else if (opt == "adam") adam(schedule, out);
   else if (opt == "lamb") lamb(schedule, out);

@@ -43,6 +43,8 @@ class Pipeline {
   void fuse(const std::vector<Stage> &stages);
   // Non-aborting form of the same check.
   bool canFuse(const std::vector<NodeRef> &stages, std::string *why = nullptr) const;
+  // Dissolve every fusion group (each stage on its own again).
+  void unfuse() { fused_.clear(); }
 
   // ---- schedule transformations: AR_C -> RS_C_AG -> fused, without rewriting the program ----
   // split(AllReduceRSAG): the AllReduce stage becomes ReduceScatter + AllGather.
@@ -78,6 +80,30 @@ class Pipeline {
   std::vector<NodeRef> stages_;
   std::vector<std::set<const Node *>> fused_;
   void rediscover();  // recompute stages_ after a transformation
+};
+
+// Derives the schedules of the CoCoNet paper from ONE pipeline written as
+// AllReduce + computation, and emits a program for each (surface of the
+// reference's src/pipeline.hpp:675-684; there it enumerates and prints):
+//   <dir>/<name>-AR_C.cu          as written, computations fused into kernels
+//   <dir>/<name>-RS_C_AG.cu       split + reorder + asSlice(canSlice)
+//   <dir>/<name>-fuse_RS_C_AG.cu  everything fused into one kernel
+// The programs are timed by building and running them (python -m
+// coconet_b200.dsl.autotune --derive ...): measuring needs the GPUs, emitting
+// does not.  The pipeline is left in its last (fused) schedule.
+class Autotuner {
+ public:
+  Autotuner() {}
+  void setOutputDir(const std::string &dir) { dir_ = dir; }
+  void autotune(Pipeline &pipeline) { autotune(pipeline, std::vector<Tensor>()); }
+  // canSlice: Replicated tensors that only the update itself reads and writes
+  // (optimizer state): they become Sliced in the last two schedules.
+  void autotune(Pipeline &pipeline, std::vector<Tensor> canSlice);
+  const std::vector<std::string> &emitted() const { return emitted_; }  // files written
+
+ private:
+  std::string dir_ = ".";
+  std::vector<std::string> emitted_;
 };
 
 }  // namespace ACCCDSL

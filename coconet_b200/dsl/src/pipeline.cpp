@@ -419,9 +419,10 @@ ReorderedStages Pipeline::reorder(std::vector<Stage> comps, Stage allGather) {
     if (!members.count(s.get())) continue;
     std::vector<NodeRef> own;
     ownedNodes(s, true, &own);
+    // Pointwise stages move; so does a Norm, which means the norm of the whole
+    // (distributed) tensor whether its operand is gathered or still in slices.
     for (const NodeRef &n : own)
-      if (isCollective(n->kind) || n->kind == NodeKind::Norm)
-        fail("reorder: stage " + s->name + " is not pointwise");
+      if (isCollective(n->kind)) fail("reorder: stage " + s->name + " contains a collective");
     for (const auto &sub : subs) substitute(s, sub.first, sub.second, true);
     if (s->kind == NodeKind::Update && s->in[0]->layout == Replicated && s->in[1]->layout == Sliced) {
       // Update(w, f(gathered)) -> c = f(slice); Update(w, AllGather(c))
@@ -442,6 +443,9 @@ ReorderedStages Pipeline::reorder(std::vector<Stage> comps, Stage allGather) {
       subs.push_back({s, comp});
       out.compStages.push_back(Stage(Expression(comp)));
       out.allGatherStages.push_back(Stage(Expression(s)));
+      // Later stages now read the slice computation, not this Update: it stays
+      // part of the pipeline for its effect on the tensor.
+      if (std::find(outputs_.begin(), outputs_.end(), s) == outputs_.end()) outputs_.push_back(s);
     } else {
       out.compStages.push_back(Stage(Expression(s)));
     }
@@ -499,6 +503,75 @@ void Pipeline::asSlice(std::vector<Tensor> tensors) {
     }
   }
   rediscover();
+}
+
+void Autotuner::autotune(Pipeline &p, std::vector<Tensor> canSlice) {
+  auto as_stages = [](const std::vector<NodeRef> &v) {
+    std::vector<Stage> out;
+    for (const NodeRef &n : v) out.push_back(Stage(Expression(n)));
+    return out;
+  };
+  auto emit = [&](const std::string &schedule) {
+    const std::string file = dir_ + "/" + p.name() + "-" + schedule + ".cu";
+    p.codegen(file);
+    emitted_.push_back(file);
+  };
+  // ---- AR_C: as written; every computation stage in one fusion group -----------
+  NodeRef ar;
+  std::vector<NodeRef> comps;
+  for (const NodeRef &s : p.stages()) {
+    if (s->kind == NodeKind::AllReduce) {
+      if (ar) fail("autotune: pipeline '" + p.name() + "' has more than one AllReduce");
+      ar = s;
+    } else if (isCollective(s->kind)) {
+      fail("autotune: write the pipeline with AllReduce only; the other schedules are derived");
+    } else {
+      comps.push_back(s);
+    }
+  }
+  if (!ar) fail("autotune: pipeline '" + p.name() + "' has no AllReduce stage");
+  if (comps.size() > 1) p.fuse(as_stages(comps));
+  emit("AR_C");
+  p.unfuse();  // the groups of this schedule do not carry over: the stages change
+
+  // ---- RS_C_AG: split, move every consumer below the AllGather, slice the state --
+  std::pair<Stage, Stage> rsag = p.split(Stage(Expression(ar)), AllReduceRSAG);
+  std::vector<Stage> consumers;  // stages that depend on the gathered sum, directly or not
+  {
+    std::set<const Node *> dep = {rsag.second.node().get()};
+    for (const NodeRef &s : p.stages()) {
+      if (dep.count(s.get())) continue;
+      std::vector<const Node *> d;
+      direct_deps(s, true, &d);
+      for (const Node *x : d)
+        if (dep.count(x)) {
+          dep.insert(s.get());
+          consumers.push_back(Stage(Expression(s)));
+          break;
+        }
+    }
+  }
+  ReorderedStages re = p.reorder(consumers, rsag.second);
+  if (!canSlice.empty()) p.asSlice(canSlice);
+  std::set<const Node *> gathers;
+  for (const Stage &s : re.allGatherStages)
+    if (s.node()->in[1]->kind == NodeKind::AllGather) gathers.insert(s.node().get());  // not sliced away
+  std::vector<NodeRef> kernel;
+  for (const NodeRef &s : p.stages())
+    if (!isCollective(s->kind) && !gathers.count(s.get())) kernel.push_back(s);
+  if (kernel.size() > 1) p.fuse(as_stages(kernel));
+  emit("RS_C_AG");
+
+  // ---- fuse_RS_C_AG: one kernel ----------------------------------------------------
+  std::vector<NodeRef> all = p.stages();
+  std::string why;
+  if (!p.canFuse(all, &why)) {
+    std::cerr << "coconet dsl: autotune: the fused schedule of '" << p.name()
+              << "' is not emitted: " << why << std::endl;
+    return;
+  }
+  p.fuse(as_stages(all));
+  emit("fuse_RS_C_AG");
 }
 
 void Pipeline::print(std::ostream &os) const {

@@ -199,13 +199,24 @@ def test_transformations_refuse_what_would_change_the_result(dsl_build, tmp_path
   auto rsag = p.split(s, AllReduceRSAG);
   p.reorder({wn}, rsag.second);''')
     assert out.returncode != 0 and "also uses the AllGather" in out.stderr
-    # a stage with a norm is not pointwise
+    # a Norm moves too: it is the norm of the whole tensor, gathered or in slices
     out = _run_dsl_program(tmp_path, '''
-  Stage s = AllReduce(Summation, g); Stage wn = Update(w, w - lr * s / Norm(s));
+  Stage s = AllReduce(Summation, g); Stage u = lr * s; Stage nrm = Norm(u);
+  Stage wn = Update(w, w - u / nrm);
   Pipeline p("p", {g, w, lr}, {wn});
   auto rsag = p.split(s, AllReduceRSAG);
+  p.reorder({u, nrm, wn}, rsag.second);
+  p.codegen("norm.cu");''')
+    assert out.returncode == 0, out.stderr
+    assert "coconetSumOverRanks" in (tmp_path / "norm.cu").read_text()   # per-rank partial sums
+    # ... but a stage that contains a collective does not
+    out = _run_dsl_program(tmp_path, '''
+  Tensor g2(Float32, N, Local, "g2");
+  Stage s = AllReduce(Summation, g); Stage wn = Update(w, w - lr * s * AllReduce(Summation, g2));
+  Pipeline p("p", {g, g2, w, lr}, {wn});
+  auto rsag = p.split(s, AllReduceRSAG);
   p.reorder({wn}, rsag.second);''')
-    assert out.returncode != 0 and "not pointwise" in out.stderr
+    assert out.returncode != 0 and "contains a collective" in out.stderr
     # asSlice of a tensor that a stage still computes on whole
     out = _run_dsl_program(tmp_path, '''
   Stage s = AllReduce(Summation, g); Stage mn = Update(m, m + s); Stage wn = Update(w, w - lr * mn);
@@ -226,3 +237,47 @@ def test_transformations_refuse_what_would_change_the_result(dsl_build, tmp_path
     assert out.stdout.split()[:3] == ["2", "2", "11"]
     text = (tmp_path / "seq.cu").read_text()
     assert "cocoReduceScatter(" in text and text.count("cocoAllGather(") == 1
+
+
+@pytest.mark.parametrize("opt", ["sgd", "adam", "lamb", "nesterov"])
+def test_autotuner_derives_the_three_schedules_from_the_allreduce_program(dsl_build, tmp_path, opt):
+    """`Autotuner::autotune(pipeline, canSlice)` (reference surface:
+    src/pipeline.hpp:675-684) on a program written once with AllReduce: three
+    programs come out, the fused one makes the same runtime call as the
+    hand-written fused schedule, the unfused ones use the runtime's collectives,
+    and all compile."""
+    out = subprocess.run([os.path.join(dsl_build, "optimizers"), opt, "autotune", str(tmp_path)],
+                         capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    files = out.stdout.split()
+    assert [os.path.basename(f) for f in files] == [f"{opt}-{s}.cu" for s in
+                                                    ("AR_C", "RS_C_AG", "fuse_RS_C_AG")]
+    ar, rs, fused = (open(f).read() for f in files)
+    assert "cocoAllReduce(comm, g, N, stream)" in ar and "cocoFused" not in ar
+    assert "cocoReduceScatter(comm, g, g + (size_t)DIVUP(N, comm_size) * rank, N, stream)" in rs
+    assert rs.count("cocoAllGather(comm, ") == 1 and "cocoFused" not in rs
+    (tmp_path / "hand").mkdir()
+    hand = _gen(dsl_build, opt, "fuse_RS_C_AG", tmp_path / "hand")
+    call = [ln.strip() for ln in hand.splitlines() if "COCOCHECK(cocoFused" in ln]
+    assert call and all(c in fused for c in call)          # the same fused call(s), argument for argument
+    if opt != "sgd":
+        assert "m[i0] = " in rs or "mom[i0] = " in rs      # the state lives on the slice
+    if opt == "lamb":
+        assert rs.count("coconetSumSquares<<<") == 2 and "coconetSumOverRanks" in rs
+    for f in files:
+        subprocess.check_call([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                               os.path.join(DSL, "rt"), "-I", os.path.join(ROOT, "include"), "-c", f,
+                               "-o", str(tmp_path / "a.o")])
+
+
+def test_autotuner_refuses_programs_it_cannot_derive_from(dsl_build, tmp_path):
+    out = _run_dsl_program(tmp_path, '''
+  Stage s = ReduceScatter(Summation, g); Stage wn = Update(w, AllGather(Scatter(w) - lr * s));
+  Pipeline p("p", {g, w, lr}, {wn});
+  Autotuner().autotune(p);''')
+    assert out.returncode != 0 and "write the pipeline with AllReduce only" in out.stderr
+    out = _run_dsl_program(tmp_path, '''
+  Stage wn = Update(w, w - lr * w);
+  Pipeline p("p", {g, w, lr}, {wn});
+  Autotuner().autotune(p);''')
+    assert out.returncode != 0 and "no AllReduce" in out.stderr
