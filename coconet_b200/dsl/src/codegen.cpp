@@ -563,6 +563,16 @@ struct Emitter {
     if (x->kind == NodeKind::Tensor) src = x->name;
     else if (x->kind == NodeKind::Update) src = x->in[0]->name;
     else if (buffer.count(x.get())) src = buffer.at(x.get());
+    else if (x->kind == NodeKind::AllReduce || x->kind == NodeKind::ReduceScatter) {
+      // the collectives work in place: the sum is in the operand's own memory
+      // (a reduce-scatter leaves it in the rank's slice of that memory)
+      const NodeRef &t = x->in[0];
+      std::string mem = t->kind == NodeKind::Tensor ? t->name
+                        : t->kind == NodeKind::Update ? t->in[0]->name
+                        : buffer.count(t.get()) ? buffer.at(t.get()) : "";
+      if (mem.empty()) fail("operand of Norm is not in memory: " + x->name);
+      src = x->kind == NodeKind::AllReduce ? mem : "(" + mem + " + (size_t)" + sliceCount() + " * rank)";
+    }
     else fail("operand of Norm is not in memory: " + x->name);
     const bool sliced = x->layout == Sliced;
     count = sliced ? "coconetSliceLen(" + N() + ", comm_size, rank)" : N();

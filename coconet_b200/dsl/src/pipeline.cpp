@@ -570,6 +570,14 @@ void Autotuner::autotune(Pipeline &p, std::vector<Tensor> canSlice) {
               << "' is not emitted: " << why << std::endl;
     return;
   }
+  bool has_norm = false;
+  for (const NodeRef &s : all) has_norm = has_norm || s->kind == NodeKind::Norm;
+  if (has_norm && p.classify(all).rule == FusedUpdate::Unknown) {
+    // a global norm inside one kernel needs the two-phase kernel, which exists for LAMB only
+    std::cerr << "coconet dsl: autotune: the fused schedule of '" << p.name()
+              << "' is not emitted: it contains a Norm and is not LAMB" << std::endl;
+    return;
+  }
   p.fuse(as_stages(all));
   emit("fuse_RS_C_AG");
 }

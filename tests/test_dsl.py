@@ -281,3 +281,25 @@ def test_autotuner_refuses_programs_it_cannot_derive_from(dsl_build, tmp_path):
   Pipeline p("p", {g, w, lr}, {wn});
   Autotuner().autotune(p);''')
     assert out.returncode != 0 and "no AllReduce" in out.stderr
+
+
+def test_autotuner_on_a_program_with_a_gradient_norm(dsl_build, tmp_path):
+    # w -= lr * gsum / ||gsum||: the Norm reads the collective's in-place result (whole
+    # buffer after AllReduce, the rank's slice after ReduceScatter); no fused schedule,
+    # because a global norm inside one kernel exists for LAMB only
+    out = _run_dsl_program(tmp_path, '''
+  Stage s = AllReduce(Summation, g); Stage nrm = Norm(s); Stage wn = Update(w, w - lr * s / nrm);
+  Pipeline p("clip", {g, w, lr}, {wn});
+  Autotuner t; t.autotune(p);
+  for (const std::string &f : t.emitted()) std::cout << f << std::endl;''')
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split() == ["./clip-AR_C.cu", "./clip-RS_C_AG.cu"]
+    assert "the fused schedule of 'clip' is not emitted" in out.stderr
+    ar, rs = (tmp_path / "clip-AR_C.cu").read_text(), (tmp_path / "clip-RS_C_AG.cu").read_text()
+    assert "coconetSumSquares<<<coconetBlocks(N), 256, 0, stream>>>(g, N, " in ar
+    assert "(g + (size_t)DIVUP(N, comm_size) * rank), coconetSliceLen(N, comm_size, rank), " in rs
+    assert "coconetSumOverRanks(comm, " in rs and "coconetSumOverRanks" not in ar
+    for f in ("clip-AR_C.cu", "clip-RS_C_AG.cu"):
+        subprocess.check_call([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                               os.path.join(DSL, "rt"), "-I", os.path.join(ROOT, "include"), "-c",
+                               str(tmp_path / f), "-o", str(tmp_path / "c.o")])
