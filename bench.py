@@ -95,9 +95,10 @@ class ClockSampler:
                 "power_w_max": max(pw) if pw else None, "reasons": reasons, "samples": len(samples)}
 
 
-def cpu_baseline(count_sample, world, reps=2):
+def cpu_baseline(count_sample, world, reps=2, threads=1):
     """The reference's CPU path (host sum of `world` gradient arrays + the
-    per-element passes) on a bounded sample, single-threaded."""
+    per-element passes) on a bounded sample: single-threaded like the
+    reference's loops by default, or on `threads` host threads."""
     import numpy as np
     import oracle_lib as O
     so = os.path.join(ROOT, "oracle", "liboracle.so")
@@ -114,20 +115,28 @@ def cpu_baseline(count_sample, world, reps=2):
     for step in range(reps):
         t0 = time.perf_counter()
         O.cpu_step_adam(grads, w, m, v, HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"],
-                        step, inv_scale=1.0 / LOSS_SCALE, w_lp=wl)
+                        step, inv_scale=1.0 / LOSS_SCALE, w_lp=wl, threads=threads)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    return {"value": world * n / best / 1e9, "unit": UNIT, "cores": 1, "kind": "port",
+    return {"value": world * n / best / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
             "sample": f"{n} of {COUNT} elements x {world} gradient arrays, best of {reps}, "
-                      f"{best * 1e3:.1f} ms per step; host has {os.cpu_count()} cores"}
+                      f"{best * 1e3:.1f} ms per step on {threads} thread(s); host has "
+                      f"{os.cpu_count()} cores"}
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    n = 1 << 24
+    # Every host thread the box offers (the elements are independent: contiguous
+    # ranges, one thread each); the sample grows with the thread count so that a
+    # step stays long enough to time.
+    import oracle_lib as O
+    threads = max(1, min(O.threads_available(), os.cpu_count() or 1))
+    n = min(COUNT, (1 << 24) * max(1, threads // 4))
     steps = max(1, min(args.steps, 3))
-    cb = cpu_baseline(n, world, reps=steps + min(args.warmup, 1))
+    cb = cpu_baseline(n, world, reps=steps + min(args.warmup, 1), threads=threads)
+    one = cpu_baseline(1 << 24, world, reps=1, threads=1)
+    cb["sample"] += f"; one thread: {one['value']:.4f} {UNIT}"
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT,
             "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 1),
             "ms_per_step": world * n / (cb["value"] * 1e9) * 1e3 * (COUNT / n),

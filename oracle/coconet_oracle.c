@@ -10,6 +10,8 @@
 #include "coconet_oracle.h"
 
 #include <math.h>
+#include <pthread.h>
+#include <unistd.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -280,4 +282,65 @@ int oracle_cpu_step_adam(const void *const *g, int world, int g_is_f16,
   memcpy(v, s2, n * sizeof(float));
   free(s0); free(s2); free(s4); free(s1); free(s3);
   return 0;
+}
+
+struct cpu_step_job {
+  const void *g[64];
+  int world, g_is_f16, step, rc;
+  float inv_scale, lr, beta1, beta2, eps;
+  float *w, *m, *v;
+  uint16_t *w_lp;
+  size_t n;
+};
+
+static void *cpu_step_thread(void *arg) {
+  struct cpu_step_job *j = (struct cpu_step_job *)arg;
+  j->rc = oracle_cpu_step_adam(j->g, j->world, j->g_is_f16, j->inv_scale, j->w, j->m, j->v,
+                               j->w_lp, j->n, j->lr, j->beta1, j->beta2, j->eps, j->step);
+  return 0;
+}
+
+int oracle_cpu_step_adam_mt(const void *const *g, int world, int g_is_f16,
+                            float inv_scale, float *w, float *m, float *v,
+                            uint16_t *w_lp, size_t n, float lr, float beta1,
+                            float beta2, float eps, int step, int threads) {
+  /* The same passes on `threads` contiguous ranges of the elements, one host
+   * thread each (the elements are independent, so the results are those of
+   * the single-threaded call bit for bit). */
+  if (threads < 1) threads = 1;
+  if (threads > 256) threads = 256;
+  if (world < 1 || world > 64) return -1;
+  struct cpu_step_job *jobs = (struct cpu_step_job *)calloc((size_t)threads, sizeof(*jobs));
+  pthread_t *tid = (pthread_t *)calloc((size_t)threads, sizeof(*tid));
+  if (!jobs || !tid) {
+    free(jobs); free(tid);
+    return -1;
+  }
+  const size_t gs = g_is_f16 ? sizeof(uint16_t) : sizeof(float);
+  int failed = 0;
+  for (int t = 0; t < threads; t++) {
+    const size_t a = n * (size_t)t / (size_t)threads, b = n * (size_t)(t + 1) / (size_t)threads;
+    struct cpu_step_job *j = &jobs[t];
+    for (int r = 0; r < world; r++) j->g[r] = (const char *)g[r] + a * gs;
+    j->world = world, j->g_is_f16 = g_is_f16, j->step = step, j->rc = 0;
+    j->inv_scale = inv_scale, j->lr = lr, j->beta1 = beta1, j->beta2 = beta2, j->eps = eps;
+    j->w = w + a, j->m = m + a, j->v = v + a, j->w_lp = w_lp ? w_lp + a : 0;
+    j->n = b - a;
+    if (pthread_create(&tid[t], 0, cpu_step_thread, j) != 0) {  // run it here instead
+      cpu_step_thread(j);
+      tid[t] = 0;
+      jobs[t].world = -1;  // marks "not joined"
+    }
+  }
+  for (int t = 0; t < threads; t++) {
+    if (jobs[t].world != -1) pthread_join(tid[t], 0);
+    failed |= jobs[t].rc != 0;
+  }
+  free(jobs); free(tid);
+  return failed ? -1 : 0;
+}
+
+int oracle_threads_available(void) {
+  const long n = sysconf(_SC_NPROCESSORS_ONLN);
+  return n > 0 ? (int)n : 1;
 }

@@ -96,6 +96,17 @@ int oracle_cpu_step_adam(const void *const *g, int world, int g_is_f16,
                          uint16_t *w_lp, size_t n, float lr, float beta1,
                          float beta2, float eps, int step);
 
+/* The same step on `threads` host threads (pthreads, contiguous ranges of the
+ * elements; results identical to the single-threaded call).  The reference's
+ * loops carry no OpenMP pragma although -fopenmp is on its link line
+ * (examples/sgd/Makefile:18); this is what they would do with one.  Used by
+ * the benchmark's reference arm, which may use every host thread. */
+int oracle_cpu_step_adam_mt(const void *const *g, int world, int g_is_f16,
+                            float inv_scale, float *w, float *m, float *v,
+                            uint16_t *w_lp, size_t n, float lr, float beta1,
+                            float beta2, float eps, int step, int threads);
+int oracle_threads_available(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -56,6 +56,9 @@ def lib():
                                            _f32p, _u16p, C.c_size_t, C.c_float, C.c_float,
                                            C.c_float, C.c_float, C.c_int]
         L.oracle_cpu_step_adam.restype = C.c_int
+        L.oracle_cpu_step_adam_mt.argtypes = L.oracle_cpu_step_adam.argtypes + [C.c_int]
+        L.oracle_cpu_step_adam_mt.restype = C.c_int
+        L.oracle_threads_available.restype = C.c_int
         L.oracle_f32_to_f16.argtypes = [C.c_float]
         L.oracle_f32_to_f16.restype = C.c_uint16
         _lib = L
@@ -98,11 +101,20 @@ def lamb(w, m, v, gsum, lr, b1, b2, eps, wd, step, variant=OVERLAP, flags=0, w_l
     return norms[0], norms[1]
 
 
-def cpu_step_adam(grads, w, m, v, lr, b1, b2, eps, step, inv_scale=1.0, w_lp=None):
+def cpu_step_adam(grads, w, m, v, lr, b1, b2, eps, step, inv_scale=1.0, w_lp=None, threads=1):
     is16 = grads[0].dtype == np.float16
-    rc = lib().oracle_cpu_step_adam(_ptr_array(grads), len(grads), int(is16), inv_scale, _fp(w),
-                                    _fp(m), _fp(v), _hp(w_lp), w.size, lr, b1, b2, eps, step)
+    if threads == 1:
+        rc = lib().oracle_cpu_step_adam(_ptr_array(grads), len(grads), int(is16), inv_scale, _fp(w),
+                                        _fp(m), _fp(v), _hp(w_lp), w.size, lr, b1, b2, eps, step)
+    else:
+        rc = lib().oracle_cpu_step_adam_mt(_ptr_array(grads), len(grads), int(is16), inv_scale,
+                                           _fp(w), _fp(m), _fp(v), _hp(w_lp), w.size, lr, b1, b2,
+                                           eps, step, threads)
     assert rc == 0
+
+
+def threads_available():
+    return int(lib().oracle_threads_available())
 
 
 # ---- the reference's own host checkers, compiled by `make -C oracle ref` ----

@@ -92,6 +92,15 @@ def test_cpu_step_matches_elementwise_adam():
     O.cpu_step_adam(gh, w2, m2, v2, 1e-3, 0.9, 0.999, 1e-6, 3, inv_scale=1 / 1024, w_lp=wl2)
     assert np.array_equal(w1, w2) and np.array_equal(wl1, wl2)
     assert np.array_equal(wl1, w1.astype(np.float16))
+    # the multi-threaded form (the benchmark's reference arm) gives the same bits
+    w3, m3, v3, wl3 = w0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float16)
+    w4, m4, v4, wl4 = w0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float16)
+    for step in range(2):
+        O.cpu_step_adam(gh, w3, m3, v3, 1e-3, 0.9, 0.999, 1e-6, step, inv_scale=1 / 1024, w_lp=wl3)
+        O.cpu_step_adam(gh, w4, m4, v4, 1e-3, 0.9, 0.999, 1e-6, step, inv_scale=1 / 1024, w_lp=wl4,
+                        threads=5)
+    assert np.array_equal(w3, w4) and np.array_equal(m3, m4) and np.array_equal(v3, v4)
+    assert np.array_equal(wl3, wl4) and O.threads_available() >= 1
 
 
 # ---- the reference's own host checkers --------------------------------------
