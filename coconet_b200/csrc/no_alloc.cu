@@ -1,11 +1,10 @@
 // cocoLambStepNoAlloc: a single-GPU LAMB step that allocates nothing.
 //
 // Some callers of this library may not allocate device memory at the moment
-// they step the optimizer: code running between cudaStreamBeginCapture and
-// cudaStreamEndCapture, a training loop whose memory pool has been frozen or
+// they step the optimizer: a training loop whose memory pool has been frozen or
 // handed over entirely to a framework's caching allocator, a process close to
-// the device's memory limit, or a real-time loop that must not take the
-// driver's allocation locks.  Creating a communicator (cocoCommInitAll /
+// the device's memory limit, or a latency-sensitive loop that must not take
+// the driver's allocation locks.  Creating a communicator (cocoCommInitAll /
 // cocoCommInitRank) calls cudaMalloc for the page that holds the kernel's
 // counters and per-CTA partial norms, so those callers cannot use
 // cocoFusedLAMB.  This entry point runs the same kernel with that page placed
@@ -15,6 +14,7 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <cstddef>
 #include <mutex>
 
 #include "coconet_rt.h"
@@ -78,11 +78,20 @@ extern "C" int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *
   if (!pd.coop) return cocoInvalidUsage;
   cudaStream_t st = (cudaStream_t)stream;
 
-  // The page keeps what the previous call left.  The flags only ever grow
-  // with `seq`, but the two CTA counters and the status word must start at
-  // zero even if an earlier kernel was cut short: clear them on the stream.
-  if (cudaMemsetAsync(&pd.page->done_count, 0,
-                      sizeof(unsigned int) * 2 + sizeof(int) * 8, st) != cudaSuccess) {
+  // The page keeps what the previous call left.  Everything a call reads
+  // before it has written it must start at zero even if an earlier kernel was
+  // cut short: the norm flags and partials, the two CTA counters and the
+  // status word.  They are one contiguous run of the page (checked below), so
+  // one stream-ordered memset clears them; the per-CTA partial sums and the
+  // last norms behind them are always written before they are read.
+  static_assert(offsetof(FlagPage, norm_part) == offsetof(FlagPage, norm_flag) + sizeof(FlagPage::norm_flag) &&
+                    offsetof(FlagPage, done_count) == offsetof(FlagPage, norm_part) + sizeof(FlagPage::norm_part) &&
+                    offsetof(FlagPage, norm_count) == offsetof(FlagPage, done_count) + sizeof(unsigned int) &&
+                    offsetof(FlagPage, status) == offsetof(FlagPage, norm_count) + sizeof(unsigned int),
+                "cocoLambStepNoAlloc clears norm_flag .. status with one memset");
+  constexpr size_t kClearBytes =
+      offsetof(FlagPage, status) + sizeof(FlagPage::status) - offsetof(FlagPage, norm_flag);
+  if (cudaMemsetAsync(pd.page->norm_flag, 0, kClearBytes, st) != cudaSuccess) {
     (void)cudaGetLastError();
     return cocoCudaError;
   }

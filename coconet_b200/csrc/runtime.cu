@@ -544,9 +544,14 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
     mc_g = mc_out = nullptr;
   }
   // NVLS moves (1 + 1/R) N s bytes per direction, peer-to-peer 2 (R-1)/R N s:
-  // the switch wins from R = 4 on ("auto").  It needs multicast addresses for
-  // both buffers, i.e. buffers registered with cocoRegisterMapped.
-  const bool want_nvls = c->algo == 1 || (c->algo == 2 && c->world >= 4);
+  // the switch wins from R = 4 on.  "auto" takes it there for 16-bit gradients
+  // only: the in-switch sum has no fixed order, which the 2e-3 tolerance of
+  // 16-bit gradients absorbs but the 1e-5 contract of fp32 gradients (fixed
+  // reduction order per world size) does not; fp32 gradients go through the
+  // switch only when the caller asks with cocoSetAlgo(comm, 1).  It needs
+  // multicast addresses for both buffers (cocoMemAlloc / cocoRegisterMapped).
+  const bool want_nvls =
+      c->algo == 1 || (c->algo == 2 && c->world >= 4 && dtype_size(pc.g_type) == 2);
   if (want_nvls && mc_g && mc_out && aligned16(mc_g) && aligned16(mc_out)) {
     ra.mc_g = mc_g;
     ra.mc_out = mc_out;

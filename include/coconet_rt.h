@@ -185,8 +185,11 @@ int cocoMemHasMulticast(cocoComm_t comm, const void *ptr, int *yes);
  * multicast address (in-switch summation order; 16-bit sums delivered rounded
  * to 16 bits; within the stated tolerances, not bit-exact).  2 (default, also
  * COCO_ALGO=auto): NVLS from world size 4 on, where it moves fewer bytes per
- * link, else peer-to-peer.  Buffers without a multicast address always take
- * the peer-to-peer path. */
+ * link, but only for 16-bit gradients (tolerance rel 2e-3); fp32 gradients
+ * keep the fixed-order peer-to-peer path, whose results are reproducible per
+ * world size to the last bit (the rel 1e-5 contract), unless the caller asks
+ * for the switch with algo 1.  Buffers without a multicast address always
+ * take the peer-to-peer path. */
 int cocoSetAlgo(cocoComm_t comm, int algo);
 
 /* ---- the fused step -----------------------------------------------------
@@ -217,10 +220,9 @@ int cocoFusedLAMB(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *
 
 /* One LAMB step on ONE GPU (world size 1, bias-corrected formulation, same
  * arguments and arithmetic as cocoFusedLAMB) for callers that may not
- * allocate device memory when they step the optimizer: inside a stream
- * capture's begin/end bracket, with a frozen or fully reserved memory pool,
- * near the device's memory limit, or in a loop that must stay clear of the
- * driver's allocation locks.  It needs no communicator and calls no
+ * allocate device memory when they step the optimizer: with a frozen or fully
+ * reserved memory pool, near the device's memory limit, or in a loop that
+ * must stay clear of the driver's allocation locks.  It needs no communicator and calls no
  * cudaMalloc/cudaFree nor any allocating library routine: the kernel's scratch
  * (CTA counters, per-CTA partial norms, status; about 33 KB) lives in a fixed
  * __device__ array inside the library image, held by every GPU that loads the

@@ -10,7 +10,9 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DSL = os.path.join(ROOT, "coconet_b200", "dsl")
-REF = os.environ.get("COCONET_REFERENCE", "/root/reference")
+# the reference tree, when there is one: COCONET_REFERENCE, else a directory
+# named "reference" beside the repository
+REF = os.environ.get("COCONET_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 

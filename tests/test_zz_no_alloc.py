@@ -1,6 +1,6 @@
 """cocoLambStepNoAlloc: the LAMB step for callers that cannot allocate device
-memory while stepping the optimizer (a stream-capture bracket, a frozen or
-fully reserved pool, a device near its memory limit).  It must give what the
+memory while stepping the optimizer (a frozen or fully reserved pool, a device
+near its memory limit, a loop that avoids the driver's allocation locks).  It must give what the
 communicator-based entry point gives.  Collected last on purpose: it shares a
 library-resident scratch array, and a failure here must not hide other tests.
 """
@@ -49,10 +49,15 @@ def test_no_alloc_matches_communicator_entry_point_twice_in_a_row(n, mixed):
             gs = 1 / 1024.0 if mixed else 1.0
             comm.fused_lamb(g, wa, ma, va, h["lr"], h["beta1"], h["beta2"], h["eps"],
                             h["weight_decay"], step, w_lp=la, grad_scale=gs)
-            before = torch.cuda.memory_allocated()
-            _no_alloc_step(g, wb, mb, vb, step, w_lp=lb, grad_scale=gs)
-            assert torch.cuda.memory_allocated() == before
             torch.cuda.synchronize()
+            # the driver's own count of free device memory also sees a raw
+            # cudaMalloc made behind torch's back (the first call is left out:
+            # loading the kernel image may take memory once)
+            free_before = torch.cuda.mem_get_info()[0]
+            _no_alloc_step(g, wb, mb, vb, step, w_lp=lb, grad_scale=gs)
+            torch.cuda.synchronize()
+            if step > 0:
+                assert torch.cuda.mem_get_info()[0] == free_before
             assert comm.status()["code"] == 0
             # same kernel, same arithmetic; only the number of CTAs (hence the
             # summation tree of the norms) may differ: fp32 tolerance of the suite
