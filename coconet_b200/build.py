@@ -6,7 +6,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcoconet_rt.so")
-SOURCES = ["fused_step.cu", "runtime.cu", "bootstrap.cpp", "no_alloc.cu", "symm_mem.cu", "collectives.cu"]
+SOURCES = ["fused_step.cu", "runtime.cu", "bootstrap.cpp", "no_alloc.cu", "symm_mem.cu", "collectives.cu",
+           "link_probe.cu"]
 HEADERS = ["fused_step.cuh", "bootstrap.h", os.path.join(ROOT, "include", "coconet_rt.h"),
            os.path.join(ROOT, "include", "coconet_device.h"),
            os.path.join(ROOT, "include", "coconet_fused_generic.cuh")]

@@ -29,6 +29,9 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <map>
+#include <mutex>
+#include <tuple>
 #include <type_traits>
 
 namespace coco {
@@ -289,7 +292,7 @@ template <typename GT> struct RawUnit<GT, 1> {
 // ---------------------------------------------------------------------------
 template <typename GT, int VEC, int RB, int HS = 4>
 __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &sa, size_t i,
-                                            float (&g)[VEC], float (&gg)[VEC]) {
+                                            float (&g)[VEC]) {
   const int R = sa.world;
   const bool ring = GradTraits<GT>::kIs16 && sa.variant == cocoVariantNccl;
   // The forked-NCCL variant reproduces the ring: the chunk owned by `rank`
@@ -317,13 +320,9 @@ __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
       if (ring) {
-        if constexpr (std::is_same<GT, __half>::value) {
-          g[e] = __half2float(hacc[e]);
-          gg[e] = __half2float(__hmul(hacc[e], hacc[e]));
-        }
+        if constexpr (std::is_same<GT, __half>::value) g[e] = __half2float(hacc[e]);
       } else {
         g[e] = __fmul_rn(g[e], sa.grad_scale);
-        gg[e] = 0.f;
       }
     }
   } else {
@@ -348,8 +347,7 @@ __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &
 #pragma unroll
           for (int k = 1; k < RB; ++k)
             if (kExact || k < R) acc = __hadd(acc, __ushort_as_half(raw[k].bits(e)));
-          g[e] = __half2float(acc);
-          gg[e] = __half2float(__hmul(acc, acc));  // (float)(S0 * S0), reduce_kernel.h:29
+          g[e] = __half2float(acc);  // the update squares it in half precision
         }
       }
       return;
@@ -361,7 +359,6 @@ __device__ __forceinline__ void reduce_unit(const RankArgs &ra, const StepArgs &
       for (int k = 1; k < RB; ++k)
         if (kExact || k < R) acc = __fadd_rn(acc, raw[k].get(e));
       g[e] = __fmul_rn(acc, sa.grad_scale);
-      gg[e] = 0.f;
     }
   }
 }
@@ -468,24 +465,31 @@ __device__ __forceinline__ void gather_unit(const RankArgs &ra, int R, size_t i,
 // reference's host checks evaluate them, so that m and v match a scalar CPU
 // evaluation bit for bit.
 // ---------------------------------------------------------------------------
+// The scalars of the update as the kernel uses them.  All but quirk_n are
+// copies of kernel parameters, which live in the constant bank: arithmetic
+// can take them as operands directly, so they need no registers of their own.
 struct Hyper {
   float lr, b1, b2, omb1, omb2, eps, wd, d1, d2;
   double d1d, d2d, r1d, r2d;
   int variant;
   bool square_first;  // (1-b2)*(g*g) instead of ((1-b2)*g)*g
+  bool nccl_m_beta2;  // forked-NCCL Adam: the first moment is updated with beta2
   float quirk_n;      // COCO_LAMB_REF_QUIRK: the element count r^2 is divided by
 };
 
 template <int OPT> __device__ __forceinline__ Hyper make_hyper(const StepArgs &sa) {
   Hyper h;
   h.lr = sa.lr, h.b1 = sa.beta1, h.b2 = sa.beta2;
-  h.omb1 = __fsub_rn(1.f, sa.beta1), h.omb2 = __fsub_rn(1.f, sa.beta2);
+  h.omb1 = sa.omb1, h.omb2 = sa.omb2;
   h.eps = sa.eps, h.wd = sa.weight_decay, h.d1 = sa.d1, h.d2 = sa.d2;
   h.d1d = sa.d1d, h.d2d = sa.d2d;
-  h.r1d = 1.0 / sa.d1d, h.r2d = 1.0 / sa.d2d;
+  h.r1d = sa.r1d, h.r2d = sa.r2d;
   h.variant = sa.variant;
   // test-adam.cu:16 squares first; lamb.cpp:81 multiplies left to right
   h.square_first = OPT == kAdam && sa.variant == cocoVariantDsl;
+  // common_kernel.h:878 passes beta2 to the m functor (Adam); the LAMB copy at
+  // :2509 passes beta1
+  h.nccl_m_beta2 = OPT == kAdam;
   h.quirk_n = (float)sa.count;
   return h;
 }
@@ -497,13 +501,20 @@ __device__ __forceinline__ float sgd_elem(const Hyper &h, float w, float g) {
 
 // New moments.  overlap: b*m + (1-b)*g, b*v + ((1-b)*g)*g
 // (multi-process-adam-scattered.cpp:112-116); dsl: (1-b)*(g*g)
-// (test-adam.cu:16); nccl: m*b2 + g*(1-b2) for BOTH moments, with the
-// half-precision square (reduce_kernel.h:27-39, common_kernel.h:875-879).
-__device__ __forceinline__ void moments_elem(const Hyper &h, float g, float gg, float &m,
-                                             float &v) {
+// (test-adam.cu:16); nccl: v*b2 + gg*(1-b2) with the half-precision square
+// and, for Adam, m*b2 + g*(1-b2) -- beta2 for BOTH moments
+// (reduce_kernel.h:27-39, common_kernel.h:875-879); its LAMB copy uses beta1
+// for m (reduce_kernel.h:391-400, common_kernel.h:2505-2511).
+__device__ __forceinline__ void moments_elem(const Hyper &h, float g, float &m, float &v) {
   if (h.variant == cocoVariantNccl) {
+    // g is the fp16 ring sum S0 widened to float (exactly), so S0 is recovered
+    // exactly; the square is taken in half precision: (float)(S0 * S0),
+    // reduce_kernel.h:29
+    const __half s0 = __float2half_rn(g);
+    const float gg = __half2float(__hmul(s0, s0));
     v = __fadd_rn(__fmul_rn(v, h.b2), __fmul_rn(gg, h.omb2));
-    m = __fadd_rn(__fmul_rn(m, h.b2), __fmul_rn(g, h.omb2));
+    m = h.nccl_m_beta2 ? __fadd_rn(__fmul_rn(m, h.b2), __fmul_rn(g, h.omb2))
+                       : __fadd_rn(__fmul_rn(m, h.b1), __fmul_rn(g, h.omb1));
   } else if (h.square_first) {
     v = __fadd_rn(__fmul_rn(h.b2, v), __fmul_rn(h.omb2, __fmul_rn(g, g)));
     m = __fadd_rn(__fmul_rn(h.b1, m), __fmul_rn(h.omb1, g));
@@ -579,12 +590,21 @@ __device__ __forceinline__ float lamb_r_elem(const Hyper &h, float w, float m_, 
 // ---------------------------------------------------------------------------
 // one unit of the data phase
 // ---------------------------------------------------------------------------
-// SGD and Adam: whole step.  LAMB phase 1: moments + norm partials only.
-template <int OPT, typename GT, typename LPT, int VEC, int RB, int HS = 4>
-__device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
-                                          size_t lo, size_t i, double &sum_w2, double &sum_r2) {
-  float g[VEC], gg[VEC], w[VEC];
-  reduce_unit<GT, VEC, RB, HS>(ra, sa, i, g, gg);
+// Everything after the reduction: SGD and Adam: the whole update and the
+// all-gather of the unit.  LAMB phase 1: moments + norm partials only.
+// g: reduced, scaled gradient.  NVLS: gather through the NVSwitch multicast
+// address.  All loads of the unit are issued first; the arithmetic then runs
+// in batches of four elements so that only four corrected moment pairs are
+// live at a time (an 8-element unit otherwise spills).
+template <typename LPT, int V>
+__device__ __forceinline__ void nvls_gather(const RankArgs &ra, int R, size_t i,
+                                            const float (&x)[V]);
+
+template <int OPT, typename LPT, int VEC, int RB, int HS = 4, bool NVLS = false>
+__device__ __forceinline__ void apply_unit(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
+                                           size_t lo, size_t i, const float (&g)[VEC],
+                                           double &sum_w2, double &sum_r2) {
+  float w[VEC];
   load_f32<VEC, HS>(ra.w + i, w);
   if constexpr (OPT == kSGD) {
 #pragma unroll
@@ -593,22 +613,30 @@ __device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa
     float m[VEC], v[VEC];
     load_f32<VEC, HS>(ra.m + (i - lo), m);
     load_f32<VEC, HS>(ra.v + (i - lo), v);
-    float m_[VEC], v_[VEC];
+    constexpr int B = VEC < 4 ? VEC : 4;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) moments_elem(h, g[e], gg[e], m[e], v[e]);
-    corrected_moments<VEC>(h, m, v, m_, v_);
+    for (int q = 0; q < VEC; q += B) {
+      float mb[B], vb[B], m_[B], v_[B];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      if constexpr (OPT == kAdam) {
-        w[e] = adam_elem(h, w[e], m_[e], v_[e]);
-      } else {
-        const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
-        if (sa.flags & COCO_LAMB_REF_QUIRK) {
-          sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), h.quirk_n);
-          sum_w2 += (double)__fmul_rn(w[e], w[e]);
+      for (int e = 0; e < B; ++e) {
+        mb[e] = m[q + e], vb[e] = v[q + e];
+        moments_elem(h, g[q + e], mb[e], vb[e]);
+        m[q + e] = mb[e], v[q + e] = vb[e];
+      }
+      corrected_moments<B>(h, mb, vb, m_, v_);
+#pragma unroll
+      for (int e = 0; e < B; ++e) {
+        if constexpr (OPT == kAdam) {
+          w[q + e] = adam_elem(h, w[q + e], m_[e], v_[e]);
         } else {
-          sum_r2 += (double)r * (double)r;
-          sum_w2 += (double)w[e] * (double)w[e];
+          const float r = lamb_r_elem(h, w[q + e], m_[e], v_[e]);
+          if (sa.flags & COCO_LAMB_REF_QUIRK) {
+            sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), h.quirk_n);
+            sum_w2 += (double)__fmul_rn(w[q + e], w[q + e]);
+          } else {
+            sum_r2 += (double)r * (double)r;
+            sum_w2 += (double)w[q + e] * (double)w[q + e];
+          }
         }
       }
     }
@@ -617,8 +645,20 @@ __device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa
   }
   if constexpr (OPT != kLAMB) {
     if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<VEC, HS>(ra.w + i, w);
-    gather_unit<LPT, VEC, RB, HS>(ra, sa.world, i, w);
+    if constexpr (NVLS)
+      nvls_gather<LPT, VEC>(ra, sa.world, i, w);
+    else
+      gather_unit<LPT, VEC, RB, HS>(ra, sa.world, i, w);
   }
+}
+
+// One unit of the register-staged data phase: reduce, then apply.
+template <int OPT, typename GT, typename LPT, int VEC, int RB, int HS = 4>
+__device__ __forceinline__ void step_unit(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
+                                          size_t lo, size_t i, double &sum_w2, double &sum_r2) {
+  float g[VEC];
+  reduce_unit<GT, VEC, RB, HS>(ra, sa, i, g);
+  apply_unit<OPT, LPT, VEC, RB, HS>(ra, sa, h, lo, i, g, sum_w2, sum_r2);
 }
 
 // LAMB phase 2: recompute r from the stored moments, apply the scaled step.
@@ -651,46 +691,53 @@ __device__ __forceinline__ void lamb_apply_unit(const RankArgs &ra, const StepAr
 // delivered rounded to 16 bits, so results agree with the P2P path only to
 // within the stated tolerances, not bit for bit.
 // ---------------------------------------------------------------------------
+// ld_reduce returns the 16 raw bytes of the reduced unit (so that several can
+// be kept in flight cheaply, 4 registers each); unpack converts them.
 template <typename GT> struct Multimem;
 template <> struct Multimem<float> {
   static constexpr int kN = 4;
-  static __device__ __forceinline__ void ld_reduce(const void *p, float (&x)[4]) {
+  static __device__ __forceinline__ uint4 ld_reduce(const void *p) {
+    float x[4];
     asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
                  : "=f"(x[0]), "=f"(x[1]), "=f"(x[2]), "=f"(x[3])
-                 : "l"(p)
-                 : "memory");
+                 : "l"(p));
+    return make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]),
+                      __float_as_uint(x[3]));
+  }
+  static __device__ __forceinline__ void unpack(const uint4 &q, float (&x)[4]) {
+    x[0] = __uint_as_float(q.x), x[1] = __uint_as_float(q.y);
+    x[2] = __uint_as_float(q.z), x[3] = __uint_as_float(q.w);
   }
 };
-template <> struct Multimem<__half> {
+template <typename T16> struct Multimem16 {
   static constexpr int kN = 8;
-  static __device__ __forceinline__ void ld_reduce(const void *p, float (&x)[8]) {
-    unsigned q[4];
+  static __device__ __forceinline__ void unpack(const uint4 &q, float (&x)[8]) {
+    const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      x[2 * k] = Bits16<T16>::to_f32((unsigned short)(w[k] & 0xffffu));
+      x[2 * k + 1] = Bits16<T16>::to_f32((unsigned short)(w[k] >> 16));
+    }
+  }
+};
+template <> struct Multimem<__half> : Multimem16<__half> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void *p) {
+    uint4 q;
     asm volatile(
         "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
-        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
-        : "l"(p)
-        : "memory");
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      x[2 * k] = Bits16<__half>::to_f32((unsigned short)(q[k] & 0xffffu));
-      x[2 * k + 1] = Bits16<__half>::to_f32((unsigned short)(q[k] >> 16));
-    }
+        : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+        : "l"(p));
+    return q;
   }
 };
-template <> struct Multimem<__nv_bfloat16> {
-  static constexpr int kN = 8;
-  static __device__ __forceinline__ void ld_reduce(const void *p, float (&x)[8]) {
-    unsigned q[4];
+template <> struct Multimem<__nv_bfloat16> : Multimem16<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void *p) {
+    uint4 q;
     asm volatile(
         "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
-        : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
-        : "l"(p)
-        : "memory");
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      x[2 * k] = Bits16<__nv_bfloat16>::to_f32((unsigned short)(q[k] & 0xffffu));
-      x[2 * k + 1] = Bits16<__nv_bfloat16>::to_f32((unsigned short)(q[k] >> 16));
-    }
+        : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+        : "l"(p));
+    return q;
   }
 };
 // 16 bytes to every rank's copy (typed .f32 only to name the register class;
@@ -726,60 +773,55 @@ __device__ __forceinline__ void nvls_gather(const RankArgs &ra, int R, size_t i,
   }
 }
 
+// The in-switch reduction has a long round trip (the switch collects the unit
+// from all R GPUs before it answers), so each thread keeps kNvlsDepth reduced
+// units in flight: the loads of the next passes are issued before the current
+// unit is worked on.  One ld_reduce per thread and pass reached 0.55 of the
+// link rate at eight ranks.
+#ifndef COCO_NVLS_DEPTH
+#define COCO_NVLS_DEPTH 3
+#endif
+constexpr int kNvlsDepth = COCO_NVLS_DEPTH;
+
 // PHASE 0: SGD / Adam step or LAMB moments; PHASE 1: LAMB apply.
 template <int OPT, typename GT, typename LPT, int PHASE>
 __device__ __forceinline__ void nvls_phase(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
                                            size_t lo, size_t nunits, size_t tid, size_t nth,
                                            double &sum_w2, double &sum_r2, float lr_scale) {
   constexpr int V = Multimem<GT>::kN;
-  for (size_t u = tid; u < nunits; u += nth) {
-    const size_t i = lo + u * V;
-    float g[V], w[V], m[V], v[V], m_[V], v_[V];
-    if constexpr (PHASE == 0) {
-      Multimem<GT>::ld_reduce((const GT *)ra.mc_g + i, g);
+  if constexpr (PHASE == 0) {
+    const GT *src = (const GT *)ra.mc_g + lo;
+    uint4 raw[kNvlsDepth];
+#pragma unroll
+    for (int k = 0; k < kNvlsDepth; ++k) {
+      const size_t un = tid + (size_t)k * nth;
+      if (un < nunits) raw[k] = Multimem<GT>::ld_reduce(src + un * V);
+    }
+    for (size_t u = tid; u < nunits; u += nth) {
+      const uint4 cur = raw[0];
+#pragma unroll
+      for (int k = 0; k + 1 < kNvlsDepth; ++k) raw[k] = raw[k + 1];
+      const size_t un = u + (size_t)kNvlsDepth * nth;
+      if (un < nunits) raw[kNvlsDepth - 1] = Multimem<GT>::ld_reduce(src + un * V);
+      float g[V];
+      Multimem<GT>::unpack(cur, g);
 #pragma unroll
       for (int e = 0; e < V; ++e) g[e] = __fmul_rn(g[e], sa.grad_scale);
+      apply_unit<OPT, LPT, V, 0, 4, true>(ra, sa, h, lo, lo + u * V, g, sum_w2, sum_r2);
     }
-    load_f32<V>(ra.w + i, w);
-    if constexpr (OPT != kSGD) {
+  } else {
+    for (size_t u = tid; u < nunits; u += nth) {
+      const size_t i = lo + u * V;
+      float w[V], m[V], v[V], m_[V], v_[V];
+      load_f32<V>(ra.w + i, w);
       load_f32<V>(ra.m + (i - lo), m);
       load_f32<V>(ra.v + (i - lo), v);
-    }
-    if constexpr (PHASE == 0) {
-      if constexpr (OPT == kSGD) {
-#pragma unroll
-        for (int e = 0; e < V; ++e) w[e] = sgd_elem(h, w[e], g[e]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < V; ++e) moments_elem(h, g[e], 0.f, m[e], v[e]);
-        corrected_moments<V>(h, m, v, m_, v_);
-#pragma unroll
-        for (int e = 0; e < V; ++e) {
-          if constexpr (OPT == kAdam) {
-            w[e] = adam_elem(h, w[e], m_[e], v_[e]);
-          } else {
-            const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
-            if (sa.flags & COCO_LAMB_REF_QUIRK) {
-              sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), h.quirk_n);
-              sum_w2 += (double)__fmul_rn(w[e], w[e]);
-            } else {
-              sum_r2 += (double)r * (double)r;
-              sum_w2 += (double)w[e] * (double)w[e];
-            }
-          }
-        }
-        store_f32<V>(ra.m + (i - lo), m);
-        store_f32<V>(ra.v + (i - lo), v);
-      }
-    } else {
       corrected_moments<V>(h, m, v, m_, v_);
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
         w[e] = __fsub_rn(w[e], __fmul_rn(lr_scale, r));
       }
-    }
-    if ((PHASE == 0 && OPT != kLAMB) || PHASE == 1) {
       if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<V>(ra.w + i, w);
       nvls_gather<LPT, V>(ra, sa.world, i, w);
     }
@@ -798,8 +840,19 @@ __device__ __forceinline__ void nvls_phase(const RankArgs &ra, const StepArgs &s
 // warp covers one contiguous run of whole 32-byte sectors (consecutive
 // elements per lane made every fp32 access touch half sectors: 1.3 % slower).
 constexpr int kHalfStride = 128;
+// COCO_DIRECT_VEC8 (build-time experiment switch): 8-element units for 16-bit
+// gradients at every world size, 1 = halves 128 elements apart (8-byte peer
+// accesses, whole sectors of the fp32 state), 2 = 8 consecutive elements per
+// lane (16-byte peer accesses).
+#ifndef COCO_DIRECT_VEC8
+#define COCO_DIRECT_VEC8 0
+#endif
 template <int OPT, typename GT, int RB> struct DirectVec {
-  static constexpr int kVec = (RB == 1 && (GradTraits<GT>::kIs16 || OPT == kSGD)) ? 8 : 4;
+  static constexpr int kVec =
+      ((RB == 1 && (GradTraits<GT>::kIs16 || OPT == kSGD)) ||
+       (COCO_DIRECT_VEC8 != 0 && RB >= 2 && GradTraits<GT>::kIs16)) ? 8 : 4;
+  // distance between the two fours of an 8-element unit
+  static constexpr int kStride = (RB == 1 || COCO_DIRECT_VEC8 == 1) ? kHalfStride : 4;
 };
 
 template <int OPT, typename GT, typename LPT, int RB>
@@ -809,14 +862,19 @@ __device__ __forceinline__ void direct_step(const RankArgs &ra, const StepArgs &
   constexpr int VEC = DirectVec<OPT, GT, RB>::kVec;
   const size_t nunits = nelems / VEC;
   if constexpr (VEC == 8) {
-    // tid and nth are multiples of the warp size apart from the lane, so
-    // u & 31 is the lane and u - lane the warp's first unit
-    const size_t nfull = nunits / 32 * 32;
-    for (size_t u = tid; u < nfull; u += nth)
-      step_unit<OPT, GT, LPT, 8, RB, kHalfStride>(ra, sa, h, lo, first + u * 8 - (u & 31) * 4,
-                                                  sum_w2, sum_r2);
-    for (size_t u = nfull + tid; u < nunits; u += nth)  // last, partial warp: consecutive
-      step_unit<OPT, GT, LPT, 8, RB>(ra, sa, h, lo, first + u * 8, sum_w2, sum_r2);
+    if constexpr (DirectVec<OPT, GT, RB>::kStride == kHalfStride) {
+      // tid and nth are multiples of the warp size apart from the lane, so
+      // u & 31 is the lane and u - lane the warp's first unit
+      const size_t nfull = nunits / 32 * 32;
+      for (size_t u = tid; u < nfull; u += nth)
+        step_unit<OPT, GT, LPT, 8, RB, kHalfStride>(ra, sa, h, lo, first + u * 8 - (u & 31) * 4,
+                                                    sum_w2, sum_r2);
+      for (size_t u = nfull + tid; u < nunits; u += nth)  // last, partial warp: consecutive
+        step_unit<OPT, GT, LPT, 8, RB>(ra, sa, h, lo, first + u * 8, sum_w2, sum_r2);
+    } else {
+      for (size_t u = tid; u < nunits; u += nth)
+        step_unit<OPT, GT, LPT, 8, RB>(ra, sa, h, lo, first + u * 8, sum_w2, sum_r2);
+    }
     // up to one 4-element unit may remain
     if ((nelems & 4) && tid == 0)
       step_unit<OPT, GT, LPT, 4, RB>(ra, sa, h, lo, first + nunits * 8, sum_w2, sum_r2);
@@ -853,13 +911,27 @@ __device__ __forceinline__ double warp_sum(double x) {
 }
 
 // ---------------------------------------------------------------------------
-// tile pipeline: bulk asynchronous copies (the TMA engine, 1-D form) stage
-// whole tiles of every input in shared memory a few tiles ahead of the math,
-// so that HBM / NVLink latency is covered by bytes in flight rather than by
-// registers.  One elected thread issues the copies; every thread consumes.
-// No cluster, no multicast: each CTA fetches its own tiles, local or remote.
+// warp rings: every warp stages the gradient tiles it is going to reduce in
+// shared memory with bulk asynchronous copies (the TMA engine, 1-D form), a
+// few tiles ahead of the math.  Latency of the peers' memory (2-3 us over
+// NVLink) is then covered by bytes in flight in shared memory, of which there
+// is plenty, instead of by registers, of which there are not.
+//
+//   tile   = 32 lanes x 16 bytes of gradient per rank (256 16-bit or 128 fp32
+//            elements); stage = the R ranks' tiles, R x 512 bytes
+//   ring   = D stages per warp, one mbarrier each; lane 0 issues the R copies
+//            of a stage, all lanes wait for its barrier, read their 16 bytes of
+//            every rank's tile, and lane 0 refills the stage for tile j + D
+//            right away -- before the update math and the stores of tile j
+//
+// Warps never wait for one another (no CTA-wide barrier in the loop).  No
+// cluster, no multicast: each warp fetches its own tiles, local or remote.
+// Every wait is bounded; a warp that gives up still waits (bounded) for the
+// copies it has in flight before the CTA may retire.
 // ---------------------------------------------------------------------------
-constexpr int kTileElemsPerThread = 2;
+constexpr int kRingMaxStages = 4;
+constexpr int kRingMaxWarps = 16;
+constexpr unsigned kRingTileBytes = 512;  // 32 lanes x 16 bytes
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) {
   return (unsigned)__cvta_generic_to_shared(p);
@@ -884,15 +956,19 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned 
   return ok != 0;
 }
 // Bounded: gives up after timeout_ns (checked every 256 probes) or 2^26 probes.
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity,
-                                          unsigned long long timeout_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(unsigned long long *bar, unsigned parity,
+                                            unsigned long long timeout_ns) {
   const unsigned long long t0 = globaltimer_ns();
   for (unsigned spin = 1; spin < (1u << 26); ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 255u) == 0u && globaltimer_ns() - t0 > timeout_ns) return false;
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity,
+                                          unsigned long long timeout_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, timeout_ns);
 }
 // global -> shared bulk copy; src, dst and bytes are multiples of 16.
 __device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes,
@@ -903,194 +979,131 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned b
       "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
-
-struct TilePlan {
-  int stages;            // 0: pipeline off
-  unsigned g_bytes;      // bytes of one rank's gradient tile
-  unsigned stage_bytes;  // all inputs of one tile
-  size_t ntiles;         // full tiles in this rank's slice
-};
-
-// Math of one tile: each thread owns kTileElemsPerThread consecutive elements.
-// PHASE 0: whole SGD / Adam step, or LAMB moments + norm partials.
-// PHASE 1: LAMB apply.
-template <int OPT, typename GT, typename LPT, int PHASE>
-__device__ __forceinline__ void tile_math(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
-                                          const unsigned char *st, const TilePlan &tp, size_t lo,
-                                          size_t e0, double &sum_w2, double &sum_r2,
-                                          float lr_scale) {
-  constexpr int V = kTileElemsPerThread;
-  const int R = sa.world;
-  const int t0 = V * threadIdx.x;
-  const size_t i = e0 + t0;
-  float g[V], gg[V], w[V], m[V], v[V];
-  const unsigned goff = PHASE == 0 ? R * tp.g_bytes : 0;
-  const int T = V * blockDim.x;
-  if constexpr (PHASE == 0) {
-    const bool ring = GradTraits<GT>::kIs16 && sa.variant == cocoVariantNccl;
-    if constexpr (GradTraits<GT>::kIs16) {
-      if (ring) {
-        if constexpr (std::is_same<GT, __half>::value) {
-          __half acc[V];
-          for (int k = 0; k < R; ++k) {
-            int p = ra.rank + 1 + k;
-            if (p >= R) p -= R;
-            const unsigned q = *reinterpret_cast<const unsigned *>(st + p * tp.g_bytes + t0 * 2);
-            const unsigned short b[V] = {(unsigned short)(q & 0xffffu), (unsigned short)(q >> 16)};
-#pragma unroll
-            for (int e = 0; e < V; ++e)
-              acc[e] = k == 0 ? __ushort_as_half(b[e]) : __hadd(acc[e], __ushort_as_half(b[e]));
-          }
-#pragma unroll
-          for (int e = 0; e < V; ++e) {
-            g[e] = __half2float(acc[e]);
-            gg[e] = __half2float(__hmul(acc[e], acc[e]));
-          }
-        }
-      } else {
-        for (int p = 0; p < R; ++p) {
-          const unsigned q = *reinterpret_cast<const unsigned *>(st + p * tp.g_bytes + t0 * 2);
-          const float x[V] = {Bits16<GT>::to_f32((unsigned short)(q & 0xffffu)),
-                              Bits16<GT>::to_f32((unsigned short)(q >> 16))};
-#pragma unroll
-          for (int e = 0; e < V; ++e) g[e] = p == 0 ? x[e] : __fadd_rn(g[e], x[e]);
-        }
-#pragma unroll
-        for (int e = 0; e < V; ++e) g[e] = __fmul_rn(g[e], sa.grad_scale), gg[e] = 0.f;
-      }
-    } else {
-      for (int p = 0; p < R; ++p) {
-        const float2 q = *reinterpret_cast<const float2 *>(st + p * tp.g_bytes + t0 * 4);
-        const float x[V] = {q.x, q.y};
-#pragma unroll
-        for (int e = 0; e < V; ++e) g[e] = p == 0 ? x[e] : __fadd_rn(g[e], x[e]);
-      }
-#pragma unroll
-      for (int e = 0; e < V; ++e) g[e] = __fmul_rn(g[e], sa.grad_scale), gg[e] = 0.f;
-    }
-  }
-  {
-    const float2 q = *reinterpret_cast<const float2 *>(st + goff + t0 * 4);
-    w[0] = q.x, w[1] = q.y;
-  }
-  if constexpr (OPT != kSGD) {
-    const float2 a = *reinterpret_cast<const float2 *>(st + goff + T * 4 + t0 * 4);
-    const float2 b = *reinterpret_cast<const float2 *>(st + goff + 2 * T * 4 + t0 * 4);
-    m[0] = a.x, m[1] = a.y;
-    v[0] = b.x, v[1] = b.y;
-  }
-  if constexpr (PHASE == 0) {
-    if constexpr (OPT == kSGD) {
-#pragma unroll
-      for (int e = 0; e < V; ++e) w[e] = sgd_elem(h, w[e], g[e]);
-    } else {
-      float m_[V], v_[V];
-#pragma unroll
-      for (int e = 0; e < V; ++e) moments_elem(h, g[e], gg[e], m[e], v[e]);
-      corrected_moments<V>(h, m, v, m_, v_);
-#pragma unroll
-      for (int e = 0; e < V; ++e) {
-        if constexpr (OPT == kAdam) {
-          w[e] = adam_elem(h, w[e], m_[e], v_[e]);
-        } else {
-          const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
-          if (sa.flags & COCO_LAMB_REF_QUIRK) {
-            sum_r2 += (double)__fdiv_rn(__fmul_rn(r, r), h.quirk_n);
-            sum_w2 += (double)__fmul_rn(w[e], w[e]);
-          } else {
-            sum_r2 += (double)r * (double)r;
-            sum_w2 += (double)w[e] * (double)w[e];
-          }
-        }
-      }
-      store_f32<V>(ra.m + (i - lo), m);
-      store_f32<V>(ra.v + (i - lo), v);
-    }
-    if constexpr (OPT != kLAMB) {
-      if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<V>(ra.w + i, w);
-      gather_unit<LPT, V, 0>(ra, R, i, w);
-    }
-  } else {
-    float m_[V], v_[V];
-    corrected_moments<V>(h, m, v, m_, v_);
-#pragma unroll
-    for (int e = 0; e < V; ++e) {
-      const float r = lamb_r_elem(h, w[e], m_[e], v_[e]);
-      w[e] = __fsub_rn(w[e], __fmul_rn(lr_scale, r));
-    }
-    if constexpr (!std::is_same<LPT, NoLp>::value) store_f32<V>(ra.w + i, w);
-    gather_unit<LPT, V, 0>(ra, R, i, w);
-  }
+__device__ __forceinline__ uint4 ld_shared_16(const void *p) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(smem_u32(p)));
+  return v;
 }
 
-// Runs this CTA's share of the slice's full tiles through the pipeline.
-// `iter` counts tiles this CTA has consumed so far (it carries the barrier
-// phases across the two LAMB phases).  Returns false if a copy did not land
-// in time (s_fail is then set for the whole CTA).
-template <int OPT, typename GT, typename LPT, int PHASE>
-__device__ __forceinline__ bool run_tiles(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
-                                          const TilePlan &tp, unsigned char *smem,
-                                          unsigned long long *full, int *s_fail, size_t lo,
-                                          unsigned &iter, double &sum_w2, double &sum_r2,
-                                          float lr_scale) {
+// Sum of the R ranks' 16 bytes of this lane, from one stage of the ring.
+template <typename GT, int VEC>
+__device__ __forceinline__ void ring_reduce(const unsigned char *stage, int lane,
+                                            const RankArgs &ra, const StepArgs &sa,
+                                            float (&g)[VEC]) {
   const int R = sa.world;
-  const int T = kTileElemsPerThread * blockDim.x;
-  const unsigned state_bytes = (OPT == kSGD ? 1u : 3u) * T * 4u;
-  const unsigned bytes = PHASE == 0 ? tp.stage_bytes : state_bytes;
-  const size_t mine =
-      tp.ntiles > blockIdx.x ? (tp.ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const unsigned base = iter;
+  const unsigned char *mine = stage + lane * 16;
+  if constexpr (std::is_same<GT, __half>::value) {
+    if (sa.variant == cocoVariantNccl) {
+      // the forked-NCCL variant: fp16 sum in ring order, starting behind the owner
+      __half acc[VEC];
+      for (int k = 0; k < R; ++k) {
+        int p = ra.rank + 1 + k;
+        if (p >= R) p -= R;
+        const uint4 q = ld_shared_16(mine + p * kRingTileBytes);
+        const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const __half x = __ushort_as_half((unsigned short)((e & 1) ? (w[e >> 1] >> 16)
+                                                                      : (w[e >> 1] & 0xffffu)));
+          acc[e] = k == 0 ? x : __hadd(acc[e], x);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) g[e] = __half2float(acc[e]);
+      return;
+    }
+  }
+  for (int p = 0; p < R; ++p) {  // rank order 0..R-1, fp32
+    const uint4 q = ld_shared_16(mine + p * kRingTileBytes);
+    float x[VEC];
+    if constexpr (GradTraits<GT>::kIs16) {
+      const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        x[e] = Bits16<GT>::to_f32((unsigned short)((e & 1) ? (w[e >> 1] >> 16)
+                                                           : (w[e >> 1] & 0xffffu)));
+    } else {
+      x[0] = __uint_as_float(q.x), x[1] = __uint_as_float(q.y);
+      x[2] = __uint_as_float(q.z), x[3] = __uint_as_float(q.w);
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) g[e] = p == 0 ? x[e] : __fadd_rn(g[e], x[e]);
+  }
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) g[e] = __fmul_rn(g[e], sa.grad_scale);
+}
 
-  auto issue = [&](size_t j) {  // thread 0 only
-    const unsigned s = (base + (unsigned)j) % (unsigned)tp.stages;
-    const size_t e0 = lo + (blockIdx.x + j * gridDim.x) * (size_t)T;
-    unsigned char *st = smem + (size_t)s * tp.stage_bytes;
-    mbar_expect_tx(&full[s], bytes);
-    unsigned off = 0;
-    if constexpr (PHASE == 0) {
-      for (int p = 0; p < R; ++p)
-        bulk_load(st + p * tp.g_bytes, (const GT *)ra.g[p] + e0, tp.g_bytes, &full[s]);
-      off = R * tp.g_bytes;
-    }
-    bulk_load(st + off, ra.w + e0, T * 4u, &full[s]);
-    if constexpr (OPT != kSGD) {
-      bulk_load(st + off + T * 4u, ra.m + (e0 - lo), T * 4u, &full[s]);
-      bulk_load(st + off + 2u * T * 4u, ra.v + (e0 - lo), T * 4u, &full[s]);
-    }
+// This warp's share of the slice's full tiles: whole SGD / Adam step, or LAMB
+// moments + norm partials.  `ring` is the warp's D stages, `bars` its D
+// barriers (initialised, phase 0).  Returns false if a copy did not land in
+// time (warp-uniform).
+template <int OPT, typename GT, typename LPT>
+__device__ __forceinline__ bool ring_step(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
+                                          size_t lo, size_t ntiles, unsigned char *ring,
+                                          unsigned long long *bars, double &sum_w2,
+                                          double &sum_r2) {
+  constexpr int VEC = 16 / (int)sizeof(GT);
+  constexpr int TE = 32 * VEC;
+  const int R = sa.world;
+  const unsigned D = (unsigned)sa.pipe_stages;
+  const int lane = threadIdx.x & 31;
+  const size_t nwarp = blockDim.x >> 5;
+  const size_t gw = (size_t)blockIdx.x * nwarp + (threadIdx.x >> 5);
+  const size_t GW = (size_t)gridDim.x * nwarp;
+  const size_t mine = ntiles > gw ? (ntiles - gw + GW - 1) / GW : 0;
+  const unsigned stage_bytes = (unsigned)R * kRingTileBytes;
+
+  auto issue = [&](size_t j) {  // lane 0 only
+    const unsigned s = (unsigned)(j % D);
+    const size_t e0 = lo + (gw + j * GW) * (size_t)TE;
+    unsigned char *st = ring + (size_t)s * stage_bytes;
+    mbar_expect_tx(&bars[s], stage_bytes);
+    for (int p = 0; p < R; ++p)
+      bulk_load(st + p * kRingTileBytes, (const GT *)ra.g[p] + e0, kRingTileBytes, &bars[s]);
   };
 
-  if (threadIdx.x == 0)
-    for (size_t j = 0; j < mine && j + 1 < (size_t)tp.stages; ++j) issue(j);
+  if (lane == 0)
+    for (size_t j = 0; j < mine && j < D; ++j) issue(j);
 
   bool ok = true;
   size_t j = 0;
   for (; j < mine; ++j) {
-    // the stage refilled here was consumed one iteration ago (barrier below)
-    if (threadIdx.x == 0 && j + tp.stages - 1 < mine) issue(j + tp.stages - 1);
-    const unsigned it = base + (unsigned)j;
-    const unsigned s = it % (unsigned)tp.stages;
-    if (!mbar_wait(&full[s], (it / (unsigned)tp.stages) & 1u, sa.timeout_ns)) *s_fail = 1;
-    __syncthreads();
-    if (*s_fail) {
+    const unsigned s = (unsigned)(j % D);
+    const bool landed = mbar_wait(&bars[s], (unsigned)((j / D) & 1u), sa.timeout_ns);
+    if (!__all_sync(0xffffffffu, landed)) {
       ok = false;
       break;
     }
-    const size_t e0 = lo + (blockIdx.x + j * gridDim.x) * (size_t)T;
-    tile_math<OPT, GT, LPT, PHASE>(ra, sa, h, smem + (size_t)s * tp.stage_bytes, tp, lo, e0,
-                                   sum_w2, sum_r2, lr_scale);
-    __syncthreads();  // everyone is done reading stage s
+    float g[VEC];
+    ring_reduce<GT, VEC>(ring + (size_t)s * stage_bytes, lane, ra, sa, g);
+    __syncwarp();  // every lane has read stage s: refill it for tile j + D
+    if (lane == 0 && j + D < mine) issue(j + D);
+    const size_t i = lo + (gw + j * GW) * (size_t)TE + (size_t)lane * VEC;
+    apply_unit<OPT, LPT, VEC, 0, 4>(ra, sa, h, lo, i, g, sum_w2, sum_r2);
   }
-  if (!ok && threadIdx.x == 0) {
-    // Copies may still be in flight into this CTA's shared memory: give each
-    // issued tile one more bounded wait before the CTA is allowed to retire.
-    const size_t issued = mine < j + tp.stages ? mine : j + tp.stages;
-    for (size_t k = j; k < issued; ++k) {
-      const unsigned it = base + (unsigned)k;
-      mbar_wait(&full[it % (unsigned)tp.stages], (it / (unsigned)tp.stages) & 1u, sa.timeout_ns);
-    }
+  if (!ok && lane == 0) {
+    // Copies may still be in flight into this warp's ring: give every issued
+    // tile one more bounded wait before the CTA is allowed to retire.
+    const size_t issued = mine < j + D ? mine : j + D;
+    for (size_t k = j; k < issued; ++k)
+      mbar_wait(&bars[k % D], (unsigned)((k / D) & 1u), sa.timeout_ns);
   }
-  iter = base + (unsigned)mine;
+  __syncwarp();
   return ok;
+}
+
+// LAMB's second phase over the elements the rings covered: 16 bytes of
+// gathered output per lane and store.
+template <typename GT, typename LPT>
+__device__ __forceinline__ void ring_apply(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
+                                           size_t lo, size_t nelems, size_t tid, size_t nth,
+                                           float lr_scale) {
+  constexpr int VEC = std::is_same<LPT, NoLp>::value ? 4 : 8;
+  const size_t nunits = nelems / VEC;  // nelems is a multiple of 128
+  for (size_t u = tid; u < nunits; u += nth)
+    lamb_apply_unit<LPT, VEC, 0>(ra, sa, h, lo, lo + u * VEC, lr_scale);
 }
 
 // ---------------------------------------------------------------------------
@@ -1100,23 +1113,23 @@ __device__ __forceinline__ bool run_tiles(const RankArgs &ra, const StepArgs &sa
 // allocation of its own (with all three in one kernel the peer-to-peer loop
 // spilled 376 bytes and lost 6 %): kPathDirect = register-staged peer loads
 // and stores for world sizes 2..8, kPathLocal = the same for world size 1
-// (wider units), kPathNvls = NVSwitch multimem, kPathTiles = bulk-copy pipeline,
+// (wider units), kPathNvls = NVSwitch multimem, kPathRing = gradients staged
+// in per-warp shared-memory rings by bulk copies (any world size),
 // kPathSegments .. kPathSegments + 3 = peer-to-peer over a list of tensors
 // (scattered calls), one kernel per world-size bucket.
 // Every path ends with the same scalar loop for what it does not cover.
-enum : int { kPathDirect = 0, kPathNvls = 1, kPathTiles = 2, kPathLocal = 3, kPathSegments = 4 };
+enum : int { kPathDirect = 0, kPathNvls = 1, kPathRing = 2, kPathLocal = 3, kPathSegments = 4 };
 
 template <int OPT, typename GT, typename LPT, int PATH>
 __global__ void __launch_bounds__(512, 2)
     fused_step_kernel(const __grid_constant__ StepArgs sa, const __grid_constant__ RankArgs one,
                       const RankArgs *__restrict__ table) {
-  extern __shared__ __align__(128) unsigned char tile_smem[];
+  extern __shared__ __align__(128) unsigned char ring_smem[];
   __shared__ RankArgs ra;
   __shared__ int s_ok;
-  __shared__ int s_fail;
   __shared__ float s_lr_scale;
   __shared__ double s_red[2][16];
-  __shared__ __align__(8) unsigned long long s_full[8];
+  __shared__ __align__(8) unsigned long long s_ring_bar[kRingMaxWarps][kRingMaxStages];
 
   {  // this (virtual) rank's pointers -> shared memory
     const RankArgs *src = table ? table + blockIdx.y : &one;
@@ -1124,12 +1137,12 @@ __global__ void __launch_bounds__(512, 2)
     int *d = reinterpret_cast<int *>(&ra);
     for (int k = threadIdx.x; k < (int)(sizeof(RankArgs) / sizeof(int)); k += blockDim.x)
       d[k] = s[k];
-    if (threadIdx.x == 0) {
-      s_ok = 1;
-      s_fail = 0;
-      for (int k = 0; k < sa.pipe_stages; ++k) mbar_init(&s_full[k], 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (threadIdx.x == 0) s_ok = 1;
+    if constexpr (PATH == kPathRing) {
+      if ((threadIdx.x & 31) == 0) {  // every warp's own barriers, one arrival each
+        for (int k = 0; k < sa.pipe_stages; ++k) mbar_init(&s_ring_bar[threadIdx.x >> 5][k], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      }
     }
   }
   __syncthreads();
@@ -1357,27 +1370,32 @@ __global__ void __launch_bounds__(512, 2)
   }
   const bool seg_done = PATH >= kPathSegments;
 
-  // Full tiles go through the bulk-copy pipeline; what is left of the slice
-  // (and everything, when the slice or a pointer is not 16-byte aligned) is
-  // done with direct loads.
-  TilePlan tp;
-  const size_t T = (size_t)kTileElemsPerThread * blockDim.x;
-  tp.stages = (PATH == kPathTiles && ra.aligned16) ? sa.pipe_stages : 0;
-  tp.g_bytes = (unsigned)(T * sizeof(GT));
-  tp.stage_bytes = (unsigned)(R * tp.g_bytes + (OPT == kSGD ? 1 : 3) * T * 4);
-  tp.ntiles = tp.stages > 0 ? L / T : 0;
-  const size_t piped = tp.ntiles * T;  // elements covered by the pipeline
+  // Ring path: the slice's full warp tiles go through the rings; what is left
+  // of the slice (and everything, when the slice or a pointer is not 16-byte
+  // aligned) is done with direct loads.
+  constexpr int kRingTileElems = 32 * (16 / (int)sizeof(GT));
+  const size_t ring_tiles =
+      (PATH == kPathRing && ra.aligned16 && sa.pipe_stages > 0) ? L / kRingTileElems : 0;
+  const size_t piped = ring_tiles * kRingTileElems;  // elements covered by the rings
   const size_t nvec_rest = ra.aligned16 ? (L - piped) / VEC : 0;
-  unsigned iter = 0;
 
   double sum_w2 = 0.0, sum_r2 = 0.0;
-  if constexpr (PATH == kPathTiles) {
-    if (ok && tp.ntiles > 0 &&
-        !run_tiles<OPT, GT, LPT, 0>(ra, sa, h, tp, tile_smem, s_full, &s_fail, lo, iter, sum_w2,
-                                    sum_r2, 0.f)) {
-      if (threadIdx.x == 0) record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
-      ok = false;
+  if constexpr (PATH == kPathRing) {
+    bool landed = true;
+    if (ok && ring_tiles > 0) {
+      const int wid = threadIdx.x >> 5;
+      // ordering of the peers' gradient writes (made visible by the start
+      // barrier's acquire) before this thread's copies through the async proxy
+      asm volatile("fence.proxy.async;" ::: "memory");
+      landed = ring_step<OPT, GT, LPT>(
+          ra, sa, h, lo, ring_tiles,
+          ring_smem + (size_t)wid * sa.pipe_stages * R * kRingTileBytes, s_ring_bar[wid], sum_w2,
+          sum_r2);
+      if (!landed && (threadIdx.x & 31) == 0)
+        record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
     }
+    // a warp whose copies did not land stops the whole CTA (uniformly)
+    if (__syncthreads_or(!landed)) ok = false;
   }
   // NVLS: whole 16-byte units of the slice go through the switch; the rest
   // (and everything when unaligned) falls through to the peer-to-peer code.
@@ -1404,7 +1422,7 @@ __global__ void __launch_bounds__(512, 2)
     else
       direct_step<OPT, GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     const size_t done_elems = PATH == kPathNvls ? nvls_units * NV
-                              : PATH == kPathTiles ? piped : piped + nvec_rest * VEC;
+                              : PATH == kPathRing ? piped : piped + nvec_rest * VEC;
     for (size_t j = done_elems + tid; j < L; j += nth)
       step_unit<OPT, GT, LPT, 1, 0>(ra, sa, h, lo, lo + j, sum_w2, sum_r2);
   }
@@ -1454,7 +1472,13 @@ __global__ void __launch_bounds__(512, 2)
             r2 += ld_volatile_f64(&me->norm_part[p][1]);
           }
           double wn, rn, sc;
-          if (sa.flags & COCO_LAMB_REF_QUIRK) {  // sample :424-433
+          if (sa.variant == cocoVariantNccl) {
+            // forked-NCCL LAMB: float norms, the ratio divided by ||r|| once
+            // more, all in float (common_kernel.h:2699)
+            const float wf = (float)sqrt(w2), rf = (float)sqrt(r2);
+            wn = wf, rn = rf;
+            sc = (double)__fdiv_rn((wf > 0) ? (rf > 0 ? __fdiv_rn(wf, rf) : 1.0f) : 1.0f, rf);
+          } else if (sa.flags & COCO_LAMB_REF_QUIRK) {  // sample :424-433
             rn = sqrt(r2);
             wn = sqrt(w2 / (double)N);
             sc = ((wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0) / rn;
@@ -1473,14 +1497,7 @@ __global__ void __launch_bounds__(512, 2)
     ok = s_ok != 0;
     if (ok) {
       const float lr_scale = s_lr_scale;
-      if constexpr (PATH == kPathTiles) {
-        if (tp.ntiles > 0 &&
-            !run_tiles<OPT, GT, LPT, 1>(ra, sa, h, tp, tile_smem, s_full, &s_fail, lo, iter,
-                                        sum_w2, sum_r2, lr_scale)) {
-          if (threadIdx.x == 0) record_status(me, cocoTimeout, rank, kPhaseCopy, -1, seq);
-          ok = false;
-        }
-      }
+      if constexpr (PATH == kPathRing) ring_apply<GT, LPT>(ra, sa, h, lo, piped, tid, nth, lr_scale);
       if constexpr (PATH == kPathNvls) {
         if (ok && nvls)
           nvls_phase<OPT, GT, LPT, 1>(ra, sa, h, lo, nvls_units, tid, nth, sum_w2, sum_r2,
@@ -1499,7 +1516,7 @@ __global__ void __launch_bounds__(512, 2)
         else
           direct_apply<GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, lr_scale);
         const size_t done_elems = PATH == kPathNvls ? nvls_units * NV
-                                  : PATH == kPathTiles ? piped : piped + nvec_rest * VEC;
+                                  : PATH == kPathRing ? piped : piped + nvec_rest * VEC;
         for (size_t j = done_elems + tid; j < L; j += nth)
           lamb_apply_unit<LPT, 1, 0>(ra, sa, h, lo, lo + j, lr_scale);
       }
@@ -1541,7 +1558,7 @@ __global__ void __launch_bounds__(512, 2)
 template <int OPT, typename GT, typename LPT> KernelPtr pick_path(int path) {
   switch (path) {
     case kPathNvls: return fused_step_kernel<OPT, GT, LPT, kPathNvls>;
-    case kPathTiles: return fused_step_kernel<OPT, GT, LPT, kPathTiles>;
+    case kPathRing: return fused_step_kernel<OPT, GT, LPT, kPathRing>;
     case kPathLocal: return fused_step_kernel<OPT, GT, LPT, kPathLocal>;
     case kPathSegments:
     case kPathSegments + 1:
@@ -1605,15 +1622,53 @@ KernelPtr pick(int opt, cocoDataType_t g, bool has_lp, cocoDataType_t lp, int pa
   return nullptr;
 }
 
-// The path a launch takes: NVLS when the call carries multicast addresses,
-// the tile pipeline when it was given stages, else the register-staged path.
-int path_of(const StepArgs &sa, const RankArgs &ra) {
-  (void)ra;
+}  // namespace
+
+// The path a launch takes: the segment kernels for lists of tensors, NVLS when
+// the call carries multicast addresses, the warp rings when it was given
+// stages, else the register-staged path.
+int fused_step_path(const StepArgs &sa) {
   if (sa.flags & kFlagScattered)  // one kernel per world-size bucket: 1, 2, <= 4, <= 8
     return kPathSegments + (sa.world == 1 ? 0 : sa.world == 2 ? 1 : sa.world <= 4 ? 2 : 3);
   if (sa.flags & kFlagNvls) return kPathNvls;
-  if (sa.pipe_stages > 0) return kPathTiles;
+  if (sa.pipe_stages > 0) return kPathRing;
   return sa.world == 1 ? kPathLocal : kPathDirect;
+}
+
+namespace {
+
+// Per (kernel, threads, dynamic shared memory): the attribute is set and the
+// occupancy queried once, then remembered (both are host calls in the path of
+// every small-message step otherwise).
+struct KernelInfo {
+  int occupancy;
+};
+std::mutex g_info_mu;
+std::map<std::tuple<const void *, int, int, size_t>, KernelInfo> g_info;  // + device
+
+cudaError_t kernel_info(KernelPtr k, int threads, size_t smem_bytes, KernelInfo *out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(g_info_mu);
+  const auto key = std::make_tuple((const void *)k, dev, threads, smem_bytes);
+  auto it = g_info.find(key);
+  if (it != g_info.end()) {
+    *out = it->second;
+    return cudaSuccess;
+  }
+  if (smem_bytes > 0) {  // static + dynamic may exceed the 48 KB default together
+    e = cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem_bytes);
+    if (e != cudaSuccess) return e;
+  }
+  KernelInfo ki = {};
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ki.occupancy, (const void *)k, threads,
+                                                    smem_bytes);
+  if (e != cudaSuccess) return e;
+  g_info[key] = ki;
+  *out = ki;
+  return cudaSuccess;
 }
 
 }  // namespace
@@ -1621,15 +1676,15 @@ int path_of(const StepArgs &sa, const RankArgs &ra) {
 cudaError_t launch_fused_step(int opt, cocoDataType_t g_type, bool has_lp, cocoDataType_t lp_type,
                               const StepArgs &sa, const RankArgs &one, const RankArgs *table,
                               const LaunchConfig &cfg, cudaStream_t stream) {
-  KernelPtr k = pick(opt, g_type, has_lp, lp_type, path_of(sa, one));
+  KernelPtr k = pick(opt, g_type, has_lp, lp_type, fused_step_path(sa));
   if (!k) return cudaErrorInvalidValue;
   const dim3 grid(cfg.ctas, cfg.nvirt > 1 ? cfg.nvirt : 1, 1);
   const dim3 block(cfg.threads, 1, 1);
   const RankArgs *tbl = cfg.nvirt > 1 ? table : nullptr;
   void *params[] = {(void *)&sa, (void *)&one, (void *)&tbl};
-  if (cfg.smem_bytes > 0) {  // static + dynamic may exceed the 48 KB default together
-    cudaError_t e = cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)cfg.smem_bytes);
+  if (cfg.smem_bytes > 0) {  // sets the shared-memory attribute on first use
+    KernelInfo ki;
+    cudaError_t e = kernel_info(k, cfg.threads, cfg.smem_bytes, &ki);
     if (e != cudaSuccess) return e;
   }
   if (cfg.cooperative)
@@ -1638,18 +1693,15 @@ cudaError_t launch_fused_step(int opt, cocoDataType_t g_type, bool has_lp, cocoD
 }
 
 cudaError_t fused_step_occupancy(int opt, cocoDataType_t g_type, bool has_lp,
-                                 cocoDataType_t lp_type, int threads, size_t smem_bytes,
+                                 cocoDataType_t lp_type, int path, int threads, size_t smem_bytes,
                                  int *ctas_per_sm) {
-  // all three paths are built under the same launch bounds
-  KernelPtr k = pick(opt, g_type, has_lp, lp_type, smem_bytes > 0 ? kPathTiles : kPathDirect);
+  KernelPtr k = pick(opt, g_type, has_lp, lp_type, path);  // the instantiation that is launched
   if (!k) return cudaErrorInvalidValue;
-  if (smem_bytes > 0) {
-    cudaError_t e = cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem_bytes);
-    if (e != cudaSuccess) return e;
-  }
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctas_per_sm, (const void *)k, threads,
-                                                       smem_bytes);
+  KernelInfo ki;
+  cudaError_t e = kernel_info(k, threads, smem_bytes, &ki);
+  if (e != cudaSuccess) return e;
+  *ctas_per_sm = ki.occupancy;
+  return cudaSuccess;
 }
 #endif  // dispatch part
 

@@ -15,8 +15,13 @@ struct LaunchConfig {
   int threads;     // threads per CTA
   int nvirt;       // virtual ranks in this launch (grid.y)
   bool cooperative;
-  size_t smem_bytes;  // dynamic shared memory of the tile pipeline
+  size_t smem_bytes;  // dynamic shared memory of the warp rings
 };
+
+// Ring geometry shared by the host's sizing and the kernel: a stage of one
+// warp holds 512 bytes (32 lanes x 16) per rank.
+constexpr int kRingStagesMax = 4;
+constexpr size_t kRingTileBytesPerRank = 512;
 
 // Host entry: enqueue the fused kernel.  `table` (device memory, nvirt
 // entries) is used when nvirt > 1, else `one` is passed by value.
@@ -24,9 +29,19 @@ cudaError_t launch_fused_step(int opt, cocoDataType_t g_type, bool has_lp, cocoD
                               const StepArgs &sa, const RankArgs &one, const RankArgs *table,
                               const LaunchConfig &cfg, cudaStream_t stream);
 
-// Largest number of co-resident CTAs per SM for the given kernel/threads.
+// Data path (kernel instantiation) a call with these scalars takes.
+int fused_step_path(const StepArgs &sa);
+
+// Largest number of co-resident CTAs per SM of the kernel that `path` selects,
+// for this block size and dynamic shared memory (remembered per kernel).
 cudaError_t fused_step_occupancy(int opt, cocoDataType_t g_type, bool has_lp,
-                                 cocoDataType_t lp_type, int threads, size_t smem_bytes,
-                                 int *ctas_per_sm);
+                                 cocoDataType_t lp_type, int path, int threads,
+                                 size_t smem_bytes, int *ctas_per_sm);
+
+// Link probe (link_probe.cu): mode 0 pull, 1 push, 2 both over peer pointers;
+// 4 multimem.ld_reduce, 5 multimem.st, 6 both through ra.mc_g / ra.mc_out;
+// unroll 1, 2 or 4 16-byte units per thread and pass; sa.count in 16-byte units.
+cudaError_t launch_link_probe(int mode, int unroll, const StepArgs &sa, const RankArgs &ra,
+                              int sm_count, int threads, cudaStream_t stream);
 
 }  // namespace coco

@@ -109,6 +109,8 @@ extern "C" int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *
   sa.d1d = 1.0 - std::pow((double)beta1, (double)(step + 1));
   sa.d2d = 1.0 - std::pow((double)beta2, (double)(step + 1));
   sa.d1 = (float)sa.d1d, sa.d2 = (float)sa.d2d;
+  sa.omb1 = 1.0f - beta1, sa.omb2 = 1.0f - beta2;
+  sa.r1d = 1.0 / sa.d1d, sa.r2d = 1.0 / sa.d2d;
   sa.pipe_stages = 0;
 
   RankArgs ra = {};
@@ -123,8 +125,8 @@ extern "C" int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *
   LaunchConfig cfg = {};
   cfg.threads = 512;
   int occ = 0;
-  if (fused_step_occupancy(kLAMB, g_type, w_lp != nullptr, lp_type, cfg.threads, 0, &occ) !=
-          cudaSuccess || occ < 1) {
+  if (fused_step_occupancy(kLAMB, g_type, w_lp != nullptr, lp_type, fused_step_path(sa),
+                           cfg.threads, 0, &occ) != cudaSuccess || occ < 1) {
     (void)cudaGetLastError();
     return cocoCudaError;
   }

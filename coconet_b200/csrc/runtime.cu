@@ -185,8 +185,9 @@ struct cocoComm {
   int ctas_per_sm = 0;  // 0 = automatic
   int threads = 512;
   int timeout_ms = 10000;
-  int smem_budget_kb = 200;  // shared memory the tile pipeline may use per SM
-  bool pipeline = false;     // COCO_PIPELINE=1: stage tiles in shared memory by bulk copies
+  int smem_budget_kb = 200;  // shared memory the warp rings may use per SM
+  int pipeline = -1;         // COCO_PIPELINE: 1 warp rings (bulk copies), 0 register-staged, unset: by world size
+  int ring_stages = 0;       // COCO_RING_STAGES: cap on the stages of a ring, 0 = as many as fit
   int algo = 2;              // 0 p2p, 1 nvls, 2 auto (COCO_ALGO=p2p|nvls|auto)
 };
 
@@ -221,7 +222,8 @@ int init_common(cocoComm *c) {
   c->ctas_per_sm = env_int("COCO_CTAS_PER_SM", 0);
   c->threads = env_int("COCO_THREADS", 512);
   if (c->threads < 32 || c->threads > 512 || (c->threads % 32) != 0) c->threads = 512;
-  c->pipeline = env_int("COCO_PIPELINE", 0) != 0;
+  c->pipeline = env_int("COCO_PIPELINE", -1);
+  c->ring_stages = env_int("COCO_RING_STAGES", 0);
   {
     const char *algo = getenv("COCO_ALGO");
     c->algo = !algo ? 2 : !strcmp(algo, "nvls") ? 1 : !strcmp(algo, "p2p") ? 0 : 2;
@@ -350,6 +352,13 @@ int peer_views(cocoComm *c, const void *ptr, size_t bytes, char *views[kMaxRanks
 // ---- launch configuration ---------------------------------------------------
 bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
 
+// Which data path serves the peer-to-peer step when COCO_PIPELINE is unset.
+bool ring_by_default(int world, int nvirt) {
+  (void)world;
+  (void)nvirt;
+  return false;
+}
+
 int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
                 cocoDataType_t lp_type, size_t count, int world, int nvirt, StepArgs *sa,
                 LaunchConfig *cfg) {
@@ -357,27 +366,37 @@ int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
   if (coop && !c->coop_supported) return cocoInvalidUsage;
   const size_t slice = (count + world - 1) / world;
 
-  // Tile pipeline: as many stages (2..4) as fit the shared-memory budget of
-  // one CTA; off when the slice has no full tile.
-  const int want_per_sm = c->ctas_per_sm > 0 ? c->ctas_per_sm : 2;
-  const size_t tile = (size_t)2 * c->threads;
-  const size_t stage_bytes =
-      (size_t)world * tile * dtype_size(g_type) + (opt == kSGD ? 1 : 3) * tile * 4;
-  const size_t budget = (size_t)c->smem_budget_kb * 1024 / want_per_sm;
-  int stages = (int)std::min<size_t>(4, budget / stage_bytes);
-  if (stages < 2 || slice < tile || !c->pipeline || (sa->flags & kFlagScattered)) stages = 0;
+  // Warp rings (gradients staged in shared memory by bulk copies): every warp
+  // of a CTA holds D stages of `world` 512-byte tiles.  As many stages (up to
+  // 4, or COCO_RING_STAGES) as fit the shared-memory budget of one CTA; off
+  // when the slice has no full tile, for lists of tensors and on the NVLS path.
+  int want_per_sm = c->ctas_per_sm > 0 ? c->ctas_per_sm : 2;
+  const size_t warps = (size_t)c->threads / 32;
+  const size_t stage_bytes = (size_t)world * kRingTileBytesPerRank * warps;
+  const size_t tile_elems = 32 * (16 / dtype_size(g_type));
+  int stages = 0;
+  const bool ring_wanted = c->pipeline > 0 || (c->pipeline < 0 && ring_by_default(world, nvirt));
+  if (ring_wanted && slice >= tile_elems && !(sa->flags & (kFlagScattered | kFlagNvls))) {
+    const size_t budget_sm = (size_t)c->smem_budget_kb * 1024;
+    // at large world sizes one stage of two CTAs may not fit: one CTA per SM then
+    if (budget_sm / want_per_sm < stage_bytes && c->ctas_per_sm <= 0) want_per_sm = 1;
+    stages = (int)std::min<size_t>(kRingStagesMax, budget_sm / want_per_sm / stage_bytes);
+    if (c->ring_stages > 0) stages = std::min(stages, c->ring_stages);
+    if (stages < 1) stages = 0;
+  }
   sa->pipe_stages = stages;
   cfg->smem_bytes = (size_t)stages * stage_bytes;
 
   int occ = 0;
-  CUDA_TRY(fused_step_occupancy(opt, g_type, has_lp, lp_type, c->threads, cfg->smem_bytes, &occ));
+  CUDA_TRY(fused_step_occupancy(opt, g_type, has_lp, lp_type, fused_step_path(*sa), c->threads,
+                                cfg->smem_bytes, &occ));
   if (occ < 1) return cocoInternalError;
   int per_sm = std::min(want_per_sm, occ);
   long ctas = (long)per_sm * c->sm_count;
   if (nvirt > 1) ctas = std::max(1L, ((long)occ * c->sm_count) / nvirt);
-  // no more CTAs than there is work: one tile (or 16-byte unit) per thread pass
+  // no more CTAs than there is work: one warp tile (or 16-byte unit) per thread pass
   const size_t vec = 4;
-  const size_t per_cta = stages > 0 ? tile : vec * c->threads;
+  const size_t per_cta = stages > 0 ? tile_elems * warps : vec * c->threads;
   const long need = (long)std::max<size_t>(1, (slice + per_cta - 1) / per_cta);
   ctas = std::max(1L, std::min(ctas, need));
   ctas = std::min<long>(ctas, kMaxCtasPerRank);
@@ -405,8 +424,10 @@ int validate(const cocoComm *c, const PendingCall &pc) {
   if (pc.sa.variant < cocoVariantOverlap || pc.sa.variant > cocoVariantNccl)
     return cocoInvalidArgument;
   if (pc.sa.variant == cocoVariantNccl) {
-    // the forked-NCCL formulation is defined for fp16 gradients + fp16 copy only
-    if (pc.opt != kAdam || pc.g_type != cocoFloat16 || !pc.w_lp || pc.lp_type != cocoFloat16)
+    // the forked-NCCL formulations (Adam, LAMB) are defined for fp16 gradients
+    // + fp16 copy of one flat buffer only
+    if (pc.opt == kSGD || pc.g_type != cocoFloat16 || !pc.w_lp || pc.lp_type != cocoFloat16 ||
+        !pc.scounts.empty())
       return cocoInvalidArgument;
   }
   if (pc.sa.variant == cocoVariantDsl && pc.opt == kAdam && !(pc.sa.beta1 != 0.f && pc.sa.beta2 != 0.f))
@@ -723,24 +744,34 @@ int enqueue(cocoComm *c, PendingCall &pc) {
   return launch_single(c, pc, g_views, out_views, mc_g, mc_out);
 }
 
+// What the kernel would otherwise derive per thread: 1 - beta as a float
+// subtraction, the reciprocals of the double denominators.
+void finish_scalars(StepArgs *sa) {
+  sa->omb1 = 1.0f - sa->beta1;
+  sa->omb2 = 1.0f - sa->beta2;
+  sa->r1d = 1.0 / sa->d1d;
+  sa->r2d = 1.0 / sa->d2d;
+}
+
 void set_denominators(StepArgs *sa, int opt, int step) {
   // m^ = m/d1, v^ = v/d2.  overlap: 1 - beta^t evaluated in double as the
   // reference's host check does (multi-process-adam-scattered.cpp:118-119);
-  // dsl Adam / nccl: beta (adam.cpp:68-69, reduce_kernel.h:33-47);
-  // dsl LAMB: 1 - beta (lamb.cpp:82-83).
+  // dsl Adam / nccl Adam and LAMB: beta (adam.cpp:68-69, reduce_kernel.h:33-47,
+  // 403-410); dsl LAMB: 1 - beta (lamb.cpp:82-83).
   sa->d1d = sa->d2d = 1.0;
   if (sa->variant == cocoVariantOverlap) {
     sa->d1d = 1.0 - std::pow((double)sa->beta1, (double)(step + 1));
     sa->d2d = 1.0 - std::pow((double)sa->beta2, (double)(step + 1));
     sa->d1 = (float)sa->d1d;
     sa->d2 = (float)sa->d2d;
-  } else if (opt == kLAMB) {
+  } else if (opt == kLAMB && sa->variant == cocoVariantDsl) {
     sa->d1 = 1.0f - sa->beta1;
     sa->d2 = 1.0f - sa->beta2;
   } else {
     sa->d1 = sa->beta1;
     sa->d2 = sa->beta2;
   }
+  finish_scalars(sa);
 }
 
 }  // namespace
@@ -1133,7 +1164,7 @@ int cocoFusedLAMB(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *
                   cocoDataType_t lp_type, float *m, float *v, size_t count, float lr,
                   float beta1, float beta2, float eps, float weight_decay, int step,
                   float grad_scale, cocoVariant_t variant, unsigned flags, cocoStream_t stream) {
-  if (!comm || step < 0 || variant == cocoVariantNccl) return cocoInvalidArgument;
+  if (!comm || step < 0) return cocoInvalidArgument;
   PendingCall pc;
   pc.opt = kLAMB;
   pc.g = g, pc.g_type = g_type, pc.w = w, pc.w_lp = w_lp, pc.lp_type = lp_type;
@@ -1141,7 +1172,9 @@ int cocoFusedLAMB(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *
   pc.sa.count = count;
   pc.sa.lr = lr, pc.sa.beta1 = beta1, pc.sa.beta2 = beta2;
   pc.sa.eps = variant == cocoVariantOverlap ? eps : 0.f;  // lamb.cpp:72,84: epsilon unused
-  pc.sa.weight_decay = weight_decay;
+  // the forked-NCCL functor hard-codes the decay factor (reduce_kernel.h:427)
+  pc.sa.weight_decay = variant == cocoVariantNccl ? 1.0f : weight_decay;
+  if (variant == cocoVariantNccl) flags &= ~COCO_LAMB_REF_QUIRK;  // it has its own norm rule
   pc.sa.grad_scale = grad_scale;
   pc.sa.variant = (int)variant;
   pc.sa.flags = flags;
@@ -1266,6 +1299,104 @@ int cocoFusedLAMBScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
   pc.sa.flags = flags;
   set_denominators(&pc.sa, kLAMB, step);
   return enqueue_scattered(comm, kLAMB, nbuff, g, g_type, w, counts, m, v, pc, stream);
+}
+
+int cocoLinkProbe(cocoComm_t comm, void *buf, size_t bytes, int mode, int unroll, int iters,
+                  double *gbs_per_direction, cocoStream_t stream) {
+  if (!comm || !buf || !gbs_per_direction || iters < 1 || mode < 0 || mode > 6)
+    return cocoInvalidArgument;
+  if (mode != 3 && unroll != 1 && unroll != 2 && unroll != 4) return cocoInvalidArgument;
+  if ((((uintptr_t)buf) & 15u) != 0 || bytes < 32u * (size_t)comm->world) return cocoInvalidArgument;
+  if (comm->group) return cocoInvalidUsage;  // one process per GPU
+  *gbs_per_direction = 0.0;
+  if (comm->world == 1) return cocoSuccess;  // no link to measure
+  DeviceGuard guard(comm->device);
+  if (!guard.ok) return cocoCudaError;
+  const int R = comm->world;
+  cudaStream_t st = (cudaStream_t)stream;
+  char *views[kMaxRanks] = {};
+  char *mc = nullptr;
+  COCO_TRY(peer_views(comm, buf, bytes, views, &mc));
+
+  PendingCall pc;
+  pc.opt = kSGD;
+  pc.g = buf, pc.w = (float *)buf;
+  pc.sa.count = bytes / 16;  // 16-byte units
+  pc.sa.world = R;
+  pc.sa.timeout_ns = (unsigned long long)comm->timeout_ms * 1000000ull;
+  RankArgs ra;
+  fill_rank_args(&ra, comm->rank, R, views, views, comm->peer_flags, pc);
+  if (mode >= 4) {  // through the switch: the buffer needs a multicast mapping
+    if (!mc || !aligned16(mc)) return cocoInvalidUsage;
+    ra.mc_g = mc;
+    ra.mc_out = mc;
+  }
+  const size_t slice_units = (pc.sa.count + R - 1) / R;
+  double dir_bytes = 0.0;  // bytes crossing this GPU's links in one direction per iteration
+  const size_t half = bytes / 2 / 16 * 16;
+  if (mode == 3) {
+    dir_bytes = (double)half;
+  } else {
+    size_t lo = (size_t)comm->rank * slice_units;
+    if (lo > pc.sa.count) lo = pc.sa.count;
+    const size_t len = std::min<size_t>(pc.sa.count - lo, slice_units);
+    if (mode <= 2)  // peer to peer: R - 1 slices in (pull) and / or out (push)
+      dir_bytes = (double)(R - 1) * (double)len * 16.0 * (mode == 2 ? 2.0 : 1.0);
+    else  // switch: the whole buffer leaves (reduce) or arrives (store) once, the slice the other way
+      dir_bytes = (double)pc.sa.count * 16.0 + (mode == 6 ? (double)len * 16.0 : 0.0);
+  }
+
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  CUDA_TRY(cudaEventCreate(&e0));
+  CUDA_TRY(cudaEventCreate(&e1));
+  int result = cocoSuccess;
+  auto once = [&]() -> int {
+    if (mode == 3) {  // copy engine: the next rank's first half into this rank's second half
+      const int p = (comm->rank + 1) % R;
+      if (cudaMemcpyAsync((char *)buf + half, views[p], half, cudaMemcpyDefault, st) != cudaSuccess)
+        return cocoCudaError;
+      return cocoSuccess;
+    }
+    pc.sa.seq = ++comm->seq;
+    if (launch_link_probe(mode, unroll, pc.sa, ra, comm->sm_count, 512, st) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return cocoCudaError;
+    }
+    comm->launches++;
+    return cocoSuccess;
+  };
+  // every rank takes every step whatever happens locally, so that the ranks'
+  // sequence numbers stay in step
+  int rc = once();  // warm-up
+  if (rc != cocoSuccess) result = rc;
+  if (cudaStreamSynchronize(st) != cudaSuccess) result = cocoCudaError;
+  rc = comm->boot->barrier();
+  if (rc != cocoSuccess && result == cocoSuccess) result = rc;
+  cudaEventRecord(e0, st);
+  for (int i = 0; i < iters; ++i) {
+    rc = once();
+    if (rc != cocoSuccess && result == cocoSuccess) result = rc;
+  }
+  cudaEventRecord(e1, st);
+  if (cudaStreamSynchronize(st) != cudaSuccess) result = cocoCudaError;
+  float ms = 0.f;
+  if (cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) result = cocoCudaError;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  (void)cudaGetLastError();
+  // the slowest rank's time and the smallest byte count give the figure all ranks report
+  std::vector<double> all(2 * (size_t)R);
+  const double mine[2] = {(double)ms / iters, dir_bytes};
+  rc = comm->boot->all_gather(mine, all.data(), sizeof(mine));
+  if (rc != cocoSuccess) return rc;
+  if (result != cocoSuccess) return result;
+  double worst_ms = 0.0, least_bytes = dir_bytes;
+  for (int r = 0; r < R; ++r) {
+    worst_ms = std::max(worst_ms, all[2 * r]);
+    least_bytes = std::min(least_bytes, all[2 * r + 1]);
+  }
+  if (worst_ms > 0.0) *gbs_per_direction = least_bytes / (worst_ms * 1e-3) / 1e9;
+  return cocoSuccess;
 }
 
 int cocoLastLambNorms(cocoComm_t comm, double out[2]) {

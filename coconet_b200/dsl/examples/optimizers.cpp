@@ -3,7 +3,7 @@
 //   AR_C          AllReduce, then the update on every element on every rank
 //   RS_C_AG       ReduceScatter, update of the rank's slice, AllGather
 //   fuse_RS_C_AG  the same, fused into one kernel (the B200 runtime's path)
-// usage: optimizers <sgd|adam|lamb|nesterov> <AR_C|RS_C_AG|fuse_RS_C_AG> [output.cu]
+// usage: optimizers <sgd|adam|lamb|nesterov|adam_derived|adam_mixed> <AR_C|RS_C_AG|fuse_RS_C_AG> [output.cu]
 //        optimizers <sgd|adam|lamb|nesterov> autotune [output directory]
 //          (the program written once with AllReduce; the three schedules are derived)
 #include <dsl.hpp>
@@ -110,6 +110,42 @@ static void lamb(const std::string &schedule, const std::string &out) {
   pipeline.codegen(out);
 }
 
+// Mixed-precision Adam: fp16 gradients with a loss scale, fp32 master weights
+// that every rank keeps for its own slice only, fp32 Sliced moments, and the
+// fp16 weights the model computes with, gathered to all ranks.  The fused
+// schedule becomes ONE cocoFusedAdam call with the fp16 copy as its gathered
+// output (what the reference's hook hard-codes as `(half*)g, w, (half*)w`,
+// src/codegen.cpp:1910).
+static void adam_mixed(const std::string &schedule, const std::string &out) {
+  if (schedule == "AR_C" || schedule == "autotune") {
+    std::cout << "adam_mixed is written on slices: RS_C_AG or fuse_RS_C_AG" << std::endl;
+    exit(1);
+  }
+  Variable N(Int32, "N");
+  Variable lr(Float32, "lr"), beta1(Float32, "beta1"), beta2(Float32, "beta2");
+  Variable inv_scale(Float32, "inv_scale");
+  Tensor g(Float16, N, Local, "g");
+  Tensor w(Float32, N, Sliced, "w");
+  Tensor wh(Float16, N, Replicated, "wh");
+  Tensor m(Float32, N, Sliced, "m");
+  Tensor v(Float32, N, Sliced, "v");
+  Stage gred = ReduceScatter(Summation, g);
+  Stage gs = Cast(Float32, gred) * inv_scale;
+  Stage mnew = Update(m, beta1 * m + (1 - beta1) * gs);
+  Stage vnew = Update(v, beta2 * v + (1 - beta2) * gs * gs);
+  Stage mhat = mnew / beta1;
+  Stage vhat = vnew / beta2;
+  Stage wnew = Update(w, w - lr * mhat / vhat);
+  Stage wcast = Cast(Float16, wnew);
+  Stage whnew = Update(wh, AllGather(wcast));
+  Pipeline pipeline("adam_mixed", {g, w, wh, m, v, lr, beta1, beta2, inv_scale}, {mnew, vnew, wnew, whnew});
+  if (schedule == "fuse_RS_C_AG")
+    pipeline.fuse({gred, gs, mnew, vnew, mhat, vhat, wnew, wcast, whnew});
+  else
+    pipeline.fuse({gs, mnew, vnew, mhat, vhat, wnew, wcast});
+  pipeline.codegen(out);
+}
+
 // Adam written ONCE, as AllReduce + update on every element, and then scheduled
 // with CoCoNet's transformations instead of being rewritten by hand:
 //   split    AllReduce -> ReduceScatter + AllGather
@@ -203,6 +239,7 @@ int main(int argc, char **argv) {
   else if (opt == "lamb") lamb(schedule, out);
   else if (opt == "nesterov") nesterov(schedule, out);
   else if (opt == "adam_derived") adam_derived(schedule, out);
+  else if (opt == "adam_mixed") adam_mixed(schedule, out);
   else { std::cout << "Invalid optimizer" << std::endl; return 1; }
   return 0;
 }

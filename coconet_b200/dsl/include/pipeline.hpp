@@ -19,6 +19,15 @@ struct FusedUpdate {
   enum Rule { Unknown = 0, SGD, Adam, LAMB } rule = Unknown;
   NodeRef grad, weight, m, v;                 // tensors
   std::string lr, beta1, beta2, decay;        // Variable names
+  // Mixed precision: `weight` is the fp32 master (a Sliced tensor: every rank
+  // keeps its own slice) and `lp` the 16-bit Replicated copy that is gathered
+  // to all ranks (the halfw argument of the reference's hook,
+  // src/codegen.cpp:1910).  Absent otherwise.
+  NodeRef lp;
+  // The reduced gradient is multiplied (or, with gscale_div, divided) by this
+  // Variable before it is used: the loss scale of mixed-precision training.
+  std::string gscale;
+  bool gscale_div = false;
 };
 
 // Schedule transformations (surface of the reference's src/pipeline.hpp:51-54,

@@ -135,6 +135,23 @@ static inline bool coconetClose(float ref, float got) {
   return d <= 1e-4f * m + 1e-6f;
 }
 
+// 16-bit results: one unit in the last place of a half is 2^-11 relative
+static inline bool coconetCloseHalf(float ref, float got) {
+  if (ref != ref && got != got) return true;
+  const float d = fabsf(ref - got), m = fmaxf(fabsf(ref), fabsf(got));
+  return d <= 1.5e-3f * m + 1e-6f;
+}
+static inline float coconetRoundHalf(float x) { return __half2float(__float2half(x)); }
+// Device tensor -> host vector of float (the host check computes in float).
+static inline void coconetToHost(std::vector<float> &h, const float *d, size_t n) {
+  CUDACHECK(cudaMemcpy(h.data(), d, n * sizeof(float), cudaMemcpyDeviceToHost));
+}
+static inline void coconetToHost(std::vector<float> &h, const half *d, size_t n) {
+  std::vector<half> tmp(n);
+  CUDACHECK(cudaMemcpy(tmp.data(), d, n * sizeof(half), cudaMemcpyDeviceToHost));
+  for (size_t i = 0; i < n; i++) h[i] = __half2float(tmp[i]);
+}
+
 // ---- pieces of the unfused schedules ------------------------------------------
 static inline size_t coconetSliceLen(size_t n, int comm_size, int rank) {
   size_t b = 0, e = 0;

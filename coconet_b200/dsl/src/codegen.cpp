@@ -487,23 +487,37 @@ struct Emitter {
     std::ostringstream c;
     const std::string gt = cocoType(fu.grad->type);
     if (fu.weight->type != Float32) fail("the fused step keeps fp32 weights ('" + fu.weight->name + "')");
+    // Mixed precision (the reference's hook passes `(half*)g, w, (half*)w`,
+    // src/codegen.cpp:1910): the 16-bit Replicated copy is what is gathered; the
+    // fp32 master is a Sliced tensor, which the runtime indexes by GLOBAL element
+    // inside the rank's slice only -- hence the pointer moved back by the slice
+    // start.
+    std::string w = fu.weight->name, lp = "NULL", lpt = "cocoFloat16";
+    if (fu.lp) {
+      if (fu.weight->layout != Sliced) fail("mixed precision: the fp32 master '" + w + "' must be Sliced");
+      w = "(" + w + " - (size_t)" + sliceCount() + " * rank)";
+      lp = fu.lp->name;
+      lpt = cocoType(fu.lp->type);
+    }
+    const std::string gs = fu.gscale.empty() ? std::string("1.0f")
+                           : fu.gscale_div ? "(1.0f / " + fu.gscale + ")" : fu.gscale;
     switch (fu.rule) {
       case FusedUpdate::SGD:
-        c << "cocoFusedSGD(comm, " << fu.grad->name << ", " << gt << ", " << fu.weight->name
-          << ", NULL, cocoFloat16, " << N() << ", " << orOne(fu.lr) << ", 1.0f, stream)";
+        c << "cocoFusedSGD(comm, " << fu.grad->name << ", " << gt << ", " << w << ", " << lp << ", "
+          << lpt << ", " << N() << ", " << orOne(fu.lr) << ", " << gs << ", stream)";
         break;
       case FusedUpdate::Adam:
-        c << "cocoFusedAdam(comm, " << fu.grad->name << ", " << gt << ", " << fu.weight->name
-          << ", NULL, cocoFloat16, " << fu.m->name << ", " << fu.v->name << ", " << N() << ", "
+        c << "cocoFusedAdam(comm, " << fu.grad->name << ", " << gt << ", " << w << ", " << lp << ", "
+          << lpt << ", " << fu.m->name << ", " << fu.v->name << ", " << N() << ", "
           << orOne(fu.lr) << ", " << fu.beta1 << ", " << fu.beta2
-          << ", 0.0f, iter, 1.0f, cocoVariantDsl, stream)";
+          << ", 0.0f, iter, " << gs << ", cocoVariantDsl, stream)";
         break;
       case FusedUpdate::LAMB:
-        c << "cocoFusedLAMB(comm, " << fu.grad->name << ", " << gt << ", " << fu.weight->name
-          << ", NULL, cocoFloat16, " << fu.m->name << ", " << fu.v->name << ", " << N() << ", "
+        c << "cocoFusedLAMB(comm, " << fu.grad->name << ", " << gt << ", " << w << ", " << lp << ", "
+          << lpt << ", " << fu.m->name << ", " << fu.v->name << ", " << N() << ", "
           << orOne(fu.lr) << ", " << fu.beta1 << ", " << fu.beta2 << ", 0.0f, "
           << (fu.decay.empty() ? std::string("0.0f") : fu.decay)
-          << ", iter, 1.0f, cocoVariantDsl, 0, stream)";
+          << ", iter, " << gs << ", cocoVariantDsl, 0, stream)";
         break;
       default: fail("unclassified fused group");
     }
@@ -603,7 +617,9 @@ struct Emitter {
       case NodeKind::Binary:
         return "(" + hostExpr(n->in[0], false) + " " + n->op + " " + hostExpr(n->in[1], false) + ")";
       case NodeKind::Sqrt: return "sqrtf(" + hostExpr(n->in[0], false) + ")";
-      case NodeKind::Cast: return "((float)" + hostExpr(n->in[0], false) + ")";
+      case NodeKind::Cast:  // values are held as float on the host: a cast to half rounds
+        return n->type == Float16 ? "coconetRoundHalf(" + hostExpr(n->in[0], false) + ")"
+                                  : "((float)" + hostExpr(n->in[0], false) + ")";
       case NodeKind::Scatter:
       case NodeKind::AllGather:
       case NodeKind::Broadcast: return hostExpr(n->in[0], false);
@@ -613,6 +629,11 @@ struct Emitter {
         return "coconetRankSum(" + hostExpr(n->in[0], false) + ", comm_size)";
       default: fail("cannot emit node in the host reference");
     }
+  }
+
+  // a 16-bit tensor may differ from the host's rounding by one unit in its last place
+  static std::string closeFn(const NodeRef &t) {
+    return t->type == Float16 ? "coconetCloseHalf" : "coconetClose";
   }
 
   void emitHostRef(std::ostream &os) const {
@@ -645,12 +666,12 @@ struct Emitter {
       const NodeRef &t = s->in[0];
       if (t->layout == Sliced) {
         os << "  for (size_t j = 0; j < len && ok; j++)\n"
-           << "    if (!coconetClose(v_" << s->name << "[lo + j], d_" << t->name << "[j])) {\n"
+           << "    if (!" << closeFn(t) << "(v_" << s->name << "[lo + j], d_" << t->name << "[j])) {\n"
            << "      printf(\"rank %d: mismatch in " << t->name << "[%ld]: ref %g, computed %g\\n\", rank, (long)j, v_"
            << s->name << "[lo + j], d_" << t->name << "[j]);\n      ok = false;\n    }\n";
       } else {
         os << "  for (size_t i0 = 0; i0 < " << N() << " && ok; i0++)\n"
-           << "    if (!coconetClose(v_" << s->name << "[i0], d_" << t->name << "[i0])) {\n"
+           << "    if (!" << closeFn(t) << "(v_" << s->name << "[i0], d_" << t->name << "[i0])) {\n"
            << "      printf(\"rank %d: mismatch in " << t->name << "[%ld]: ref %g, computed %g\\n\", rank, (long)i0, v_"
            << s->name << "[i0], d_" << t->name << "[i0]);\n      ok = false;\n    }\n";
       }
@@ -721,8 +742,10 @@ struct Emitter {
     decl.push_back("int rank");
     call.push_back("rank");
 
+    // the host evaluation holds every value as float: programs over fp32 and fp16
     bool all_float = true;
-    for (const NodeRef &a : args) all_float = all_float && a->type == Float32;
+    for (const NodeRef &a : args)
+      all_float = all_float && (a->type == Float32 || (a->type == Float16 && a->kind == NodeKind::Tensor));
     if (all_float) emitHostRef(os);
 
     os << "void " << p.name() << "(";
@@ -790,9 +813,9 @@ struct Emitter {
     // allocator (peer mappings + NVSwitch multicast where the node has it).
     std::set<const Node *> symmetric;
     for (const Step &st : steps) {
-      if (st.kind == Step::Fused) {
+      if (st.kind == Step::Fused) {  // what peers read (gradients) and write (the gathered tensor)
         symmetric.insert(st.fused.grad.get());
-        symmetric.insert(st.fused.weight.get());
+        symmetric.insert(st.fused.lp ? st.fused.lp.get() : st.fused.weight.get());
       }
       if (st.kind == Step::FusedGeneric) {
         symmetric.insert(st.ggrad.get());
@@ -848,8 +871,7 @@ struct Emitter {
         if (a->kind == NodeKind::Tensor) {
           const std::string cnt = a->layout == Sliced ? sliceCount() : N();
           os << "      std::vector<float> h_" << a->name << "(" << cnt << "), d_" << a->name << "(" << cnt << ");\n";
-          os << "      CUDACHECK(cudaMemcpy(h_" << a->name << ".data(), " << a->name << ", " << cnt
-             << " * sizeof(float), cudaMemcpyDeviceToHost));\n";
+          os << "      coconetToHost(h_" << a->name << ", " << a->name << ", " << cnt << ");\n";
         }
       os << "      { int iter = 0; " << p.name() << "(";
       for (size_t k = 0; k < call.size(); ++k) os << (k ? ", " : "") << call[k];
@@ -859,8 +881,7 @@ struct Emitter {
       for (const NodeRef &a : args)
         if (a->kind == NodeKind::Tensor) {
           const std::string cnt = a->layout == Sliced ? sliceCount() : N();
-          os << "      CUDACHECK(cudaMemcpy(d_" << a->name << ".data(), " << a->name << ", " << cnt
-             << " * sizeof(float), cudaMemcpyDeviceToHost));\n";
+          os << "      coconetToHost(d_" << a->name << ", " << a->name << ", " << cnt << ");\n";
         }
       os << "      bool pass = hostRef(" << N() << ", comm_size, rank";
       for (const NodeRef &a : args) {

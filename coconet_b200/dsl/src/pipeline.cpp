@@ -289,75 +289,125 @@ FusedUpdate Pipeline::classify(const std::vector<NodeRef> &group) const {
   std::vector<NodeRef> with_absent = fvars;
   with_absent.push_back(nullptr);
 
-  if (state.empty() && norms.empty()) {  // SGD: w' = w - lr * g
-    for (const NodeRef &lr : with_absent) {
-      bool ok = true;
+  // Mixed precision: the gathered Replicated tensor is a 16-bit COPY of fp32
+  // master weights that every rank keeps as a Sliced tensor.  The master is the
+  // Sliced update whose new value is the one the copy receives (a Cast is the
+  // identity on the sample values).
+  if (fu.weight->type == Float16) {
+    NodeRef master;
+    for (const NodeRef &u : state) {
+      bool same = u->in[0]->type == Float32;
       for (const Probe &p : probes)
-        ok = ok && close(p.updated.at(fu.weight.get()),
-                         val(p, fu.weight) - opt(p, lr) * val(p, fu.grad));
-      if (ok) {
-        fu.rule = FusedUpdate::SGD;
-        fu.lr = lr ? lr->name : "";
-        return fu;
+        same = same && close(p.updated.at(u->in[0].get()), p.updated.at(fu.weight.get()));
+      if (same) {
+        if (master) return fu;  // ambiguous
+        master = u;
       }
     }
+    if (!master) return fu;  // 16-bit weights without an fp32 master: no kernel for that
+    fu.lp = fu.weight;
+    fu.weight = master->in[0];
+    state.erase(std::find(state.begin(), state.end(), master));
+  }
+
+  // The gradient as the update uses it: the reduced sum itself, or the sum
+  // times / divided by one Variable (the loss scale).
+  struct GradForm {
+    NodeRef var;
+    bool div;
+  };
+  std::vector<GradForm> gforms = {{nullptr, false}};
+  for (const NodeRef &s : fvars) {
+    gforms.push_back({s, false});
+    gforms.push_back({s, true});
+  }
+  auto geff = [&](const Probe &p, const GradForm &f) {
+    const double g = val(p, fu.grad);
+    return !f.var ? g : f.div ? g / val(p, f.var) : g * val(p, f.var);
+  };
+  auto note_scale = [&](const GradForm &f) {
+    fu.gscale = f.var ? f.var->name : "";
+    fu.gscale_div = f.div;
+  };
+
+  if (state.empty() && norms.empty()) {  // SGD: w' = w - lr * g
+    for (const GradForm &gf : gforms)
+      for (const NodeRef &lr : with_absent) {
+        if (gf.var && gf.var == lr) continue;
+        bool ok = true;
+        for (const Probe &p : probes)
+          ok = ok && close(p.updated.at(fu.weight.get()),
+                           val(p, fu.weight) - opt(p, lr) * geff(p, gf));
+        if (ok) {
+          fu.rule = FusedUpdate::SGD;
+          fu.lr = lr ? lr->name : "";
+          note_scale(gf);
+          // w - (lr * s) * g cannot be told from w - lr * (s * g): with both a
+          // learning rate and a scale the first match (no scale) is kept
+          return fu;
+        }
+      }
     return fu;
   }
   if (state.size() != 2) return fu;
 
-  for (int perm = 0; perm < 2; ++perm) {
-    const NodeRef m = state[perm]->in[0], v = state[1 - perm]->in[0];
-    for (const NodeRef &b1 : fvars)
-      for (const NodeRef &b2 : fvars) {
-        bool moments_ok = true;
-        for (const Probe &p : probes) {
-          const double g = val(p, fu.grad);
-          moments_ok = moments_ok &&
-                       close(p.updated.at(m.get()), val(p, b1) * val(p, m) + (1 - val(p, b1)) * g) &&
-                       close(p.updated.at(v.get()), val(p, b2) * val(p, v) + (1 - val(p, b2)) * g * g);
-        }
-        if (!moments_ok) continue;
-        if (norms.empty()) {  // Adam as the DSL writes it: w - lr * (m'/b1) / (v'/b2)
-          for (const NodeRef &lr : with_absent) {
-            bool ok = true;
-            for (const Probe &p : probes) {
-              const double mh = p.updated.at(m.get()) / val(p, b1);
-              const double vh = p.updated.at(v.get()) / val(p, b2);
-              ok = ok && close(p.updated.at(fu.weight.get()), val(p, fu.weight) - opt(p, lr) * mh / vh);
-            }
-            if (ok) {
-              fu.rule = FusedUpdate::Adam;
-              fu.m = m, fu.v = v;
-              fu.beta1 = b1->name, fu.beta2 = b2->name, fu.lr = lr ? lr->name : "";
-              return fu;
-            }
+  for (const GradForm &gf : gforms)
+    for (int perm = 0; perm < 2; ++perm) {
+      const NodeRef m = state[perm]->in[0], v = state[1 - perm]->in[0];
+      for (const NodeRef &b1 : fvars)
+        for (const NodeRef &b2 : fvars) {
+          if (gf.var && (gf.var == b1 || gf.var == b2)) continue;
+          bool moments_ok = true;
+          for (const Probe &p : probes) {
+            const double g = geff(p, gf);
+            moments_ok = moments_ok &&
+                         close(p.updated.at(m.get()), val(p, b1) * val(p, m) + (1 - val(p, b1)) * g) &&
+                         close(p.updated.at(v.get()), val(p, b2) * val(p, v) + (1 - val(p, b2)) * g * g);
           }
-        } else if (norms.size() == 2) {  // LAMB: r = m^/sqrt(v^) + decay*w; w - lr*(|w|/|r|)*r
-          for (int np = 0; np < 2; ++np) {
-            const NodeRef nw = norms[np], nr = norms[1 - np];
-            for (const NodeRef &lr : with_absent)
-              for (const NodeRef &wd : with_absent) {
-                bool ok = true;
-                for (Probe &p : probes) {
-                  const double mh = p.updated.at(m.get()) / (1 - val(p, b1));
-                  const double vh = p.updated.at(v.get()) / (1 - val(p, b2));
-                  const double r = mh / std::sqrt(vh) + opt(p, wd) * val(p, fu.weight);
-                  ok = ok && close(p.eval(nr->in[0]), r) && close(p.eval(nw->in[0]), val(p, fu.weight)) &&
-                       close(p.updated.at(fu.weight.get()),
-                             val(p, fu.weight) - opt(p, lr) * (val(p, nw) / val(p, nr)) * r);
-                }
-                if (ok) {
-                  fu.rule = FusedUpdate::LAMB;
-                  fu.m = m, fu.v = v;
-                  fu.beta1 = b1->name, fu.beta2 = b2->name;
-                  fu.lr = lr ? lr->name : "", fu.decay = wd ? wd->name : "";
-                  return fu;
-                }
+          if (!moments_ok) continue;
+          if (norms.empty()) {  // Adam as the DSL writes it: w - lr * (m'/b1) / (v'/b2)
+            for (const NodeRef &lr : with_absent) {
+              bool ok = true;
+              for (const Probe &p : probes) {
+                const double mh = p.updated.at(m.get()) / val(p, b1);
+                const double vh = p.updated.at(v.get()) / val(p, b2);
+                ok = ok && close(p.updated.at(fu.weight.get()), val(p, fu.weight) - opt(p, lr) * mh / vh);
               }
+              if (ok) {
+                fu.rule = FusedUpdate::Adam;
+                fu.m = m, fu.v = v;
+                fu.beta1 = b1->name, fu.beta2 = b2->name, fu.lr = lr ? lr->name : "";
+                note_scale(gf);
+                return fu;
+              }
+            }
+          } else if (norms.size() == 2) {  // LAMB: r = m^/sqrt(v^) + decay*w; w - lr*(|w|/|r|)*r
+            for (int np = 0; np < 2; ++np) {
+              const NodeRef nw = norms[np], nr = norms[1 - np];
+              for (const NodeRef &lr : with_absent)
+                for (const NodeRef &wd : with_absent) {
+                  bool ok = true;
+                  for (Probe &p : probes) {
+                    const double mh = p.updated.at(m.get()) / (1 - val(p, b1));
+                    const double vh = p.updated.at(v.get()) / (1 - val(p, b2));
+                    const double r = mh / std::sqrt(vh) + opt(p, wd) * val(p, fu.weight);
+                    ok = ok && close(p.eval(nr->in[0]), r) && close(p.eval(nw->in[0]), val(p, fu.weight)) &&
+                         close(p.updated.at(fu.weight.get()),
+                               val(p, fu.weight) - opt(p, lr) * (val(p, nw) / val(p, nr)) * r);
+                  }
+                  if (ok) {
+                    fu.rule = FusedUpdate::LAMB;
+                    fu.m = m, fu.v = v;
+                    fu.beta1 = b1->name, fu.beta2 = b2->name;
+                    fu.lr = lr ? lr->name : "", fu.decay = wd ? wd->name : "";
+                    note_scale(gf);
+                    return fu;
+                  }
+                }
+            }
           }
         }
-      }
-  }
+    }
   return fu;
 }
 

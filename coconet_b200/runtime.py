@@ -93,6 +93,8 @@ _SIGNATURES = {
     "cocoAllGather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cocoFusedGenericPlan": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t,
                                        C.c_float, C.c_void_p, C.c_void_p]),
+    "cocoLinkProbe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int,
+                                C.POINTER(C.c_double), C.c_void_p]),
     "cocoLastLambNorms": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "cocoGetStatus": (C.c_int, [C.c_void_p, C.POINTER(_Status)]),
     "cocoSliceBounds": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_size_t),
@@ -382,6 +384,19 @@ class Communicator:
                                             _ptr(v), lr, beta1, beta2, eps, weight_decay, step,
                                             grad_scale, variant, flags, _stream(stream)),
                "cocoFusedLAMBScattered")
+
+    def link_probe(self, buf, mode, unroll=1, iters=5, stream=None):
+        """GB/s per direction per GPU of a pull ("pull"), push ("push"), pull +
+        push ("both") kernel with the fused step's access shape, of the copy
+        engine ("copy"), or of the same through the NVSwitch ("switch_reduce",
+        "switch_store", "switch_both"; `buf` from mem_alloc), over `buf`
+        (overwritten).  Collective; synchronises."""
+        code = {"pull": 0, "push": 1, "both": 2, "copy": 3, "switch_reduce": 4,
+                "switch_store": 5, "switch_both": 6}[mode]
+        out = C.c_double()
+        _check(lib().cocoLinkProbe(self._h, _ptr(buf), buf.numel() * buf.element_size(), code,
+                                   unroll, iters, C.byref(out), _stream(stream)), "cocoLinkProbe")
+        return out.value
 
     # ---- introspection ----
     def status(self):

@@ -78,9 +78,9 @@ inline int AllReduce_pipe(float lr, float beta1, float beta2, __half *g, float *
                        beta1, beta2, 0.0f, 0, 1.0f, cocoVariantNccl, stream);
 }
 
-/* LAMB form (nccl/src/nccl.h.in:215).  Computes the LAMB of the DSL program the
- * call was emitted from (examples/lamb/lamb.cpp:79-88) with the fork's constant
- * weight decay 1.0 (reduce_kernel.h:427), not the fork's kernel slips. */
+/* LAMB form of the first fork, functor for functor (nccl/src/nccl.h.in:215;
+ * reduce_kernel.h:391-452, common_kernel.h:2472-2535, 2687-2726): fp16 ring
+ * sum, decay factor 1.0, the trust ratio divided by ||r|| once more. */
 template <typename DT, typename Op>
 inline int AllReduce_pipe(float lr, float beta1, float beta2, __half *g, float *w, __half *halfw,
                           float *m, float *v, float *r, size_t count, DT, cocoComm_t comm, Op,
@@ -90,7 +90,7 @@ inline int AllReduce_pipe(float lr, float beta1, float beta2, __half *g, float *
   const int rc = coco_compat::slice_begin(comm, count, &lo);
   if (rc != cocoSuccess) return rc;
   return cocoFusedLAMB(comm, g, cocoFloat16, w, halfw, cocoFloat16, m + lo, v + lo, count, lr,
-                       beta1, beta2, 0.0f, 1.0f, 0, 1.0f, cocoVariantDsl, 0, stream);
+                       beta1, beta2, 0.0f, 1.0f, 0, 1.0f, cocoVariantNccl, 0, stream);
 }
 
 #endif  /* COCONET_COMPAT_H_ */

@@ -102,8 +102,12 @@ struct StepArgs {
   float lr, beta1, beta2, eps, weight_decay, grad_scale;
   float d1, d2;               // denominators of m^ = m/d1, v^ = v/d2 ...
   double d1d, d2d;            // ... in double for the bias-corrected form
-  int pipe_stages;            // stages of the bulk-copy tile pipeline, 0 = off
+  int pipe_stages;            // stages of each warp's gradient ring (bulk copies), 0 = off
   int pad;
+  // Derived on the host so that the kernel reads them as constants instead of
+  // holding them in registers: 1 - beta (float subtraction), 1/d in double.
+  float omb1, omb2;
+  double r1d, r2d;
 };
 
 }  // namespace coco

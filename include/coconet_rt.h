@@ -78,9 +78,12 @@ typedef enum {
   /* the DSL programs as written: examples/adam/adam.cpp:65-71 and its frozen
    * check examples/test-adam.cu:14-38; examples/lamb/lamb.cpp:79-88. */
   cocoVariantDsl = 1,
-  /* the forked-NCCL functors, fp16 gradient sum in ring order included:
-   * nccl/src/collectives/device/reduce_kernel.h:27-62,
-   * common_kernel.h:853-923.  Needs fp16 gradients and w_lp. */
+  /* the forked-NCCL functors, fp16 gradient sum in ring order included.
+   * Adam (AllReduce_pipe TYPE 0): nccl/src/collectives/device/
+   * reduce_kernel.h:27-62, common_kernel.h:853-923.  LAMB (TYPE 1):
+   * reduce_kernel.h:391-452, common_kernel.h:2472-2535, 2687-2726 -- decay
+   * factor 1.0 whatever weight_decay says, no epsilon, m/beta1 and v/beta2,
+   * scale = (||w||/||r||)/||r||.  Needs fp16 gradients and an fp16 w_lp. */
   cocoVariantNccl = 2
 } cocoVariant_t;
 
@@ -309,6 +312,26 @@ struct cocoGenericPlan;
 int cocoFusedGenericPlan(cocoComm_t comm, const void *g, cocoDataType_t g_type, float *w,
                          size_t count, float grad_scale, cocoStream_t stream,
                          struct cocoGenericPlan *plan);
+
+/* Collective diagnostic: what the links between the ranks' GPUs give a kernel
+ * with the fused step's access shape and nothing else to do.  `buf` holds
+ * `bytes` on every rank (16-byte aligned; peer-mapped on first use like the
+ * fused calls' buffers; its contents are overwritten).  mode 0: every rank
+ * pulls its slice of `buf` from all peers with 16-byte loads, `unroll` (1, 2
+ * or 4) units in flight per thread and peer; 1: pushes its slice to all peers
+ * with 16-byte stores; 2: both at once (the fused step's traffic without the
+ * update); 3: the copy engine moves half of the next rank's buffer
+ * (cudaMemcpyAsync; `unroll` ignored); 4 / 5 / 6: the same three through the
+ * NVSwitch -- one multimem.ld_reduce per 16 bytes of the rank's slice, one
+ * multimem.st, or both (`buf` must come from cocoMemAlloc with a multicast
+ * mapping, else cocoInvalidUsage; its bytes are read as fp32).  One untimed iteration, then `iters`
+ * timed with CUDA events on `stream`; the call synchronises the stream.
+ * *gbs_per_direction = bytes that cross one GPU's links in one direction per
+ * iteration / the slowest rank's time per iteration, in GB/s (0 at world size
+ * 1), identical on all ranks.  The reference has no counterpart: its kernels
+ * were only timed end to end (experiments/generate-pdf/dsl_vs_apex.py:93-96). */
+int cocoLinkProbe(cocoComm_t comm, void *buf, size_t bytes, int mode, int unroll, int iters,
+                  double *gbs_per_direction, cocoStream_t stream);
 
 /* Norms of the last LAMB step on this communicator: out[0] = ||w||,
  * out[1] = ||r|| as used for the trust ratio.  Synchronise the stream first. */

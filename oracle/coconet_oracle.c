@@ -214,6 +214,52 @@ int oracle_lamb(float *w, float *m, float *v, uint16_t *w_lp,
       m[i] = mn;
       v[i] = vn;
     }
+  } else if (variant == ORACLE_VARIANT_NCCL) {
+    /* The forked-NCCL LAMB functors (AllReduce_pipe TYPE 1):
+     * nccl/src/collectives/device/reduce_kernel.h:391-452 as called from
+     * common_kernel.h:2472-2535 (first pass) and 2687-2726 (second pass);
+     * norms: all_reduce_computation.h:929-977.
+     *   v  = v*b2 + float(S0*S0 in half)*(1-b2)        mixedbinOp1
+     *   v_ = v/b2                                      binOp2
+     *   m  = m*b1 + float(S0)*(1-b1)                   mixedbinOp3 (beta1: the
+     *        Simple-protocol copy passes the right coefficient, :2509)
+     *   m_ = m/b1                                      binOp4
+     *   r  = m_/sqrtf(v_) + 1.0f*w                     rOp: the decay factor is
+     *        the constant 1.0f, whatever the caller wanted (reduce_kernel.h:427)
+     *   wNorm = sqrtf(sum w*w), rNorm = sqrtf(sum r*r), sums in fp32
+     *   scale = ((wNorm > 0) ? (rNorm > 0 ? wNorm/rNorm : 1) : 1) / rNorm   (:2699)
+     *   w  = w - (lr*scale)*r;  halfw = half(w)        delta, weightUpdate, :2715
+     * gsum holds S0, the fp16 ring sum, widened to float (exactly).  The
+     * reference accumulates the two sums with atomics in no fixed order; this
+     * restatement adds them in element order, in fp32 like the reference. */
+    float w2f = 0.0f, r2f = 0.0f;
+    for (size_t i = 0; i < n; i++) {
+      const float gf = gsum[i];
+      const float gg = oracle_f16_to_f32(oracle_f32_to_f16(gf * gf));
+      const float vn = (v[i] * beta2) + (gg * (1 - beta2));
+      const float v_ = vn / beta2;
+      const float mn = (m[i] * beta1) + (gf * (1 - beta1));
+      const float m_ = mn / beta1;
+      const float r = m_ / sqrtf(v_) + 1.0f * w[i];
+      rbuf[i] = r;
+      w2f += w[i] * w[i];
+      r2f += r * r;
+      m[i] = mn;
+      v[i] = vn;
+    }
+    const float wn = sqrtf(w2f), rn = sqrtf(r2f);
+    if (norms_out) {
+      norms_out[0] = wn;
+      norms_out[1] = rn;
+    }
+    const float scale = ((wn > 0) ? (rn > 0 ? wn / rn : 1.0f) : 1.0f) / rn;
+    for (size_t i = 0; i < n; i++) {
+      const float d = (lr * scale) * rbuf[i];
+      w[i] = w[i] - d;
+      if (w_lp) w_lp[i] = oracle_f32_to_f16(w[i]);
+    }
+    free(rbuf);
+    return 0;
   } else {
     free(rbuf);
     return -1;

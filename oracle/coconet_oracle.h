@@ -34,9 +34,11 @@ enum {
   /* The DSL programs taken literally: examples/adam/adam.cpp:65-71
    * (m/beta1, v/beta2, w - m_/v_), examples/lamb/lamb.cpp:79-88. */
   ORACLE_VARIANT_DSL = 1,
-  /* The forked-NCCL device functors, including the beta2-for-m slip:
-   * nccl/src/collectives/device/reduce_kernel.h:36-68,
-   * nccl/src/collectives/device/common_kernel.h:862-923. */
+  /* The forked-NCCL device functors.  Adam (AllReduce_pipe TYPE 0), including
+   * the beta2-for-m slip: nccl/src/collectives/device/reduce_kernel.h:36-68,
+   * common_kernel.h:862-923.  LAMB (TYPE 1): reduce_kernel.h:391-452,
+   * common_kernel.h:2472-2535, 2687-2726 (decay factor 1.0, fp32 norms, the
+   * trust ratio divided by ||r|| once more). */
   ORACLE_VARIANT_NCCL = 2,
 };
 
@@ -75,7 +77,9 @@ int oracle_adam(float *w, float *m, float *v, uint16_t *w_lp,
 
 /* One LAMB step on one tensor of n elements (all slices together: the norms
  * are global).  Returns ||w|| and ||r|| as used through norms_out[2] when
- * non-NULL. */
+ * non-NULL.  For ORACLE_VARIANT_NCCL gsum holds the fp16 ring sum widened to
+ * float, and eps, weight_decay, step and flags are ignored (the functors have
+ * no epsilon, no bias correction, and a decay factor of 1.0). */
 int oracle_lamb(float *w, float *m, float *v, uint16_t *w_lp,
                 const float *gsum, size_t n, float lr, float beta1,
                 float beta2, float eps, float weight_decay, int step,

@@ -128,7 +128,7 @@ int main(int argc, char **argv) {
     ok &= report("adam-mixed", bad, rank);
     cudaFree(g), cudaFree(halfw), cudaFree(w), cudaFree(m), cudaFree(v);
   }
-  {  // ---- LAMB form (nccl.h.in:215): the DSL program's LAMB with weight decay 1 ----
+  {  // ---- LAMB form (nccl.h.in:215): the fork's LAMB functors (reduce_kernel.h:391-452) ----
     __half *g = toDevice(hgh), *halfw = nullptr;
     CUDACHECK(cudaMalloc(&halfw, SZ * sizeof(__half)));
     float *w = toDevice(hw), *m = toDevice(hm), *v = toDevice(hv), *r = nullptr;
@@ -137,16 +137,17 @@ int main(int argc, char **argv) {
     std::vector<float> gw = toHost(w, SZ);
     std::vector<__half> gh = toHost(halfw, SZ);
     std::vector<float> rr(SZ);
-    double w2 = 0, r2 = 0;
+    float w2 = 0, r2 = 0;  // fp32 sums like the fork's (its order is not fixed: tolerance below)
     for (size_t i = 0; i < SZ; i++) {
-      const float s = gsum16[i];
-      const float m1 = beta1 * hm[i] + (1.f - beta1) * s;
-      const float v1 = beta2 * hv[i] + ((1.f - beta2) * s) * s;
-      rr[i] = (m1 / (1.f - beta1)) / sqrtf(v1 / (1.f - beta2)) + 1.0f * hw[i];
-      w2 += (double)hw[i] * hw[i], r2 += (double)rr[i] * rr[i];
+      const float s = __half2float(gring[i]);                      // fp16 ring sum
+      const float ss = __half2float(__float2half(s * s));          // the square is taken in fp16
+      const float v1 = hv[i] * beta2 + ss * (1.f - beta2);
+      const float m1 = hm[i] * beta1 + s * (1.f - beta1);          // beta1: the LAMB copy is right
+      rr[i] = (m1 / beta1) / sqrtf(v1 / beta2) + 1.0f * hw[i];     // decay factor 1.0, no epsilon
+      w2 += hw[i] * hw[i], r2 += rr[i] * rr[i];
     }
-    const double wn = sqrt(w2), rn = sqrt(r2);
-    const float scale = lr * (float)((wn > 0 && rn > 0) ? wn / rn : 1.0);
+    const float wn = sqrtf(w2), rn = sqrtf(r2);
+    const float scale = lr * (((wn > 0) ? (rn > 0 ? wn / rn : 1.0f) : 1.0f) / rn);  // the extra /||r||
     size_t bad = 0;
     for (size_t i = 0; i < SZ; i++) {
       const float w1 = hw[i] - scale * rr[i];

@@ -9,7 +9,8 @@ LIBDIR = os.path.join(ROOT, "coconet_b200")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 SCALARS = {"COCONET_SCALAR_lr": "0.01", "COCONET_SCALAR_beta1": "0.9", "COCONET_SCALAR_beta2": "0.999",
-           "COCONET_SCALAR_decay": "0.01", "COCONET_SCALAR_mu": "0.9"}
+           "COCONET_SCALAR_decay": "0.01", "COCONET_SCALAR_mu": "0.9",
+           "COCONET_SCALAR_inv_scale": "0.125"}
 
 
 def build_program(opt, schedule, workdir):

@@ -34,6 +34,10 @@ def _gen(build, opt, schedule, tmp_path):
              "0.0f, iter, 1.0f, cocoVariantDsl, stream)"),
     ("lamb", "cocoFusedLAMB(comm, g, cocoFloat32, w, NULL, cocoFloat16, m, v, N, lr, beta1, beta2, "
              "0.0f, decay, iter, 1.0f, cocoVariantDsl, 0, stream)"),
+    # mixed precision: fp16 gradients, the loss-scale Variable as the gradient scale, the fp32
+    # master Sliced (indexed by global element inside the slice), the fp16 copy gathered
+    ("adam_mixed", "cocoFusedAdam(comm, g, cocoFloat16, (w - (size_t)DIVUP(N, comm_size) * rank), wh, "
+                   "cocoFloat16, m, v, N, lr, beta1, beta2, 0.0f, iter, inv_scale, cocoVariantDsl, stream)"),
 ])
 def test_fused_schedule_emits_one_runtime_call(dsl_build, tmp_path, opt, call):
     text = _gen(dsl_build, opt, "fuse_RS_C_AG", tmp_path)
@@ -100,7 +104,8 @@ def test_reference_example_programs_are_a_drop_in(dsl_build, tmp_path, ex):
 
 
 @pytest.mark.parametrize("opt,schedule", [("adam", "fuse_RS_C_AG"), ("lamb", "fuse_RS_C_AG"),
-                                          ("lamb", "RS_C_AG"), ("sgd", "AR_C")])
+                                          ("lamb", "RS_C_AG"), ("sgd", "AR_C"),
+                                          ("adam_mixed", "fuse_RS_C_AG"), ("adam_mixed", "RS_C_AG")])
 def test_emitted_programs_compile_for_sm100a(dsl_build, tmp_path, opt, schedule):
     _gen(dsl_build, opt, schedule, tmp_path)
     src = str(tmp_path / f"{opt}-{schedule}.cu")

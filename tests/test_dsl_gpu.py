@@ -17,7 +17,9 @@ pytestmark = pytest.mark.gpu
                                           ("lamb", "fuse_RS_C_AG"), ("adam", "RS_C_AG"),
                                           ("lamb", "AR_C"), ("nesterov", "fuse_RS_C_AG"),
                                           ("adam_derived", "RS_C_AG"),
-                                          ("adam_derived", "fuse_RS_C_AG")])
+                                          ("adam_derived", "fuse_RS_C_AG"),
+                                          ("adam_mixed", "fuse_RS_C_AG"),
+                                          ("adam_mixed", "RS_C_AG")])
 def test_emitted_program_runs_and_checks_world_1(tmp_path, opt, schedule):
     exe = B.build_program(opt, schedule, str(tmp_path))
     env = dict(os.environ, RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", MASTER_ADDR="127.0.0.1",

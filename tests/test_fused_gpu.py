@@ -311,6 +311,58 @@ def test_adam_nccl_variant_matches_oracle_ring_sum():
 
 
 @pytest.mark.parametrize("R", [1, 2, 8])
+def test_lamb_nccl_variant_known_answer(R):
+    # forked-NCCL LAMB functors on the constants of the reference's frozen tests
+    # (g = 1 per rank, w = m = v = 0, beta = 0.5, lr = 1): S0 = R, v^ = R^2,
+    # m^ = R, r = 1 everywhere, ||w|| = 0 so scale = 1/||r|| = 1/sqrt(n), and
+    # w' = -1/sqrt(n) for any R (reduce_kernel.h:391-452, common_kernel.h:2699)
+    n = 4096
+    ranks = Ranks(K.LAMB, R, n, seed=0, lp_dtype=torch.float16)
+    try:
+        for r in range(R):
+            ranks.w[r].zero_()
+        ones16 = [np.ones(n, np.float16) for _ in range(R)]
+        ranks.step(ones16, 0, variant=coco.VARIANT_NCCL, hyper=dict(lr=1.0, beta1=0.5, beta2=0.5))
+        for r in range(R):
+            lo, hi = K.slice_bounds(n, R, r)
+            assert torch.all(ranks.w[r][lo:hi] == -1.0 / 64.0)
+            assert torch.all(ranks.lp[r] == -1.0 / 64.0)
+            assert torch.all(ranks.m[r][: hi - lo] == R / 2) and torch.all(ranks.v[r][: hi - lo] == R * R / 2)
+    finally:
+        ranks.close()
+
+
+@pytest.mark.parametrize("R,n", [(1, 5000), (4, 1 << 16), (8, (1 << 18) + 24)])
+def test_lamb_nccl_variant_matches_oracle(R, n):
+    # fp16 ring sum per slice owner, beta1 for m, decay factor 1.0 whatever the
+    # caller passes, float norms, scale = (||w||/||r||)/||r||; two steps
+    ranks = Ranks(K.LAMB, R, n, seed=14, lp_dtype=torch.float16)
+    w = K.make_weights(n, 14)
+    m, v = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    wl = np.zeros(n, np.float16)
+    try:
+        for step in range(2):
+            grads = K.make_grads(R, n, 14, step, dtype=np.float16, loss_scale=256.0)
+            ranks.step(grads, step, variant=coco.VARIANT_NCCL,
+                       hyper=dict(lr=1e-3, beta1=0.9, beta2=0.999, weight_decay=0.01))
+            gsum = np.empty(n, np.float32)
+            for r in range(R):
+                lo, hi = K.slice_bounds(n, R, r)
+                gsum[lo:hi] = O.reduce_f16_ring([x[lo:hi].copy() for x in grads], owner=r).astype(np.float32)
+            norms = O.lamb(w, m, v, gsum, 1e-3, 0.9, 0.999, 0.0, 0.01, step, O.NCCL, w_lp=wl)
+            for r in range(R):
+                lo, hi = K.slice_bounds(n, R, r)
+                assert np.array_equal(ranks.m[r].cpu().numpy()[: hi - lo], m[lo:hi])
+                assert np.array_equal(ranks.v[r].cpu().numpy()[: hi - lo], v[lo:hi])
+                K.assert_close(ranks.w[r].cpu().numpy()[lo:hi], w[lo:hi], RTOL_FP32, f"w step {step}")
+                K.assert_close(ranks.lp[r].float().cpu().numpy(), wl.astype(np.float32), 1e-3, "w_lp")
+            wn, rn = ranks.comms[0].last_lamb_norms()
+            np.testing.assert_allclose([wn, rn], norms, rtol=2e-6)  # fp32 sums vs double sums
+    finally:
+        ranks.close()
+
+
+@pytest.mark.parametrize("R", [1, 2, 8])
 @pytest.mark.parametrize("n", [11, 4099, 1 << 20, (1 << 20) + 3])
 def test_lamb_fp32(R, n):
     ranks = Ranks(K.LAMB, R, n, seed=9)

@@ -23,7 +23,7 @@ def _why(r):
     return (r.stdout[k:k + 4000] if k >= 0 else r.stdout[-3000:]) + r.stderr[-1500:]
 
 
-def _launch(case, world, timeout=600):
+def _launch(case, world, timeout=600, extra_env=None):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
@@ -31,6 +31,7 @@ def _launch(case, world, timeout=600):
     env = dict(os.environ)
     # plain peer loads only; no NVLS anywhere in these child processes
     env.update(NCCL_NVLS_ENABLE="0", COCO_TIMEOUT_MS=env.get("COCO_TIMEOUT_MS", "5000"))
+    env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(HERE, "mp_worker.py"), case]
@@ -41,6 +42,16 @@ def _launch(case, world, timeout=600):
 def test_parity_all_gpus():
     world = min(_ngpu(), 8)
     r = _launch("parity", world)
+    assert r.returncode == 0, _why(r)
+    assert r.stdout.count("ok ") >= 8, r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_parity_through_the_warp_rings_all_gpus():
+    # the same cases with the gradients staged by bulk copies out of the peers'
+    # IPC-mapped memory (COCO_PIPELINE=1): bit-exact like the register-staged path
+    world = min(_ngpu(), 8)
+    r = _launch("parity", world, extra_env={"COCO_PIPELINE": "1"})
     assert r.returncode == 0, _why(r)
     assert r.stdout.count("ok ") >= 8, r.stdout
 
@@ -65,7 +76,8 @@ def test_nvls_multicast_path():
                                           ("sgd", "RS_C_AG"), ("nesterov", "fuse_RS_C_AG"),
                                           ("lamb", "RS_C_AG"), ("adam", "AR_C"),
                                           ("adam_derived", "RS_C_AG"),
-                                          ("adam_derived", "fuse_RS_C_AG")])
+                                          ("adam_derived", "fuse_RS_C_AG"),
+                                          ("adam_mixed", "fuse_RS_C_AG")])
 def test_emitted_program_multi_rank(tmp_path, opt, schedule):
     """A DSL-emitted C++ program, one process per GPU, started without MPI."""
     import dsl_build_util as B

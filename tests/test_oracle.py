@@ -162,3 +162,42 @@ def test_ref_checker_accepts_oracle_overlap(kind, betas):
     bad = w.copy(); bad[3] = bad[3] * 1.001 + 1e-3
     g = _grads(R, n, 1, 1e-3)
     assert not O.ref_overlap_check(kind, g, 25, w, bad, rm, rv, b1, b2, -lr, eps)
+
+
+def test_lamb_nccl_variant_known_answer_and_decay_constant():
+    # reduce_kernel.h:391-452 / common_kernel.h:2699 on the frozen tests' constants:
+    # r = 1 everywhere, ||w|| = 0 -> scale = 1/sqrt(n), w' = -1/sqrt(n) for any R
+    n = 4096
+    for R in (1, 2, 8):
+        gsum = np.full(n, float(R), np.float32)       # fp16 ring sum of R ones
+        w, m, v = np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float32)
+        wl = np.zeros(n, np.float16)
+        wn, rn = O.lamb(w, m, v, gsum, 1.0, 0.5, 0.5, 0.0, 0.01, 0, O.NCCL, w_lp=wl)
+        assert np.all(w == np.float32(-1.0 / 64.0)) and np.all(wl == np.float16(-1.0 / 64.0))
+        assert np.all(m == R / 2) and np.all(v == R * R / 2)
+        assert wn == 0.0 and rn == 64.0
+    # the decay factor is the constant 1.0: weight_decay and eps are ignored
+    rng = np.random.default_rng(3)
+    g = rng.standard_normal(1000).astype(np.float16).astype(np.float32)
+    outs = []
+    for wd, eps in ((0.01, 1e-6), (0.5, 0.0)):
+        w = (rng.standard_normal(1000) * 0 + np.linspace(-0.05, 0.05, 1000)).astype(np.float32)
+        m, v = np.zeros(1000, np.float32), np.zeros(1000, np.float32)
+        O.lamb(w, m, v, g, 1e-3, 0.9, 0.999, eps, wd, 0, O.NCCL)
+        outs.append(w)
+    assert np.array_equal(outs[0], outs[1])
+    # against the formula written out in numpy (fp32 throughout)
+    w0 = np.linspace(-0.05, 0.05, 1000).astype(np.float32)
+    f = np.float32
+    gg = (g * g).astype(np.float16).astype(np.float32)
+    vn = gg * (f(1) - f(0.999))
+    mn = g * (f(1) - f(0.9))
+    r = (mn / f(0.9)) / np.sqrt(vn / f(0.999)) + f(1.0) * w0
+    w2, r2 = f(0), f(0)
+    for a, b in zip(w0, r):
+        w2 = f(w2 + a * a)
+        r2 = f(r2 + b * b)
+    wn, rn = np.sqrt(w2), np.sqrt(r2)
+    scale = f(f(wn / rn) / rn)
+    want = (w0 - f(f(1e-3) * scale) * r).astype(np.float32)
+    assert np.array_equal(outs[0], want)
