@@ -776,19 +776,21 @@ def main():
             # weights are O(2e-2): differences are taken relative to |w| + 1e-3 (the floor the
             # parity tests use); moments relative to |x| + rms(x), since single elements of m
             # nearly cancel
-            max_rel = 0.0
+            detail = {}
             exact_w = None
             if ow is not None:
-                max_rel = rel_err(got_w, ow, 1e-3)
+                detail["w"] = rel_err(got_w, ow, 1e-3)
                 exact_w = bool(np.array_equal(got_w, ow))
                 if owl is not None:
-                    max_rel = max(max_rel, rel_err(got_out.astype(np.float32), owl.astype(np.float32), 1e-3))
+                    detail["gathered"] = rel_err(got_out.astype(np.float32), owl.astype(np.float32), 1e-3)
                     exact_w = exact_w and bool(np.array_equal(got_out.view(np.uint16), owl.view(np.uint16)))
                 else:
-                    max_rel = max(max_rel, rel_err(got_out, ow, 1e-3))
-            if cfg["opt"] != "sgd" and not exact_mv:
+                    detail["gathered"] = rel_err(got_out, ow, 1e-3)
+            if cfg["opt"] != "sgd":
                 # v = (1 - b2) g^2 doubles the relative error of g: a third of its error counts
-                max_rel = max(max_rel, rel_err(got_m, om, rms(om)), rel_err(got_v, ov, rms(ov)) / 3.0)
+                detail["m"] = rel_err(got_m, om, rms(om))
+                detail["v"] = rel_err(got_v, ov, rms(ov)) / 3.0
+            max_rel = max(detail.values()) if detail else 0.0
             ok = max_rel <= tol_w and gather_ok and replicas_ok
             if fixed_order:  # fixed summation order: the moments match a CPU evaluation bit for bit
                 ok = ok and exact_mv
@@ -801,7 +803,7 @@ def main():
                 dist.all_reduce(flags, op=dist.ReduceOp.MIN)
                 dist.all_reduce(worst, op=dist.ReduceOp.MAX)
             parity = {"checked": int(idx.size) * R, "steps": T, "path": "nvls" if use_nvls else "p2p",
-                      "max_rel": float(worst.item()), "tolerance": tol_w,
+                      "max_rel": float(worst.item()), "tolerance": tol_w, "rank0_detail": detail,
                       "exact_mv": bool(flags[1].item()), "exact_w": bool(flags[2].item()),
                       "gather_ok": gather_ok, "replicas_identical": replicas_ok,
                       "ok": bool(flags[0].item()),

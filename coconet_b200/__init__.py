@@ -22,10 +22,11 @@ from .runtime import (  # noqa: F401
     scattered_slice_elems,
     scattered_tensor_place,
     slice_bounds,
+    topology_check,
 )
 
 __all__ = [
     "CocoError", "Communicator", "HostBootstrap", "VARIANT_DSL", "VARIANT_NCCL", "VARIANT_OVERLAP",
     "LAMB_REF_QUIRK", "group", "lib", "library_path", "rendezvous_address", "scattered_slice_elems", "scattered_tensor_place",
-    "slice_bounds",
+    "slice_bounds", "topology_check",
 ]

@@ -1,5 +1,7 @@
 #include "bootstrap.h"
 
+#include <algorithm>
+
 #include <arpa/inet.h>
 #include <errno.h>
 #include <netdb.h>
@@ -162,7 +164,25 @@ int Bootstrap::init(int world, int rank, const std::string &addr, int timeout_ms
   }
 }
 
-int Bootstrap::all_gather(const void *send, void *recv, size_t bytes) {
+// Every exchange starts with a small header -- which collective this is (a
+// running count kept by every rank), of what kind, and how many bytes the rank
+// contributes -- so that ranks that fell out of step (one of them skipped or
+// added a collective, or disagrees on the size) get cocoInvalidUsage instead of
+// one rank's handle blob being read as another's barrier byte.  After a
+// mismatch the connection is out of step for good: every later call fails.
+namespace {
+constexpr uint32_t kMagic = 0xC0C0B007u;
+struct Header {
+  uint32_t magic;
+  uint32_t kind;    // 0 all-gather, 1 barrier; in rank 0's reply: 0 ok, 1 mismatch
+  uint64_t op;      // index of this collective on the communicator
+  uint64_t bytes;   // per-rank payload
+};
+}  // namespace
+
+int Bootstrap::exchange(const void *send, void *recv, size_t bytes, unsigned kind) {
+  if (broken_) return cocoInvalidUsage;
+  const uint64_t op = ++op_;
   if (world_ == 1) {
     if (recv != send) memcpy(recv, send, bytes);
     return cocoSuccess;
@@ -170,25 +190,57 @@ int Bootstrap::all_gather(const void *send, void *recv, size_t bytes) {
   char *out = (char *)recv;
   if (rank_ == 0) {
     memmove(out, send, bytes);
+    bool mismatch = false;
     for (int r = 1; r < world_; ++r) {
-      int rc = recv_all(peer_fd_[r], out + (size_t)r * bytes, bytes);
+      Header h;
+      int rc = recv_all(peer_fd_[r], &h, sizeof(h));
+      if (rc != cocoSuccess) return rc;
+      if (h.magic != kMagic || h.kind != kind || h.op != op || h.bytes != bytes) {
+        mismatch = true;  // drain what the rank sends behind its header, within reason
+        std::vector<char> sink(4096);
+        uint64_t left = h.magic == kMagic ? std::min<uint64_t>(h.bytes, 1u << 24) : 0;
+        while (left > 0) {
+          const size_t n = (size_t)std::min<uint64_t>(left, sink.size());
+          if (recv_all(peer_fd_[r], sink.data(), n) != cocoSuccess) break;
+          left -= n;
+        }
+        continue;
+      }
+      rc = recv_all(peer_fd_[r], out + (size_t)r * bytes, bytes);
       if (rc != cocoSuccess) return rc;
     }
+    Header reply = {kMagic, mismatch ? 1u : 0u, op, (uint64_t)bytes};
+    int result = mismatch ? cocoInvalidUsage : cocoSuccess;
     for (int r = 1; r < world_; ++r) {
-      int rc = send_all(peer_fd_[r], out, bytes * world_);
-      if (rc != cocoSuccess) return rc;
+      int rc = send_all(peer_fd_[r], &reply, sizeof(reply));
+      if (rc == cocoSuccess && !mismatch) rc = send_all(peer_fd_[r], out, bytes * world_);
+      if (rc != cocoSuccess && result == cocoSuccess) result = rc;
     }
-    return cocoSuccess;
+    if (mismatch) broken_ = true;
+    return result;
   }
-  int rc = send_all(root_fd_, send, bytes);
+  const Header h = {kMagic, kind, op, (uint64_t)bytes};
+  int rc = send_all(root_fd_, &h, sizeof(h));
+  if (rc == cocoSuccess) rc = send_all(root_fd_, send, bytes);
   if (rc != cocoSuccess) return rc;
+  Header reply;
+  rc = recv_all(root_fd_, &reply, sizeof(reply));
+  if (rc != cocoSuccess) return rc;
+  if (reply.magic != kMagic || reply.kind != 0 || reply.op != op) {
+    broken_ = true;
+    return cocoInvalidUsage;
+  }
   return recv_all(root_fd_, out, bytes * world_);
+}
+
+int Bootstrap::all_gather(const void *send, void *recv, size_t bytes) {
+  return exchange(send, recv, bytes, 0);
 }
 
 int Bootstrap::barrier() {
   std::vector<char> tmp(world_ > 0 ? world_ : 1);
   char me = 1;
-  return all_gather(&me, tmp.data(), 1);
+  return exchange(&me, tmp.data(), 1, 1);
 }
 
 }  // namespace coco

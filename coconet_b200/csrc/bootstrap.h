@@ -22,7 +22,9 @@ class Bootstrap {
   // until timeout_ms).  Returns 0, or a cocoResult_t.
   int init(int world, int rank, const std::string &addr, int timeout_ms);
 
-  // recv must hold world * bytes; slot r receives rank r's `send`.
+  // recv must hold world * bytes; slot r receives rank r's `send`.  Ranks that
+  // are not in the same collective (count, kind or size differ) get
+  // cocoInvalidUsage, and so does every later call.
   int all_gather(const void *send, void *recv, size_t bytes);
   int barrier();
 
@@ -30,7 +32,10 @@ class Bootstrap {
   int rank() const { return rank_; }
 
  private:
+  int exchange(const void *send, void *recv, size_t bytes, unsigned kind);
   int world_ = 0, rank_ = -1;
+  unsigned long long op_ = 0;   // collectives issued so far on this rank
+  bool broken_ = false;         // the ranks fell out of step
   int listen_fd_ = -1;
   int root_fd_ = -1;            // non-root: connection to rank 0
   std::vector<int> peer_fd_;    // root: connection to each rank (index = rank)

@@ -34,6 +34,14 @@
 #include <tuple>
 #include <type_traits>
 
+// Build-time experiment switches of the single-rank 16-bit path (A/B runs).
+#ifndef COCO_LOCAL16_SHUFFLE
+#define COCO_LOCAL16_SHUFFLE 0   // 1: 16-byte gradient loads / copy stores, halves exchanged by shuffles
+#endif
+#ifndef COCO_LOCAL16_THREADS
+#define COCO_LOCAL16_THREADS 512  // block size the kernel is compiled for (registers: 65536 / (2 x this))
+#endif
+
 namespace coco {
 
 typedef void (*KernelPtr)(const StepArgs, const RankArgs, const RankArgs *);
@@ -262,9 +270,26 @@ template <typename GT> struct RawUnit<GT, 8> {
   }
   // elements i..i+3 and i+HS..i+HS+3
   template <int HS> __device__ __forceinline__ void load_halves(const void *base, size_t i) {
+#if COCO_LOCAL16_SHUFFLE
+    // The warp's 32 units are 256 consecutive elements (lane t: 4t.. and
+    // 128+4t..).  Every lane loads 16 contiguous bytes of them (elements
+    // 8t..8t+7) and the lanes exchange halves: element 4t+k sits in lane t/2,
+    // words 2(t&1) and 2(t&1)+1; element 128+4t+k in lane 16 + t/2.  Must be
+    // called by all 32 lanes.
+    static_assert(HS == 128, "the exchange is written for the 128-element half stride");
+    const int t = threadIdx.x & 31;
+    const uint4 c = ld_sys_16((const unsigned short *)base + i + 4 * t);
+    const int s0 = t >> 1, s1 = 16 + (t >> 1);
+    const unsigned a0 = __shfl_sync(0xffffffffu, c.x, s0), a1 = __shfl_sync(0xffffffffu, c.y, s0);
+    const unsigned a2 = __shfl_sync(0xffffffffu, c.z, s0), a3 = __shfl_sync(0xffffffffu, c.w, s0);
+    const unsigned b0 = __shfl_sync(0xffffffffu, c.x, s1), b1 = __shfl_sync(0xffffffffu, c.y, s1);
+    const unsigned b2 = __shfl_sync(0xffffffffu, c.z, s1), b3 = __shfl_sync(0xffffffffu, c.w, s1);
+    q = (t & 1) ? make_uint4(a2, a3, b2, b3) : make_uint4(a0, a1, b0, b1);
+#else
     const uint2 a = ld_sys_8((const unsigned short *)base + i);
     const uint2 b = ld_sys_8((const unsigned short *)base + i + HS);
     q = make_uint4(a.x, a.y, b.x, b.y);
+#endif
   }
   __device__ __forceinline__ unsigned short bits(int k) const {
     const unsigned wd = (k >> 1) == 0 ? q.x : (k >> 1) == 1 ? q.y : (k >> 1) == 2 ? q.z : q.w;
@@ -446,8 +471,24 @@ __device__ __forceinline__ void gather_unit(const RankArgs &ra, int R, size_t i,
         st_sys_16(dst, make_uint4(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16),
                                   h[4] | ((unsigned)h[5] << 16), h[6] | ((unsigned)h[7] << 16)));
       } else {
+#if COCO_LOCAL16_SHUFFLE
+        // the reverse exchange: lane s assembles elements 8s..8s+7 of the warp's
+        // 256 from lanes 2(s&15) and 2(s&15)+1 (their first fours for s < 16,
+        // their second fours otherwise) and stores 16 contiguous bytes
+        static_assert(HS == 128, "the exchange is written for the 128-element half stride");
+        const int t = threadIdx.x & 31;
+        const unsigned A0 = h[0] | ((unsigned)h[1] << 16), A1 = h[2] | ((unsigned)h[3] << 16);
+        const unsigned B0 = h[4] | ((unsigned)h[5] << 16), B1 = h[6] | ((unsigned)h[7] << 16);
+        const int s0 = 2 * (t & 15), s1 = s0 + 1;
+        const unsigned x0 = __shfl_sync(0xffffffffu, A0, s0), x1 = __shfl_sync(0xffffffffu, A1, s0);
+        const unsigned x2 = __shfl_sync(0xffffffffu, A0, s1), x3 = __shfl_sync(0xffffffffu, A1, s1);
+        const unsigned y0 = __shfl_sync(0xffffffffu, B0, s0), y1 = __shfl_sync(0xffffffffu, B1, s0);
+        const unsigned y2 = __shfl_sync(0xffffffffu, B0, s1), y3 = __shfl_sync(0xffffffffu, B1, s1);
+        st_sys_16(dst + 4 * t, t < 16 ? make_uint4(x0, x1, x2, x3) : make_uint4(y0, y1, y2, y3));
+#else
         st_sys_8(dst, make_uint2(h[0] | ((unsigned)h[1] << 16), h[2] | ((unsigned)h[3] << 16)));
         st_sys_8(dst + HS, make_uint2(h[4] | ((unsigned)h[5] << 16), h[6] | ((unsigned)h[7] << 16)));
+#endif
       }
     };
     if constexpr (RB == 0) {
@@ -1120,8 +1161,13 @@ __device__ __forceinline__ void ring_apply(const RankArgs &ra, const StepArgs &s
 // Every path ends with the same scalar loop for what it does not cover.
 enum : int { kPathDirect = 0, kPathNvls = 1, kPathRing = 2, kPathLocal = 3, kPathSegments = 4 };
 
+// Threads per CTA a path's kernel is compiled for (two CTAs per SM).
+template <int PATH, typename GT> struct BlockThreads {
+  static constexpr int value = (PATH == kPathLocal && GradTraits<GT>::kIs16) ? COCO_LOCAL16_THREADS : 512;
+};
+
 template <int OPT, typename GT, typename LPT, int PATH>
-__global__ void __launch_bounds__(512, 2)
+__global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
     fused_step_kernel(const __grid_constant__ StepArgs sa, const __grid_constant__ RankArgs one,
                       const RankArgs *__restrict__ table) {
   extern __shared__ __align__(128) unsigned char ring_smem[];
@@ -1633,6 +1679,11 @@ int fused_step_path(const StepArgs &sa) {
   if (sa.flags & kFlagNvls) return kPathNvls;
   if (sa.pipe_stages > 0) return kPathRing;
   return sa.world == 1 ? kPathLocal : kPathDirect;
+}
+
+int fused_step_block_threads(int path, cocoDataType_t g_type) {
+  const bool is16 = g_type != cocoFloat32;
+  return (path == kPathLocal && is16) ? COCO_LOCAL16_THREADS : 512;
 }
 
 namespace {

@@ -123,7 +123,7 @@ extern "C" int cocoLambStepNoAlloc(const void *g, cocoDataType_t g_type, float *
   ra.aligned16 = (al16(g) && al16(w) && al16(m) && al16(v) && al16(ra.out[0])) ? 1 : 0;
 
   LaunchConfig cfg = {};
-  cfg.threads = 512;
+  cfg.threads = fused_step_block_threads(fused_step_path(sa), g_type);
   int occ = 0;
   if (fused_step_occupancy(kLAMB, g_type, w_lp != nullptr, lp_type, fused_step_path(sa),
                            cfg.threads, 0, &occ) != cudaSuccess || occ < 1) {

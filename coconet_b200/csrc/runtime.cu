@@ -9,6 +9,7 @@
 // (nccl/src/init.cc:972-1021).
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -125,6 +126,9 @@ struct PendingCall {
   float *m = nullptr, *v = nullptr;
   StepArgs sa = {};
   cudaStream_t stream = nullptr;
+  // stand-alone collective of a single-process group (kCollAllReduce ...), 0 = a fused step
+  int coll = 0;
+  void *aux = nullptr;  // reduce-scatter: recv; all-gather: send
   // scattered calls: the parameters are lists of tensors
   std::vector<const void *> sg;
   std::vector<float *> sw;
@@ -156,6 +160,9 @@ FlatLayout flat_layout(const size_t *counts, size_t n, int world) {
 struct LocalGroup;  // ranks that live in one process
 
 constexpr size_t kCommPageBytes = sizeof(FlagPage) + sizeof(TensorNorms);
+// per device of a single-process group: the virtual ranks' argument blocks and,
+// behind them, one pointer-sized functor per rank for the stand-alone collectives
+constexpr size_t kGroupTableBytes = sizeof(RankArgs) * kMaxRanks + 16 * kMaxRanks;
 
 }  // namespace
 
@@ -189,13 +196,14 @@ struct cocoComm {
   int pipeline = -1;         // COCO_PIPELINE: 1 warp rings (bulk copies), 0 register-staged, unset: by world size
   int ring_stages = 0;       // COCO_RING_STAGES: cap on the stages of a ring, 0 = as many as fit
   int algo = 2;              // 0 p2p, 1 nvls, 2 auto (COCO_ALGO=p2p|nvls|auto)
+  cocoTopology_t topo = {};  // peer access / performance between the ranks' GPUs
 };
 
 namespace {
 
 struct LocalGroup {
   std::vector<cocoComm *> comms;         // index = rank
-  std::map<int, RankArgs *> table_dev;   // device -> table for virtual ranks
+  std::map<int, RankArgs *> table_dev;   // device -> table for virtual ranks (+ kMaxRanks pointers behind it)
   std::mutex mu;
 };
 
@@ -386,22 +394,23 @@ int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
   }
   sa->pipe_stages = stages;
   cfg->smem_bytes = (size_t)stages * stage_bytes;
+  const int path = fused_step_path(*sa);
+  const int threads = std::min(c->threads, fused_step_block_threads(path, g_type));
 
   int occ = 0;
-  CUDA_TRY(fused_step_occupancy(opt, g_type, has_lp, lp_type, fused_step_path(*sa), c->threads,
-                                cfg->smem_bytes, &occ));
+  CUDA_TRY(fused_step_occupancy(opt, g_type, has_lp, lp_type, path, threads, cfg->smem_bytes, &occ));
   if (occ < 1) return cocoInternalError;
   int per_sm = std::min(want_per_sm, occ);
   long ctas = (long)per_sm * c->sm_count;
   if (nvirt > 1) ctas = std::max(1L, ((long)occ * c->sm_count) / nvirt);
   // no more CTAs than there is work: one warp tile (or 16-byte unit) per thread pass
   const size_t vec = 4;
-  const size_t per_cta = stages > 0 ? tile_elems * warps : vec * c->threads;
+  const size_t per_cta = stages > 0 ? tile_elems * warps : vec * (size_t)threads;
   const long need = (long)std::max<size_t>(1, (slice + per_cta - 1) / per_cta);
   ctas = std::max(1L, std::min(ctas, need));
   ctas = std::min<long>(ctas, kMaxCtasPerRank);
   cfg->ctas = (int)ctas;
-  cfg->threads = c->threads;
+  cfg->threads = threads;
   cfg->nvirt = nvirt;
   cfg->cooperative = coop;
   return cocoSuccess;
@@ -602,7 +611,7 @@ int flush_group(LocalGroup *grp) {
     const PendingCall &pc = grp->comms[r]->pending;
     if (pc.opt != first.opt || pc.g_type != first.g_type || pc.sa.count != first.sa.count ||
         (pc.w_lp != nullptr) != (first.w_lp != nullptr) || pc.lp_type != first.lp_type ||
-        pc.sa.seq != first.sa.seq) {
+        pc.sa.seq != first.sa.seq || pc.coll != first.coll) {
       for (cocoComm *c : grp->comms) c->has_pending = false;
       return cocoInvalidUsage;  // ranks disagree on the operation
     }
@@ -626,6 +635,27 @@ int flush_group(LocalGroup *grp) {
     for (size_t k = 0; k < ranks.size(); ++k)
       fill_rank_args(&host[k], ranks[k], R, g_views, out_views, flags,
                      grp->comms[ranks[k]]->pending);
+    if (pc0.coll != 0) {  // stand-alone collective: the generic kernel, one launch per device
+      RankArgs *&slot = grp->table_dev[kv.first];
+      if (!slot && cudaMalloc((void **)&slot, kGroupTableBytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        result = cocoCudaError;
+        break;
+      }
+      void *aux[kMaxRanks] = {};
+      for (size_t k = 0; k < ranks.size(); ++k) aux[k] = grp->comms[ranks[k]]->pending.aux;
+      cudaError_t e = launch_collective_group(pc0.coll, pc0.sa, host.data(), aux, (int)ranks.size(), slot,
+                                              (char *)slot + sizeof(RankArgs) * kMaxRanks,
+                                              lead->sm_count, pc0.stream);
+      if (e != cudaSuccess) {
+        COCO_WARN("collective launch failed: %s", cudaGetErrorString(e));
+        (void)cudaGetLastError();
+        result = cocoCudaError;
+        break;
+      }
+      lead->launches++;
+      continue;
+    }
     const bool scattered = !pc0.scounts.empty();
     if (scattered) {  // one address space: every rank's tensors are addressed directly
       const size_t nb = pc0.scounts.size();
@@ -684,7 +714,7 @@ int flush_group(LocalGroup *grp) {
     RankArgs *table = nullptr;
     if (ranks.size() > 1) {
       RankArgs *&slot = grp->table_dev[kv.first];
-      if (!slot && cudaMalloc((void **)&slot, sizeof(RankArgs) * kMaxRanks) != cudaSuccess) {
+      if (!slot && cudaMalloc((void **)&slot, kGroupTableBytes) != cudaSuccess) {
         result = cocoCudaError;
         break;
       }
@@ -710,7 +740,27 @@ int flush_group(LocalGroup *grp) {
   return result;
 }
 
+// NVTX range around the host side of a fused call (the reference marks its
+// kernels for the profiler the same way, nccl/src/include/nvtx.h, used from
+// enqueue.cc): named after the update rule, visible to any attached tool,
+// free when none is.  COCO_NVTX=0 switches it off.
+struct NvtxRange {
+  bool on;
+  explicit NvtxRange(const PendingCall &pc) {
+    static const bool enabled = env_int("COCO_NVTX", 1) != 0;
+    on = enabled;
+    if (on)
+      nvtxRangePushA(pc.coll ? "coconet collective"
+                     : pc.opt == kSGD ? "coconet fused SGD"
+                     : pc.opt == kAdam ? "coconet fused Adam" : "coconet fused LAMB");
+  }
+  ~NvtxRange() {
+    if (on) nvtxRangePop();
+  }
+};
+
 int enqueue(cocoComm *c, PendingCall &pc) {
+  NvtxRange range(pc);
   COCO_TRY(validate(c, pc));
   if (pc.sa.count == 0) return cocoSuccess;
   pc.sa.world = c->world;
@@ -776,6 +826,68 @@ void set_denominators(StepArgs *sa, int opt, int step) {
 
 }  // namespace
 
+// One rank's row of the topology table: what the driver says about reaching
+// each peer's GPU from this rank's.
+struct TopoRow {
+  int access[kMaxRanks], perf[kMaxRanks], atomics[kMaxRanks];
+};
+
+int discover_topology(cocoComm *c) {
+  const int R = c->world;
+  char mine[32] = {};
+  if (cudaDeviceGetPCIBusId(mine, sizeof(mine), c->device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    mine[0] = 0;
+  }
+  std::vector<char> ids(32 * (size_t)R);
+  COCO_TRY(c->boot->all_gather(mine, ids.data(), 32));
+  TopoRow row;
+  for (int p = 0; p < R; ++p) {
+    row.access[p] = row.perf[p] = row.atomics[p] = -1;
+    if (p == c->rank) {
+      row.access[p] = 1, row.perf[p] = 0, row.atomics[p] = 1;
+      continue;
+    }
+    int dev = -1;
+    const char *id = ids.data() + 32 * (size_t)p;
+    if (!id[0] || cudaDeviceGetByPCIBusId(&dev, id) != cudaSuccess) {
+      (void)cudaGetLastError();
+      continue;  // that GPU is not visible to this process: the driver cannot say
+    }
+    if (dev == c->device) {  // two ranks on one GPU
+      row.access[p] = 1, row.perf[p] = 0, row.atomics[p] = 1;
+      continue;
+    }
+    int v = 0;
+    if (cudaDeviceGetP2PAttribute(&v, cudaDevP2PAttrAccessSupported, c->device, dev) == cudaSuccess)
+      row.access[p] = v;
+    if (cudaDeviceGetP2PAttribute(&v, cudaDevP2PAttrPerformanceRank, c->device, dev) == cudaSuccess)
+      row.perf[p] = v;
+    if (cudaDeviceGetP2PAttribute(&v, cudaDevP2PAttrNativeAtomicSupported, c->device, dev) == cudaSuccess)
+      row.atomics[p] = v;
+    (void)cudaGetLastError();
+  }
+  std::vector<TopoRow> all(R);
+  COCO_TRY(c->boot->all_gather(&row, all.data(), sizeof(TopoRow)));
+  cocoTopology_t &t = c->topo;
+  memset(&t, 0, sizeof(t));
+  t.world = R;
+  std::vector<int> acc(R * R), perf(R * R);
+  for (int a = 0; a < R; ++a)
+    for (int b = 0; b < R; ++b) {
+      t.access[a][b] = acc[a * R + b] = all[a].access[b];
+      t.perf_rank[a][b] = perf[a * R + b] = all[a].perf[b];
+      t.native_atomics[a][b] = all[a].atomics[b];
+    }
+  const int rc = cocoTopologyCheck(R, acc.data(), perf.data(), &t.uniform);
+  if (rc != cocoSuccess)
+    COCO_WARN("rank %d: some pair of GPUs has no peer access; the fused step needs it", c->rank);
+  else if (!t.uniform)
+    COCO_WARN("rank %d: the GPUs are not equally near to one another (unequal P2P performance ranks)",
+              c->rank);
+  return rc;
+}
+
 // What symm_mem.cu needs from a communicator.
 namespace coco {
 int comm_world(cocoComm_t c) { return c->world; }
@@ -787,6 +899,23 @@ int comm_all_gather(cocoComm_t c, const void *send, void *recv, size_t bytes) {
   if (!c->boot) return cocoInvalidUsage;
   return c->boot->all_gather(send, recv, bytes);
 }
+int comm_enqueue_collective(cocoComm_t c, int kind, const void *g, float *w, void *aux,
+                            size_t count, cocoStream_t stream) {
+  if (!c->group) return cocoInvalidUsage;
+  PendingCall pc;
+  pc.opt = kSGD;  // no optimizer state: the collective's functor is chosen by `coll`
+  pc.coll = kind;
+  pc.aux = aux;
+  pc.g = g, pc.g_type = cocoFloat32, pc.w = w;
+  pc.sa.count = count;
+  pc.sa.grad_scale = 1.0f;
+  pc.sa.variant = cocoVariantOverlap;
+  pc.sa.d1 = pc.sa.d2 = 1.f;
+  pc.sa.d1d = pc.sa.d2d = 1.0;
+  pc.stream = (cudaStream_t)stream;
+  return enqueue(c, pc);
+}
+int comm_release_allocs(cocoComm_t c);  // symm_mem.cu
 int comm_add_mapped_region(cocoComm_t c, void *ptr, size_t bytes, void *const *peers, void *mc) {
   return cocoRegisterMapped(c, ptr, bytes, peers, mc);
 }
@@ -868,6 +997,7 @@ int cocoCommInitRank(cocoComm_t *comm, int world, int rank, const char *bootstra
   for (int r : rcs)
     if (r != cocoSuccess) return r;
   if (world > 1) {
+    COCO_TRY(discover_topology(c.get()));  // same verdict on every rank: the table is shared
     Region reg;
     COCO_TRY(map_region_ipc(c.get(), c->flags, kCommPageBytes, &reg));
     for (int p = 0; p < world; ++p) c->peer_flags[p] = (FlagPage *)reg.peer[p];
@@ -943,6 +1073,18 @@ int cocoCommDestroy(cocoComm_t comm) {
   if (!comm) return cocoInvalidArgument;
   DeviceGuard guard(comm->device);
   cudaDeviceSynchronize();
+  // symmetric allocations the caller did not free: released here (collective
+  // in process mode), so that nothing stays bound to a multicast object
+  int result = comm_release_allocs(comm);
+  if (comm->boot && comm->world > 1) {
+    // Peers have this rank's flag page (and buffers) mapped and may still be
+    // in the end phase of their last kernel: nobody unmaps or frees before
+    // every rank has synchronised its device and arrived here.  Bounded by the
+    // bootstrap's timeout; a rank that is gone does not hold the others up
+    // for ever.
+    const int rc = comm->boot->barrier();
+    if (rc != cocoSuccess && result == cocoSuccess) result = rc;
+  }
   for (auto &kv : comm->ipc_open) cudaIpcCloseMemHandle(kv.second.base);
   if (comm->group) {
     std::lock_guard<std::mutex> lock(comm->group->mu);
@@ -964,6 +1106,41 @@ int cocoCommDestroy(cocoComm_t comm) {
   if (comm->seg_dev) cudaFree(comm->seg_dev);
   (void)cudaGetLastError();
   delete comm;
+  return result;
+}
+
+int cocoTopologyCheck(int world, const int *access, const int *perf_rank, int *uniform) {
+  if (world < 1 || world > kMaxRanks || !access || !perf_rank || !uniform) return cocoInvalidArgument;
+  *uniform = 1;
+  int seen = -1;
+  for (int a = 0; a < world; ++a)
+    for (int b = 0; b < world; ++b) {
+      if (a == b) continue;
+      if (access[a * world + b] == 0) return cocoPeerError;
+      if (access[a * world + b] < 0) *uniform = 0;  // unknown is not "uniform"
+      const int p = perf_rank[a * world + b];
+      if (p < 0) continue;
+      if (seen < 0) seen = p;
+      else if (p != seen) *uniform = 0;
+    }
+  return cocoSuccess;
+}
+
+int cocoCommTopology(cocoComm_t comm, cocoTopology_t *topology) {
+  if (!comm || !topology) return cocoInvalidArgument;
+  if (comm->group || comm->world == 1) {  // one process: every pair was checked at creation
+    memset(topology, 0, sizeof(*topology));
+    topology->world = comm->world;
+    for (int a = 0; a < comm->world; ++a)
+      for (int b = 0; b < comm->world; ++b) {
+        topology->access[a][b] = 1;
+        topology->perf_rank[a][b] = a == b ? 0 : -1;
+        topology->native_atomics[a][b] = a == b ? 1 : -1;
+      }
+    topology->uniform = comm->world == 1;
+    return cocoSuccess;
+  }
+  *topology = comm->topo;
   return cocoSuccess;
 }
 

@@ -460,6 +460,38 @@ extern "C" int cocoMemFree(cocoComm_t comm, void *ptr) {
   return rc;
 }
 
+// Called by cocoCommDestroy: whatever the communicator still holds is freed
+// (collectively, like cocoMemFree: every rank must hold the same number of
+// allocations) and its entry disappears, so that memory bound to a multicast
+// object does not outlive the communicator and a later communicator at the same
+// address inherits nothing.
+namespace coco {
+int comm_release_allocs(cocoComm_t comm) {
+  int result = cocoSuccess;
+  for (;;) {
+    void *next = nullptr;
+    {
+      std::lock_guard<std::mutex> lock(g_mu);
+      auto it = g_allocs.find(comm);
+      if (it == g_allocs.end()) break;
+      if (it->second.empty()) {
+        g_allocs.erase(it);
+        break;
+      }
+      next = it->second.begin()->first;
+    }
+    const int rc = cocoMemFree(comm, next);
+    if (rc != cocoSuccess) {
+      if (result == cocoSuccess) result = rc;
+      std::lock_guard<std::mutex> lock(g_mu);
+      auto it = g_allocs.find(comm);
+      if (it != g_allocs.end()) it->second.erase(next);  // never loop on a failing entry
+    }
+  }
+  return result;
+}
+}  // namespace coco
+
 extern "C" int cocoMemHasMulticast(cocoComm_t comm, const void *ptr, int *yes) {
   if (!comm || !ptr || !yes) return cocoInvalidArgument;
   std::lock_guard<std::mutex> lock(g_mu);

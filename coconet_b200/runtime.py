@@ -19,6 +19,11 @@ class CocoError(RuntimeError):
         super().__init__(f"{what}: {error_string(code)} ({code})")
 
 
+class _Topology(C.Structure):
+    _fields_ = [("world", C.c_int), ("access", (C.c_int * 8) * 8), ("perf_rank", (C.c_int * 8) * 8),
+                ("native_atomics", (C.c_int * 8) * 8), ("uniform", C.c_int)]
+
+
 class _Status(C.Structure):
     _fields_ = [("code", C.c_int), ("rank", C.c_int), ("phase", C.c_int), ("peer", C.c_int),
                 ("seq", C.c_uint64)]
@@ -41,6 +46,9 @@ _SIGNATURES = {
     "cocoCommCount": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "cocoCommUserRank": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "cocoCommCuDevice": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "cocoCommTopology": (C.c_int, [C.c_void_p, C.POINTER(_Topology)]),
+    "cocoTopologyCheck": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                    C.POINTER(C.c_int)]),
     "cocoBarrier": (C.c_int, [C.c_void_p]),
     "cocoAllGatherHost": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "cocoBootstrapInit": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_char_p, C.c_int]),
@@ -150,6 +158,17 @@ def scattered_slice_elems(counts, world):
     out = C.c_size_t()
     _check(lib().cocoScatteredSliceElems(len(counts), arr, world, C.byref(out)), "cocoScatteredSliceElems")
     return out.value
+
+
+def topology_check(world, access, perf_rank):
+    """The rule communicators apply to the peer-access table at creation, on a
+    table of the caller's (lists of lists; no GPU needed).  Returns (result
+    code, uniform)."""
+    flat_a = (C.c_int * (world * world))(*[x for row in access for x in row])
+    flat_p = (C.c_int * (world * world))(*[x for row in perf_rank for x in row])
+    uni = C.c_int()
+    rc = lib().cocoTopologyCheck(world, flat_a, flat_p, C.byref(uni))
+    return rc, bool(uni.value)
 
 
 def slice_bounds(count, world, rank):
@@ -399,6 +418,18 @@ class Communicator:
         return out.value
 
     # ---- introspection ----
+    def topology(self):
+        """Peer access and relative P2P performance between the ranks' GPUs as
+        found at creation: dict with world, access, perf_rank (lists of lists,
+        -1 = unknown) and uniform."""
+        t = _Topology()
+        _check(lib().cocoCommTopology(self._h, C.byref(t)), "cocoCommTopology")
+        n = t.world
+        return {"world": n, "uniform": bool(t.uniform),
+                "access": [[t.access[a][b] for b in range(n)] for a in range(n)],
+                "perf_rank": [[t.perf_rank[a][b] for b in range(n)] for a in range(n)],
+                "native_atomics": [[t.native_atomics[a][b] for b in range(n)] for a in range(n)]}
+
     def status(self):
         """First device-side failure since the last call, as a dict (code 0 =
         none).  Synchronise the stream first."""

@@ -138,17 +138,50 @@ template <> struct Grad<__half> {
 
 }  // namespace coco_generic
 
+// The vector loop of the data phase for a world size of at most RB (1, 2, 4 or
+// 8): RB gradient slots per unit instead of always eight, of which all are
+// loaded before the first is used.
+template <typename GT, class F, int RB>
+__device__ __forceinline__ void cocoGenericVectorLoop(const coco::StepArgs &sa, const coco::RankArgs &ra,
+                                                      const F &f, size_t lo, size_t nvec, size_t tid,
+                                                      size_t nth, int Rr, int Rw) {
+  using namespace coco_generic;
+  for (size_t u = tid; u < nvec; u += nth) {
+    const size_t j = u * 4, gi = lo + j;
+    float g[4] = {0.f, 0.f, 0.f, 0.f}, x[RB][4];
+#pragma unroll
+    for (int p = 0; p < RB; ++p)
+      if (p < Rr) Grad<GT>::load4(ra.g[p], gi, x[p]);
+#pragma unroll
+    for (int p = 0; p < RB; ++p)
+      if (p < Rr) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) g[e] = p == 0 ? x[0][e] : __fadd_rn(g[e], x[p][e]);
+      }
+    const float4 w4 = *reinterpret_cast<const float4 *>(ra.w + gi);
+    float4 o;
+    o.x = f(j + 0, gi + 0, __fmul_rn(g[0], sa.grad_scale), w4.x);
+    o.y = f(j + 1, gi + 1, __fmul_rn(g[1], sa.grad_scale), w4.y);
+    o.z = f(j + 2, gi + 2, __fmul_rn(g[2], sa.grad_scale), w4.z);
+    o.w = f(j + 3, gi + 3, __fmul_rn(g[3], sa.grad_scale), w4.w);
+#pragma unroll
+    for (int p = 0; p < RB; ++p)
+      if (p < Rw) st_sys_f4((float *)ra.out[p] + gi, o);
+  }
+}
+
 // One rank's fused step with a caller-supplied update.  GT: gradient element
-// type (float or __half); weights and the gathered output are fp32.
+// type (float or __half); weights and the gathered output are fp32.  `src` is
+// the rank's argument block (kernel parameter or device memory); the CTAs of
+// one rank are blockIdx.x = 0 .. gridDim.x - 1.
 template <typename GT, class F>
-__global__ void __launch_bounds__(512, 2)
-    cocoGenericFusedKernel(const __grid_constant__ coco::StepArgs sa,
-                           const __grid_constant__ coco::RankArgs ra_in, const F f) {
+__device__ __forceinline__ void cocoGenericFusedBody(const coco::StepArgs &sa, const coco::RankArgs *src,
+                                                     const F &f) {
   using namespace coco_generic;
   __shared__ coco::RankArgs ra;
   __shared__ int s_ok;
   {
-    const int *s = reinterpret_cast<const int *>(&ra_in);
+    const int *s = reinterpret_cast<const int *>(src);
     int *d = reinterpret_cast<int *>(&ra);
     for (int k = threadIdx.x; k < (int)(sizeof(coco::RankArgs) / sizeof(int)); k += blockDim.x)
       d[k] = s[k];
@@ -193,28 +226,14 @@ __global__ void __launch_bounds__(512, 2)
   const bool gather = (sa.flags & coco::kFlagNoGather) == 0;
   const int Rr = reduce ? R : 0, Rw = gather ? R : 0;
   if (ok) {
-    for (size_t u = tid; u < nvec; u += nth) {
-      const size_t j = u * 4, gi = lo + j;
-      float g[4] = {0.f, 0.f, 0.f, 0.f}, x[coco::kMaxRanks][4];
-#pragma unroll
-      for (int p = 0; p < coco::kMaxRanks; ++p)
-        if (p < Rr) Grad<GT>::load4(ra.g[p], gi, x[p]);
-#pragma unroll
-      for (int p = 0; p < coco::kMaxRanks; ++p)
-        if (p < Rr) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) g[e] = p == 0 ? x[0][e] : __fadd_rn(g[e], x[p][e]);
-        }
-      const float4 w4 = *reinterpret_cast<const float4 *>(ra.w + gi);
-      float4 o;
-      o.x = f(j + 0, gi + 0, __fmul_rn(g[0], sa.grad_scale), w4.x);
-      o.y = f(j + 1, gi + 1, __fmul_rn(g[1], sa.grad_scale), w4.y);
-      o.z = f(j + 2, gi + 2, __fmul_rn(g[2], sa.grad_scale), w4.z);
-      o.w = f(j + 3, gi + 3, __fmul_rn(g[3], sa.grad_scale), w4.w);
-#pragma unroll
-      for (int p = 0; p < coco::kMaxRanks; ++p)
-        if (p < Rw) st_sys_f4((float *)ra.out[p] + gi, o);
-    }
+    if (R == 1)
+      cocoGenericVectorLoop<GT, F, 1>(sa, ra, f, lo, nvec, tid, nth, Rr, Rw);
+    else if (R == 2)
+      cocoGenericVectorLoop<GT, F, 2>(sa, ra, f, lo, nvec, tid, nth, Rr, Rw);
+    else if (R <= 4)
+      cocoGenericVectorLoop<GT, F, 4>(sa, ra, f, lo, nvec, tid, nth, Rr, Rw);
+    else
+      cocoGenericVectorLoop<GT, F, coco::kMaxRanks>(sa, ra, f, lo, nvec, tid, nth, Rr, Rw);
     for (size_t j = nvec * 4 + tid; j < L; j += nth) {
       const size_t gi = lo + j;
       float g = 0.f;
@@ -256,6 +275,25 @@ __global__ void __launch_bounds__(512, 2)
       }
     }
   }
+}
+
+template <typename GT, class F>
+__global__ void __launch_bounds__(512, 2)
+    cocoGenericFusedKernel(const __grid_constant__ coco::StepArgs sa,
+                           const __grid_constant__ coco::RankArgs ra_in, const F f) {
+  cocoGenericFusedBody<GT, F>(sa, &ra_in, f);
+}
+
+// Several ranks that share one GPU (virtual ranks of a single-process
+// communicator) as ONE cooperative launch: blockIdx.y is the rank, whose
+// argument block and functor come from tables in device memory.  Kernels that
+// wait for one another must never be separate launches on one GPU.
+template <typename GT, class F>
+__global__ void __launch_bounds__(512, 2)
+    cocoGenericFusedKernelMulti(const __grid_constant__ coco::StepArgs sa,
+                                const coco::RankArgs *__restrict__ table, const F *__restrict__ ftable) {
+  const F f = ftable[blockIdx.y];
+  cocoGenericFusedBody<GT, F>(sa, table + blockIdx.y, f);
 }
 
 // Host: enqueue one fused step with the update `f` on `stream`.

@@ -27,6 +27,15 @@
  *  - buffers read or written by peers (g, and w or w_lp) are peer-mapped on
  *    first use (a collective host-side exchange) unless registered before
  *    with cocoRegister.
+ *  - a fused call that fails on the host at world size > 1 (a buffer that
+ *    cannot be mapped, a launch error) leaves this rank's call count ahead of
+ *    its peers': the communicator then refuses every further call with
+ *    cocoInvalidUsage.  Destroy it, as after a device-side timeout.  Argument
+ *    errors (cocoInvalidArgument) are found before that and are harmless.
+ *  - buffers that the runtime peer-mapped on first use stay mapped for the
+ *    life of the communicator: keep them allocated until it is destroyed, or
+ *    hand them to cocoDeregister first (an allocator that reuses the address
+ *    for another tensor would otherwise meet the peers' old mappings).
  *  - every device-side wait is bounded (COCO_TIMEOUT_MS, default 10000); on
  *    expiry the kernel records {code, rank, phase, peer} in a host-visible
  *    status word and returns.  Read it with cocoGetStatus after synchronising
@@ -120,10 +129,41 @@ int cocoCommInitRank(cocoComm_t *comm, int world, int rank, const char *bootstra
  * GPU). */
 int cocoCommInitAll(cocoComm_t *comms, int n, const int *devices);
 
+/* Collective in process mode (all ranks call it; bounded by the bootstrap's
+ * timeout): every rank synchronises its device, symmetric allocations that
+ * were not freed with cocoMemFree are released, and only when all ranks have
+ * arrived are the peers' mappings closed and the flag page freed -- a peer may
+ * still be finishing its last kernel on this rank's memory before that. */
 int cocoCommDestroy(cocoComm_t comm);
 int cocoCommCount(cocoComm_t comm, int *world);
 int cocoCommUserRank(cocoComm_t comm, int *rank);
 int cocoCommCuDevice(cocoComm_t comm, int *device);
+
+/* What cocoCommInitRank learned about the links between the ranks' GPUs: the
+ * counterpart of the reference's peer-access check and topology search
+ * (nccl/src/transport/p2p.cc:118-238, nccl/src/graph/*.cc), reduced to what a
+ * one-hop NVSwitch node needs.  Every rank asks the driver, for each peer's
+ * GPU (found by PCI bus id), whether it can map that GPU's memory and at
+ * which relative performance (cudaDeviceGetP2PAttribute), and the rows are
+ * gathered over the bootstrap.  A pair WITHOUT peer access fails the
+ * communicator at creation with cocoPeerError (the fused step is built on
+ * peer loads and stores; there is no staged fallback); unequal performance
+ * ranks are reported (uniform = 0, a warning under COCO_DEBUG=WARN) because
+ * the one-shot exchange assumes every peer is equally near.
+ * [a][b] is rank a's view of rank b's GPU; -1 = the driver did not say (the
+ * peer's GPU is not visible to this process); the diagonal is 1 / 0 / 1. */
+typedef struct {
+  int world;
+  int access[COCO_MAX_RANKS][COCO_MAX_RANKS];
+  int perf_rank[COCO_MAX_RANKS][COCO_MAX_RANKS];
+  int native_atomics[COCO_MAX_RANKS][COCO_MAX_RANKS];
+  int uniform; /* every pair reachable, all known performance ranks equal */
+} cocoTopology_t;
+int cocoCommTopology(cocoComm_t comm, cocoTopology_t *topology);
+/* The rule above on a caller-supplied table (row-major world x world, needs
+ * no GPU): cocoPeerError if some access[a][b] == 0 for a != b, else
+ * cocoSuccess with *uniform set. */
+int cocoTopologyCheck(int world, const int *access, const int *perf_rank, int *uniform);
 
 /* Host-side barrier and all-gather of small blobs over the bootstrap (what
  * the emitted programs used MPI_Barrier / MPI_Bcast for). */
@@ -178,7 +218,8 @@ int cocoRegisterMapped(cocoComm_t comm, void *ptr, size_t bytes, void *const *pe
  * communicator; put the gradients and the gathered weights in such buffers to
  * get the NVLS path without any other library.  At world size 1 this is
  * cudaMalloc.  COCO_NO_MULTICAST=1 skips the multicast mapping.  Free with
- * cocoMemFree (collective) before destroying the communicator. */
+ * cocoMemFree (collective); what is still allocated when the communicator is
+ * destroyed is released then. */
 int cocoMemAlloc(cocoComm_t comm, void **ptr, size_t bytes);
 int cocoMemFree(cocoComm_t comm, void *ptr);
 int cocoMemHasMulticast(cocoComm_t comm, const void *ptr, int *yes);

@@ -39,3 +39,17 @@ def test_frozen_style_program_passes_its_host_checks(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.split() == ["PASSED", "sgd", "PASSED", "adam", "PASSED", "adam-mixed",
                                 "PASSED", "lamb"], r.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("R", [2, 3])
+def test_frozen_style_program_with_virtual_ranks_on_one_gpu(tmp_path, R):
+    # the four arities at more than one rank without more than one GPU: all R
+    # ranks live in the process (cocoCommInitAll, device 0 listed R times) and
+    # each AllReduce_pipe round is one grouped launch
+    exe = _build(tmp_path, link=True)
+    env = dict(os.environ, COMPAT_VIRTUAL_RANKS=str(R))
+    r = subprocess.run([exe, "10007"], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.split() == ["PASSED", "sgd", "PASSED", "adam", "PASSED", "adam-mixed",
+                                "PASSED", "lamb"], r.stdout

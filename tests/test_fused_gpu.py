@@ -342,7 +342,9 @@ def test_lamb_nccl_variant_matches_oracle(R, n):
     wl = np.zeros(n, np.float16)
     try:
         for step in range(2):
-            grads = K.make_grads(R, n, 14, step, dtype=np.float16, loss_scale=256.0)
+            # gradients of one sign: a ring sum that cancels to exactly zero gives v = 0 and
+            # 0/0 in this formulation (it has no epsilon), which would make the check vacuous
+            grads = [np.abs(x) for x in K.make_grads(R, n, 14, step, dtype=np.float16, loss_scale=256.0)]
             ranks.step(grads, step, variant=coco.VARIANT_NCCL,
                        hyper=dict(lr=1e-3, beta1=0.9, beta2=0.999, weight_decay=0.01))
             gsum = np.empty(n, np.float32)
@@ -357,7 +359,10 @@ def test_lamb_nccl_variant_matches_oracle(R, n):
                 K.assert_close(ranks.w[r].cpu().numpy()[lo:hi], w[lo:hi], RTOL_FP32, f"w step {step}")
                 K.assert_close(ranks.lp[r].float().cpu().numpy(), wl.astype(np.float32), 1e-3, "w_lp")
             wn, rn = ranks.comms[0].last_lamb_norms()
-            np.testing.assert_allclose([wn, rn], norms, rtol=2e-6)  # fp32 sums vs double sums
+            assert np.isfinite(norms).all() and np.isfinite(w).all()
+            # the oracle adds the squares in fp32 in element order (the fork: fp32 atomics in
+            # no fixed order), the kernel in double: they agree to fp32 summation error
+            np.testing.assert_allclose([wn, rn], norms, rtol=2e-4)
     finally:
         ranks.close()
 

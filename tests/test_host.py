@@ -103,6 +103,26 @@ def _bs_worker(world, rank, port, q, mode):
             q.put((rank, "skipped"))
             return
         bs = coco.HostBootstrap(world, rank, f"127.0.0.1:{port}", timeout_ms=1500 if mode == "absent" else 20000)
+        if mode in ("size_mismatch", "kind_mismatch"):
+            bs.barrier()
+            try:  # rank 1 is in another collective than the rest: every rank must be told
+                if mode == "size_mismatch":
+                    bs.all_gather(bytes(64 if rank == 1 else 8))
+                elif rank == 1:
+                    bs.all_gather(b"x")
+                else:
+                    bs.barrier()
+                first = "passed"
+            except coco.CocoError as e:
+                first = f"error {e.code}"
+            try:  # and the connection stays refused afterwards
+                bs.barrier()
+                second = "passed"
+            except coco.CocoError as e:
+                second = f"error {e.code}"
+            bs.close()
+            q.put((rank, (first, second)))
+            return
         out = []
         for rnd in range(3):
             blob = bytes([rank, rnd]) * 50
@@ -145,6 +165,33 @@ def test_bootstrap_times_out_when_a_rank_never_joins():
     assert res[2] == "skipped"
     assert res[0] == "error 5"  # rank 0 gives up in accept()
     assert res[1].startswith("error")  # connected, then the root went away
+
+
+@pytest.mark.parametrize("mode", ["size_mismatch", "kind_mismatch"])
+def test_bootstrap_refuses_ranks_that_are_out_of_step(mode):
+    # a rank in a different collective (other size, or an all-gather against a
+    # barrier) must not have its bytes taken for the others': invalid usage (2)
+    # on every rank, then and afterwards
+    res = _run(3, mode)
+    assert res == {r: ("error 2", "error 2") for r in range(3)}
+
+
+def test_topology_rule_on_fake_tables():
+    # what cocoCommInitRank applies to the gathered cudaDeviceGetP2PAttribute rows
+    R = 4
+    full = [[1] * R for _ in range(R)]
+    flat_perf = [[0] * R for _ in range(R)]
+    assert coco.topology_check(R, full, flat_perf) == (0, True)           # NVSwitch: all equal
+    ring = [[0 if a == b else (0 if abs(a - b) in (1, R - 1) else 1) for b in range(R)] for a in range(R)]
+    assert coco.topology_check(R, full, ring) == (0, False)               # unequal performance ranks
+    cut = [row[:] for row in full]
+    cut[2][3] = 0
+    assert coco.topology_check(R, cut, flat_perf)[0] == 6                 # cocoPeerError
+    unknown = [row[:] for row in full]
+    unknown[0][1] = -1
+    assert coco.topology_check(R, unknown, flat_perf) == (0, False)       # the driver did not say
+    assert coco.topology_check(1, [[1]], [[0]]) == (0, True)
+    assert coco.lib().cocoTopologyCheck(9, None, None, None) == 1
 
 
 # ---- world-size-2 host path under torch.distributed (gloo, CPU) --------------
