@@ -560,6 +560,51 @@ def numa_bind(local_rank):
     return None
 
 
+def run_probe(args, rank, world, local_rank):
+    """The link yardstick alone: every mode and unroll of cocoLinkProbe over a
+    1 GiB buffer (GB/s per direction per GPU), plus, where the node has an
+    NVSwitch multicast mapping, the same through the switch and the time of the
+    hybrid split (part of the slice through the switch, the rest peer to peer)."""
+    import torch
+    import torch.distributed as dist
+    import coconet_b200 as coco
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world < 2:
+        raise SystemExit("--probe measures links: launch it with torchrun on 2 or more GPUs")
+    dist.init_process_group("nccl", device_id=dev)
+    comm = coco.Communicator.from_torch_distributed()
+    out = {}
+    try:
+        buf = torch.zeros(1 << 28, dtype=torch.float32, device=dev)
+        comm.register(buf)
+        out["copy_engine"] = round(comm.link_probe(buf, "copy"), 1)
+        for mode in ("pull", "push", "both"):
+            for u in (1, 2, 4):
+                out[f"{mode}_u{u}"] = round(comm.link_probe(buf, mode, unroll=u), 1)
+        sym = comm.mem_alloc(1 << 28, torch.float32)
+        sym.zero_()
+        torch.cuda.synchronize()
+        if comm.has_multicast(sym):
+            for mode in ("switch_reduce", "switch_store", "switch_both"):
+                for u in (1, 2, 4):
+                    out[f"{mode}_u{u}"] = round(comm.link_probe(sym, mode, unroll=u), 1)
+            out["hybrid_us_by_sixteenths_through_switch"] = {
+                str(k): round(comm.link_probe(sym, "hybrid", unroll=k), 1) for k in (0, 4, 8, 10, 12, 14, 16)}
+        st = comm.status()
+        if rank == 0:
+            print(json.dumps({"link_probe": out, "n_gpus": world, "unit": "GB/s per direction per GPU",
+                              "buffer_bytes": 1 << 30, "status": st["code"],
+                              "topology": comm.topology()}), flush=True)
+        torch.cuda.synchronize()
+        comm.mem_free(sym)
+    finally:
+        comm.destroy()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -578,6 +623,7 @@ def main():
                     help="who makes the symmetric memory of the NVLS path")
     ap.add_argument("--sweep", action="store_true", help="message-size sweep instead of one workload")
     ap.add_argument("--sweep-max-log", type=int, default=30)
+    ap.add_argument("--probe", action="store_true", help="the link yardstick alone (N > 1)")
     ap.add_argument("--algo", default=os.environ.get("COCO_BENCH_ALGO", "auto"),
                     choices=["auto", "p2p", "nvls"],
                     help="nvls: gradients and gathered weights in symmetric memory with an NVSwitch "
@@ -599,6 +645,9 @@ def main():
 
     if args.sweep:
         run_sweep(args, rank, world, local_rank)
+        return
+    if args.probe:
+        run_probe(args, rank, world, local_rank)
         return
 
     import numpy as np

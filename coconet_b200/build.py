@@ -23,17 +23,26 @@ def _stale():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build_library(force=False, verbose=False):
+def build_library(force=False, verbose=False, checked=False):
     """Compile for sm_100a only; returns the path of the shared library.  The
     kernel file is compiled as four parts in parallel (see COCO_PART in
-    fused_step.cu)."""
+    fused_step.cu).  `checked` builds libcoconet_rt_checked.so beside it: the
+    same library with per-unit bounds and alignment checks in the kernels that
+    record cocoInternalError in the status word (load it with
+    COCO_RT_LIBRARY=<that file>)."""
+    if checked:
+        return _build(os.path.join(HERE, "libcoconet_rt_checked.so"), os.path.join(HERE, "build", "checked"),
+                      ["-DCOCO_CHECKED=1"], verbose)
     if not force and not _stale():
         return LIB
+    return _build(LIB, os.path.join(HERE, "build"), [], verbose)
+
+
+def _build(lib, objdir, extra, verbose):
     from concurrent.futures import ThreadPoolExecutor
-    objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     base = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-            "-Xcompiler", "-fPIC", "-diag-suppress", "177", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
+            "-Xcompiler", "-fPIC", "-diag-suppress", "177", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC] + extra
     if verbose:
         base += ["-Xptxas", "-v"]
     jobs = []
@@ -47,9 +56,9 @@ def build_library(force=False, verbose=False):
         jobs.append((base + ["-c", os.path.join(CSRC, src), "-o", obj], obj))
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
         list(pool.map(lambda j: subprocess.check_call(j[0]), jobs))
-    subprocess.check_call([NVCC, "-shared", "-cudart", "shared", "-Wno-deprecated-gpu-targets", "-o", LIB] + [j[1] for j in jobs])
-    return LIB
+    subprocess.check_call([NVCC, "-shared", "-cudart", "shared", "-Wno-deprecated-gpu-targets", "-o", lib] + [j[1] for j in jobs])
+    return lib
 
 
 if __name__ == "__main__":
-    print(build_library(force=True, verbose="-v" in os.sys.argv))
+    print(build_library(force=True, verbose="-v" in os.sys.argv, checked="--checked" in os.sys.argv))

@@ -38,8 +38,25 @@
 #ifndef COCO_LOCAL16_SHUFFLE
 #define COCO_LOCAL16_SHUFFLE 0   // 1: 16-byte gradient loads / copy stores, halves exchanged by shuffles
 #endif
+#ifndef COCO_CHECKED
+#define COCO_CHECKED 0  // 1: bounds and alignment checks per unit that set the status word
+#endif
+// Block size the single-rank kernels are compiled for, two CTAs per SM: the
+// register budget is 65536 / (2 x this).  The 16-bit-gradient kernels work on
+// 8-element units and spill at 64 registers; at 384 threads they have 80 and
+// measured 0.957 of the HBM copy peak against 0.910 at 512 (mixed-precision
+// Adam, 334 M elements; 256 threads, 116 registers, no spills at all: 0.801 --
+// too few warps).
 #ifndef COCO_LOCAL16_THREADS
-#define COCO_LOCAL16_THREADS 512  // block size the kernel is compiled for (registers: 65536 / (2 x this))
+#define COCO_LOCAL16_THREADS 384
+#endif
+#ifndef COCO_LOCAL32_THREADS
+#define COCO_LOCAL32_THREADS 512
+#endif
+// The same for the multi-rank paths (register-staged, switch, warp rings) with
+// 16-bit gradients.
+#ifndef COCO_MULTI16_THREADS
+#define COCO_MULTI16_THREADS 512
 #endif
 
 namespace coco {
@@ -645,6 +662,26 @@ template <int OPT, typename LPT, int VEC, int RB, int HS = 4, bool NVLS = false>
 __device__ __forceinline__ void apply_unit(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
                                            size_t lo, size_t i, const float (&g)[VEC],
                                            double &sum_w2, double &sum_r2) {
+#if COCO_CHECKED
+  // Checked build (python -m coconet_b200.build --checked): every unit proves
+  // that it lies inside the rank's slice and, for vector units, that its
+  // addresses are 16-byte aligned; a unit that does not is skipped and the
+  // status word says so (cocoInternalError), instead of a stray access.
+  {
+    const size_t S_ = (sa.count + sa.world - 1) / sa.world;
+    const size_t lo_ = (size_t)ra.rank * S_ < sa.count ? (size_t)ra.rank * S_ : sa.count;
+    const size_t hi_ = lo_ + S_ < sa.count ? lo_ + S_ : sa.count;
+    const size_t last = i + (VEC > 4 ? HS + 4 : VEC);  // one past the unit's last element
+    const bool in_slice = (sa.flags & kFlagScattered) || (i >= lo_ && last <= hi_);
+    const bool aligned = VEC < 4 || ((((uintptr_t)(ra.w + i)) & 15u) == 0 &&
+                                     (OPT == kSGD || ((((uintptr_t)(ra.m + (i - lo))) & 15u) == 0 &&
+                                                      (((uintptr_t)(ra.v + (i - lo))) & 15u) == 0)));
+    if (!in_slice || !aligned) {
+      record_status(ra.flags[ra.rank], cocoInternalError, ra.rank, kPhaseCheck, -1, sa.seq);
+      return;
+    }
+  }
+#endif
   float w[VEC];
   load_f32<VEC, HS>(ra.w + i, w);
   if constexpr (OPT == kSGD) {
@@ -1163,7 +1200,9 @@ enum : int { kPathDirect = 0, kPathNvls = 1, kPathRing = 2, kPathLocal = 3, kPat
 
 // Threads per CTA a path's kernel is compiled for (two CTAs per SM).
 template <int PATH, typename GT> struct BlockThreads {
-  static constexpr int value = (PATH == kPathLocal && GradTraits<GT>::kIs16) ? COCO_LOCAL16_THREADS : 512;
+  static constexpr int value =
+      PATH == kPathLocal ? (GradTraits<GT>::kIs16 ? COCO_LOCAL16_THREADS : COCO_LOCAL32_THREADS)
+      : (PATH < kPathSegments && GradTraits<GT>::kIs16) ? COCO_MULTI16_THREADS : 512;
 };
 
 template <int OPT, typename GT, typename LPT, int PATH>
@@ -1683,7 +1722,8 @@ int fused_step_path(const StepArgs &sa) {
 
 int fused_step_block_threads(int path, cocoDataType_t g_type) {
   const bool is16 = g_type != cocoFloat32;
-  return (path == kPathLocal && is16) ? COCO_LOCAL16_THREADS : 512;
+  if (path == kPathLocal) return is16 ? COCO_LOCAL16_THREADS : COCO_LOCAL32_THREADS;
+  return (path < kPathSegments && is16) ? COCO_MULTI16_THREADS : 512;
 }
 
 namespace {

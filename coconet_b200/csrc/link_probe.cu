@@ -137,6 +137,102 @@ __global__ void __launch_bounds__(512)
   }
 }
 
+// Hybrid: the even CTAs take the first `sa.pad` sixteenths of the rank's slice
+// through the switch (multimem.ld_reduce + multimem.st), the odd CTAs the rest
+// peer to peer (pull from all peers + push to all peers), at the same time.
+// Tells whether the switch's reductions and plain peer traffic compete for
+// the same resource or can overlap.
+template <int RB>
+__global__ void __launch_bounds__(512)
+    hybrid_probe_kernel(const __grid_constant__ StepArgs sa, const __grid_constant__ RankArgs ra_in) {
+  using namespace coco_generic;
+  __shared__ RankArgs ra;
+  __shared__ int s_ok;
+  {
+    const int *s = reinterpret_cast<const int *>(&ra_in);
+    int *d = reinterpret_cast<int *>(&ra);
+    for (int k = threadIdx.x; k < (int)(sizeof(RankArgs) / sizeof(int)); k += blockDim.x)
+      d[k] = s[k];
+    if (threadIdx.x == 0) s_ok = 1;
+  }
+  __syncthreads();
+  const int R = sa.world, rank = ra.rank;
+  FlagPage *me = ra.flags[rank];
+  const unsigned long long seq = sa.seq;
+  if (threadIdx.x < 32) {
+    const int p = threadIdx.x;
+    const bool peer = p < R && p != rank;
+    if (blockIdx.x == 0 && peer) st_release(&ra.flags[p]->arrive[rank], seq);
+    bool late = false;
+    if (peer) late = !wait_flag(&me->arrive[p], seq, sa.timeout_ns);
+    const unsigned bad = __ballot_sync(0xffffffffu, late);
+    if (bad && threadIdx.x == 0) {
+      record(me, cocoTimeout, rank, kPhaseStart, __ffs(bad) - 1, seq);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+  const size_t N = sa.count;
+  const size_t S = (N + R - 1) / R;
+  const size_t lo = (size_t)rank * S < N ? (size_t)rank * S : N;
+  const size_t hi = lo + S < N ? lo + S : N;
+  const size_t L = hi - lo;
+  const size_t cut = L / 16 * (size_t)sa.pad;  // units [0, cut) through the switch
+  const bool via_switch = (blockIdx.x & 1) == 0;
+  const size_t half_ctas = via_switch ? (gridDim.x + 1) / 2 : gridDim.x / 2;
+  const size_t tid = (size_t)(blockIdx.x >> 1) * blockDim.x + threadIdx.x;
+  const size_t nth = half_ctas * blockDim.x;
+  if (ok && via_switch) {
+    for (size_t u = tid; u < cut; u += 2 * nth) {
+      const size_t u2 = u + nth;
+      uint4 a = mc_ld_reduce_16((const uint4 *)ra.mc_g + lo + u), b = a;
+      if (u2 < cut) b = mc_ld_reduce_16((const uint4 *)ra.mc_g + lo + u2);
+      mc_st_16((uint4 *)ra.mc_out + lo + u, a);
+      if (u2 < cut) mc_st_16((uint4 *)ra.mc_out + lo + u2, b);
+    }
+  } else if (ok && nth > 0) {
+    for (size_t u = cut + tid; u < L; u += nth) {
+      uint4 acc = make_uint4(rank, (unsigned)u, 0, 0), x[RB - 1];
+#pragma unroll
+      for (int q = 0; q < RB - 1; ++q) {
+        int p = rank + 1 + q;
+        if (p >= R) p -= R;
+        if (q < R - 1) x[q] = ld_peer_16((const uint4 *)ra.g[p] + lo + u);
+      }
+#pragma unroll
+      for (int q = 0; q < RB - 1; ++q)
+        if (q < R - 1) acc.x ^= x[q].x, acc.y ^= x[q].y, acc.z ^= x[q].z, acc.w ^= x[q].w;
+#pragma unroll
+      for (int q = 0; q < RB - 1; ++q) {
+        int p = rank + 1 + q;
+        if (p >= R) p -= R;
+        if (q < R - 1) st_peer_16((uint4 *)ra.out[p] + lo + u, acc);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    unsigned prev = 0;
+    if (threadIdx.x == 0) {
+      prev = atomicAdd(&me->done_count, 1u);
+      if (prev == gridDim.x - 1) me->done_count = 0;
+      __threadfence_system();
+    }
+    prev = __shfl_sync(0xffffffffu, prev, 0);
+    if (prev == gridDim.x - 1) {
+      const int p = threadIdx.x;
+      const bool peer = p < R && p != rank;
+      if (peer) st_release(&ra.flags[p]->done[rank], seq);
+      bool late = false;
+      if (peer && ok) late = !wait_flag(&me->done[p], seq, sa.timeout_ns);
+      const unsigned bad = __ballot_sync(0xffffffffu, late);
+      if (bad && threadIdx.x == 0) record(me, cocoTimeout, rank, kPhaseEnd, __ffs(bad) - 1, seq);
+    }
+  }
+}
+
 // MODE 0 pull, 1 push, 2 both.  U: units of 16 bytes per thread and pass.
 // RB: compile-time bound on the world size (RB - 1 peer slots per unit).
 // sa.count = 16-byte units of the whole buffer; the rank's slice is sliced as
@@ -287,7 +383,11 @@ cudaError_t launch_link_probe(int mode, int unroll, const StepArgs &sa, const Ra
                : mode == 2 ? pick_world<2>(sa.world, unroll)
                : mode == 4 ? pick_switch<0>(unroll)
                : mode == 5 ? pick_switch<1>(unroll)
-               : mode == 6 ? pick_switch<2>(unroll) : nullptr;
+               : mode == 6 ? pick_switch<2>(unroll)
+               : mode == 7 ? (sa.world <= 2 ? (ProbePtr)hybrid_probe_kernel<2>
+                              : sa.world <= 4 ? (ProbePtr)hybrid_probe_kernel<4>
+                                              : (ProbePtr)hybrid_probe_kernel<8>)
+                           : nullptr;
   if (!k) return cudaErrorInvalidValue;
   int occ = 0;  // the deeper unrolls hold more registers: fewer CTAs per SM
   cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void *)k, threads, 0);

@@ -379,7 +379,8 @@ int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
   // 4, or COCO_RING_STAGES) as fit the shared-memory budget of one CTA; off
   // when the slice has no full tile, for lists of tensors and on the NVLS path.
   int want_per_sm = c->ctas_per_sm > 0 ? c->ctas_per_sm : 2;
-  const size_t warps = (size_t)c->threads / 32;
+  // block size of the multi-rank paths (the ring's shared memory depends on it)
+  const size_t warps = (size_t)std::min(c->threads, fused_step_block_threads(0, g_type)) / 32;
   const size_t stage_bytes = (size_t)world * kRingTileBytesPerRank * warps;
   const size_t tile_elems = 32 * (16 / dtype_size(g_type));
   int stages = 0;
@@ -1480,9 +1481,11 @@ int cocoFusedLAMBScattered(cocoComm_t comm, size_t nbuff, const void *const *g,
 
 int cocoLinkProbe(cocoComm_t comm, void *buf, size_t bytes, int mode, int unroll, int iters,
                   double *gbs_per_direction, cocoStream_t stream) {
-  if (!comm || !buf || !gbs_per_direction || iters < 1 || mode < 0 || mode > 6)
+  if (!comm || !buf || !gbs_per_direction || iters < 1 || mode < 0 || mode > 7)
     return cocoInvalidArgument;
-  if (mode != 3 && unroll != 1 && unroll != 2 && unroll != 4) return cocoInvalidArgument;
+  // mode 7 (hybrid): `unroll` is the number of sixteenths of the slice that go through the switch
+  if (mode == 7 && (unroll < 0 || unroll > 16)) return cocoInvalidArgument;
+  if (mode != 3 && mode != 7 && unroll != 1 && unroll != 2 && unroll != 4) return cocoInvalidArgument;
   if ((((uintptr_t)buf) & 15u) != 0 || bytes < 32u * (size_t)comm->world) return cocoInvalidArgument;
   if (comm->group) return cocoInvalidUsage;  // one process per GPU
   *gbs_per_direction = 0.0;
@@ -1517,7 +1520,10 @@ int cocoLinkProbe(cocoComm_t comm, void *buf, size_t bytes, int mode, int unroll
     size_t lo = (size_t)comm->rank * slice_units;
     if (lo > pc.sa.count) lo = pc.sa.count;
     const size_t len = std::min<size_t>(pc.sa.count - lo, slice_units);
-    if (mode <= 2)  // peer to peer: R - 1 slices in (pull) and / or out (push)
+    if (mode == 7) {  // reported as the time of one iteration in microseconds instead of a rate
+      pc.sa.pad = unroll;
+      dir_bytes = 1e3;
+    } else if (mode <= 2)  // peer to peer: R - 1 slices in (pull) and / or out (push)
       dir_bytes = (double)(R - 1) * (double)len * 16.0 * (mode == 2 ? 2.0 : 1.0);
     else  // switch: the whole buffer leaves (reduce) or arrives (store) once, the slice the other way
       dir_bytes = (double)pc.sa.count * 16.0 + (mode == 6 ? (double)len * 16.0 : 0.0);
@@ -1573,6 +1579,7 @@ int cocoLinkProbe(cocoComm_t comm, void *buf, size_t bytes, int mode, int unroll
     least_bytes = std::min(least_bytes, all[2 * r + 1]);
   }
   if (worst_ms > 0.0) *gbs_per_direction = least_bytes / (worst_ms * 1e-3) / 1e9;
+  if (mode == 7) *gbs_per_direction = worst_ms * 1e3;  // microseconds per iteration
   return cocoSuccess;
 }
 

@@ -411,7 +411,7 @@ class Communicator:
         "switch_store", "switch_both"; `buf` from mem_alloc), over `buf`
         (overwritten).  Collective; synchronises."""
         code = {"pull": 0, "push": 1, "both": 2, "copy": 3, "switch_reduce": 4,
-                "switch_store": 5, "switch_both": 6}[mode]
+                "switch_store": 5, "switch_both": 6, "hybrid": 7}[mode]
         out = C.c_double()
         _check(lib().cocoLinkProbe(self._h, _ptr(buf), buf.numel() * buf.element_size(), code,
                                    unroll, iters, C.byref(out), _stream(stream)), "cocoLinkProbe")

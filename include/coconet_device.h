@@ -18,7 +18,7 @@ constexpr int kMaxLambTensors = COCO_MAX_LAMB_TENSORS;  // tensors of one scatte
 enum Opt : int { kSGD = 0, kAdam = 1, kLAMB = 2 };
 
 // Phases recorded in the status word when a bounded wait gives up.
-enum Phase : int { kPhaseStart = 1, kPhaseNorm = 2, kPhaseEnd = 3, kPhaseCopy = 4 };
+enum Phase : int { kPhaseStart = 1, kPhaseNorm = 2, kPhaseEnd = 3, kPhaseCopy = 4, kPhaseCheck = 5 };
 
 // One per rank, in device memory, mapped into every peer.  Zero at creation;
 // every flag only ever grows (it holds the sequence number of a fused call),

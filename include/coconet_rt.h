@@ -104,7 +104,8 @@ typedef enum {
 typedef struct {
   int code;        /* cocoResult_t of the first device-side failure, 0 if none */
   int rank;        /* rank that recorded it */
-  int phase;       /* 1 start barrier, 2 norm exchange, 3 end barrier, 4 tile copy */
+  int phase;       /* 1 start barrier, 2 norm exchange, 3 end barrier, 4 bulk copy of a
+                      gradient tile, 5 a bounds / alignment check of the checked build */
   int peer;        /* peer rank that was waited for, -1 if n/a */
   uint64_t seq;    /* sequence number of the fused call */
 } cocoStatus_t;
@@ -365,7 +366,11 @@ int cocoFusedGenericPlan(cocoComm_t comm, const void *g, cocoDataType_t g_type, 
  * (cudaMemcpyAsync; `unroll` ignored); 4 / 5 / 6: the same three through the
  * NVSwitch -- one multimem.ld_reduce per 16 bytes of the rank's slice, one
  * multimem.st, or both (`buf` must come from cocoMemAlloc with a multicast
- * mapping, else cocoInvalidUsage; its bytes are read as fp32).  One untimed iteration, then `iters`
+ * mapping, else cocoInvalidUsage; its bytes are read as fp32); 7: both ways
+ * at once -- the even CTAs take the first `unroll` sixteenths of the slice
+ * through the switch, the odd CTAs the rest peer to peer -- and the result is
+ * the time of one iteration in MICROSECONDS instead of a rate (it tells
+ * whether the two kinds of traffic overlap or compete).  One untimed iteration, then `iters`
  * timed with CUDA events on `stream`; the call synchronises the stream.
  * *gbs_per_direction = bytes that cross one GPU's links in one direction per
  * iteration / the slowest rank's time per iteration, in GB/s (0 at world size

@@ -342,9 +342,11 @@ def test_lamb_nccl_variant_matches_oracle(R, n):
     wl = np.zeros(n, np.float16)
     try:
         for step in range(2):
-            # gradients of one sign: a ring sum that cancels to exactly zero gives v = 0 and
-            # 0/0 in this formulation (it has no epsilon), which would make the check vacuous
-            grads = [np.abs(x) for x in K.make_grads(R, n, 14, step, dtype=np.float16, loss_scale=256.0)]
+            # gradients in [0.5, 1.5): this formulation has no epsilon and squares the sum in
+            # half precision, so a sum that cancels or is below 2.4e-4 gives v = 0 and a
+            # non-finite r, which would make the check vacuous
+            grads = [(np.abs(x) + 0.5).astype(np.float16)
+                     for x in K.make_grads(R, n, 14, step, dtype=np.float32, dist="uniform")]
             ranks.step(grads, step, variant=coco.VARIANT_NCCL,
                        hyper=dict(lr=1e-3, beta1=0.9, beta2=0.999, weight_decay=0.01))
             gsum = np.empty(n, np.float32)
@@ -422,10 +424,14 @@ def test_lamb_dsl_variant_and_mixed():
 
 
 @pytest.mark.parametrize("opt,R,n", [(K.ADAM, 2, 1 << 20), (K.ADAM, 8, 1 << 20), (K.LAMB, 4, 1 << 20),
-                                     (K.SGD, 2, (1 << 18) + 5), (K.ADAM, 1, (1 << 20) + 3)])
-def test_bulk_copy_tile_pipeline(monkeypatch, opt, R, n):
-    # the optional shared-memory staging path (COCO_PIPELINE=1) must give the
-    # same results as the default register-staged path
+                                     (K.SGD, 2, (1 << 18) + 5), (K.ADAM, 1, (1 << 20) + 3),
+                                     (K.ADAM, 3, (1 << 19) + 264), (K.LAMB, 8, (1 << 20) + 8),
+                                     (K.SGD, 8, 1 << 16), (K.ADAM, 4, 300)])
+def test_warp_ring_path(monkeypatch, opt, R, n):
+    # the shared-memory staging path (COCO_PIPELINE=1: per-warp rings filled by bulk
+    # copies) must give the same bits as the register-staged path: whole tiles
+    # through the rings, ragged ends and slices shorter than a tile through the
+    # scalar loop
     monkeypatch.setenv("COCO_PIPELINE", "1")
     ranks = Ranks(opt, R, n, seed=21, lp_dtype=torch.float16 if opt == K.ADAM else None)
     ora = K.OracleState(opt, n, seed=21, lp=opt == K.ADAM)
@@ -440,6 +446,46 @@ def test_bulk_copy_tile_pipeline(monkeypatch, opt, R, n):
                 ranks.step(grads, step)
                 ora.step(grads, step)
             _check_against(ranks, ora, exact_w=opt != K.LAMB)
+    finally:
+        ranks.close()
+
+
+@pytest.mark.parametrize("stages", ["1", "2", "4"])
+def test_warp_ring_depths_and_block_sizes(monkeypatch, stages):
+    monkeypatch.setenv("COCO_PIPELINE", "1")
+    monkeypatch.setenv("COCO_RING_STAGES", stages)
+    monkeypatch.setenv("COCO_THREADS", "256" if stages == "2" else "512")
+    R, n = 2, (1 << 21) + 40
+    ranks = Ranks(K.ADAM, R, n, seed=23)          # fp32 gradients, fp32 weights gathered
+    ora = K.OracleState(K.ADAM, n, seed=23)
+    try:
+        for step in range(3):
+            grads = K.make_grads(R, n, 23, step)
+            ranks.step(grads, step)
+            ora.step(grads, step)
+            _check_against(ranks, ora, exact_w=True)
+    finally:
+        ranks.close()
+
+
+def test_warp_ring_path_forked_nccl_variant(monkeypatch):
+    # the fp16 ring-order sum (owner + 1 first) read out of the staged tiles
+    monkeypatch.setenv("COCO_PIPELINE", "1")
+    R, n = 4, 1 << 16
+    ranks = Ranks(K.ADAM, R, n, seed=8, lp_dtype=torch.float16)
+    try:
+        grads = K.make_grads(R, n, 8, 0, dtype=np.float16, loss_scale=512.0)
+        w0 = K.make_weights(n, 8)
+        ranks.step(grads, 0, variant=coco.VARIANT_NCCL, hyper=dict(lr=1e-3, beta1=0.9, beta2=0.999))
+        for r in range(R):
+            lo, hi = K.slice_bounds(n, R, r)
+            gh = O.reduce_f16_ring([x[lo:hi].copy() for x in grads], owner=r)
+            w, m, v = w0[lo:hi].copy(), np.zeros(hi - lo, np.float32), np.zeros(hi - lo, np.float32)
+            wl = np.zeros(hi - lo, np.float16)
+            O.adam(w, m, v, None, 1e-3, 0.9, 0.999, 0.0, 0, O.NCCL, w_lp=wl, gsum_h=gh)
+            assert np.array_equal(ranks.m[r].cpu().numpy()[: hi - lo], m)
+            assert np.array_equal(ranks.v[r].cpu().numpy()[: hi - lo], v)
+            K.assert_close(ranks.w[r].cpu().numpy()[lo:hi], w, RTOL_FP32, "w")
     finally:
         ranks.close()
 
