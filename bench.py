@@ -292,6 +292,13 @@ def run_sweep(args, rank, world, local_rank):
     vf = torch.zeros(max_n, device=dev)
     gb32 = torch.empty(max_n, dtype=torch.float32, device=dev)
     gb16 = torch.empty(max_n, dtype=torch.float16, device=dev)
+    # RS_C_AG arm: the reduced slice, the gather's input and output
+    gsl32 = torch.empty(Smax, dtype=torch.float32, device=dev)
+    gsl16 = torch.empty(Smax, dtype=torch.float16, device=dev)
+    ag32 = torch.zeros(Smax, dtype=torch.float32, device=dev)
+    ag16 = torch.zeros(Smax, dtype=torch.float16, device=dev)
+    agf32 = torch.empty(Smax * R, dtype=torch.float32, device=dev)
+    agf16 = torch.empty(Smax * R, dtype=torch.float16, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     if use_nvls:
         comm.set_algo("nvls")
@@ -378,9 +385,38 @@ def run_sweep(args, rank, world, local_rank):
         def stock_copy_only(i):
             gb.copy_(g)
 
+        # RS_C_AG: reduce-scatter, update of the slice, all-gather of the updated slice
+        # (the gather's input is a stand-in of the slice's size and type: timing only)
+        SR = S * R
+        even = SR == n
+        out_t = (lp if lp is not None else w)
+        gsl = (gsl16 if gt == "f16" else gsl32)[:S]
+        ag_in = (ag16 if gt == "f16" else ag32)[:S]
+        ag_out = (agf16 if gt == "f16" else agf32)[:SR]
+        lo_r = min(n, rank * S)
+        w_own = w[lo_r:lo_r + S] if even else None      # ragged counts: the arm is skipped
+        lp_own = out_t[lo_r:lo_r + S] if (even and lp is not None) else None
+
+        def stock_rs(i):
+            gb.copy_(g)
+            if world > 1:
+                dist.reduce_scatter_tensor(gsl, gb)
+            if opt == "sgd":
+                local.fused_sgd(gsl, w_own, 1e-3, w_lp=lp_own, grad_scale=gs)
+            elif opt == "adam":
+                local.fused_adam(gsl, w_own, m[:S], v[:S], h["lr"], h["beta1"], h["beta2"], h["eps"], i,
+                                 w_lp=lp_own, grad_scale=gs)
+            else:
+                local.fused_lamb(gsl, w_own, m[:S], v[:S], h["lr"], h["beta1"], h["beta2"], h["eps"],
+                                 0.01, i, w_lp=lp_own, grad_scale=gs)
+            if world > 1:
+                dist.all_gather_into_tensor(ag_out, ag_in)
+
         steps = 5 if n >= (1 << 26) else 10
         ms = time_ms(fused, steps, 3)
-        base = time_ms(stock, steps, 3) - time_ms(stock_copy_only, steps, 3)
+        t_copy = time_ms(stock_copy_only, steps, 3)
+        base = time_ms(stock, steps, 3) - t_copy
+        base_rs = (time_ms(stock_rs, steps, 3) - t_copy) if world > 1 and even else None
         s_g = 2 if gt == "f16" else 4
         s_o = 2 if gt == "f16" else 4
         state = {"sgd": 8, "adam": 24, "lamb": 36}[opt] + (s_o if gt == "f16" else 0)
@@ -391,11 +427,13 @@ def run_sweep(args, rank, world, local_rank):
         out.append({"opt": opt, "grad": gt, "count": n, "world": R, "ms_back_to_back": b2b,
                     "algo": "nvls" if use_nvls else "p2p", "ms": ms, "bus_gbs": b_bus / ms / 1e6,
                     "hbm_gbs": b_hbm / ms / 1e6, "roof_frac": t_roof / (ms * 1e-3),
-                    "stock_nccl_plus_update_ms": base, "speedup": base / ms})
+                    "stock_nccl_plus_update_ms": base, "stock_rs_update_ag_ms": base_rs,
+                    "speedup": min(base, base_rs or base) / ms})
         if rank == 0:
             p = out[-1]
             print(f"# {opt:5s} {gt} n={n:>11d} fused {ms:9.4f} ms  bus {p['bus_gbs']:7.1f} GB/s  "
-                  f"hbm {p['hbm_gbs']:7.1f} GB/s  roof {p['roof_frac']:.3f}  stock {base:9.4f} ms  "
+                  f"hbm {p['hbm_gbs']:7.1f} GB/s  roof {p['roof_frac']:.3f}  AR_C {base:9.4f} ms  "
+                  f"RS_C_AG {(base_rs if base_rs is not None else float('nan')):9.4f} ms  "
                   f"x{p['speedup']:.2f}" + (f"  back-to-back {b2b * 1e3:7.1f} us" if b2b else ""), flush=True)
     # ---- a list of tensors shaped like BERT-large (24 layers, hidden 1024, FFN 4096,
     # vocabulary 30522, 512 positions: 398 tensors, 336 M elements) through the scattered
