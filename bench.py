@@ -860,19 +860,20 @@ def main():
                 if cfg["opt"] != "sgd" else True
             fixed_order = not use_nvls
             tol_w = 1e-5 if cfg["grad"] == "f32" and fixed_order else 2e-3
-            # weights are O(2e-2): differences are taken relative to |w| + 1e-3 (the floor the
-            # parity tests use); moments relative to |x| + rms(x), since single elements of m
-            # nearly cancel
+            # Every quantity is compared relative to its own scale: |got - want| / (max(|got|,
+            # |want|) + rms(want)).  A plain relative error is meaningless for the elements of
+            # w and m that lie near zero, and the switch path's 16-bit-rounded sums move every
+            # element by about 2^-12 of the typical gradient per step.
             detail = {}
             exact_w = None
             if ow is not None:
-                detail["w"] = rel_err(got_w, ow, 1e-3)
+                detail["w"] = rel_err(got_w, ow, rms(ow))
                 exact_w = bool(np.array_equal(got_w, ow))
                 if owl is not None:
-                    detail["gathered"] = rel_err(got_out.astype(np.float32), owl.astype(np.float32), 1e-3)
+                    detail["gathered"] = rel_err(got_out.astype(np.float32), owl.astype(np.float32), rms(ow))
                     exact_w = exact_w and bool(np.array_equal(got_out.view(np.uint16), owl.view(np.uint16)))
                 else:
-                    detail["gathered"] = rel_err(got_out, ow, 1e-3)
+                    detail["gathered"] = rel_err(got_out, ow, rms(ow))
             if cfg["opt"] != "sgd":
                 # v = (1 - b2) g^2 doubles the relative error of g: a third of its error counts
                 detail["m"] = rel_err(got_m, om, rms(om))
@@ -896,7 +897,8 @@ def main():
                       "ok": bool(flags[0].item()),
                       "what": "oracle on 64 Ki + 512 Ki + 64 Ki elements of every rank's slice after all "
                               "timed and warm-up steps: master weights, m, v, gathered copy; every "
-                              "rank's copy compared with the owners' bits"
+                              "rank's copy compared with the owners' bits; max_rel = max |got - want| / "
+                              "(max(|got|, |want|) + rms(want)) over all of them (v: a third of it)"
                               + ("; LAMB: moments only (the weights need the global norms)"
                                  if cfg["opt"] == "lamb" else ""),
                       "oracle_s": round(time.perf_counter() - t0, 2)}
@@ -908,15 +910,17 @@ def main():
             hg.copy_(g[0])
             hout = torch.empty(N, dtype=out.dtype).pin_memory()
             # Every step copies its gradients in from pinned host memory and the gathered
-            # weights out to pinned host memory.  The copies run on two side streams: step
-            # i's gradients (double-buffered on the device) travel while step i-1's weights
-            # are still on their way out; the kernel of step i waits for both (it overwrites
-            # the weights the outgoing copy reads).
+            # weights out to pinned host memory.  The copies run on two side streams and
+            # both ends are double-buffered on the device: step i+1's gradients travel in
+            # while step i computes, and step i's weights -- copied aside on the device
+            # right after its kernel (0.2 ms) -- travel out while step i+1 computes.
             cur = torch.cuda.current_stream()
             s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
             ev_in = [torch.cuda.Event(), torch.cuda.Event()]
             ev_kernel = [torch.cuda.Event(), torch.cuda.Event()]
+            ev_staged = torch.cuda.Event()
             ev_out = torch.cuda.Event()
+            stage = torch.empty_like(out)
 
             def e2e_step(i):
                 b = i & 1
@@ -925,22 +929,24 @@ def main():
                     g[b].copy_(hg, non_blocking=True)
                     ev_in[b].record(s_in)
                 cur.wait_event(ev_in[b])
-                cur.wait_event(ev_out)             # the previous weights have left `out`
                 fused_step(g[b])
                 ev_kernel[b].record(cur)
-                s_out.wait_event(ev_kernel[b])
+                cur.wait_event(ev_out)             # the previous weights have left the staging copy
+                stage.copy_(out, non_blocking=True)
+                ev_staged.record(cur)
+                s_out.wait_event(ev_staged)
                 with torch.cuda.stream(s_out):
-                    hout.copy_(out, non_blocking=True)
+                    hout.copy_(stage, non_blocking=True)
                     ev_out.record(s_out)
 
             k = max(3, min(args.steps, 10))
             ems = timed(e2e_step, k, 2, finish=lambda: cur.wait_event(ev_out))
             e2e = {"value": R * N / (ems * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ems,
                    "h2d_bytes_per_step": N * s_g, "d2h_bytes_per_step": N * s_o,
-                   "overlap": "copies on two side streams, gradients double-buffered",
+                   "overlap": "copies on two side streams, gradients and outgoing weights double-buffered",
                    "host_gbs_all_ranks": R * N * (s_g + s_o) / (ems * 1e-3) / 1e9,
                    "numa_node": numa}
-            del hg, hout
+            del hg, hout, stage
 
         # ---- stock NCCL arms: AR_C (all-reduce + update over all elements) and RS_C_AG
         # (reduce-scatter + update of the slice + all-gather), the reference's two unfused
