@@ -503,6 +503,11 @@ std::vector<Segment> build_segments(int rank, int world, const FlatLayout &L,
     sg.last_rank = (int)((t1 - 1) / L.slice);
     out.push_back(sg);
   }
+  unsigned long long chunks = 0;  // chunk numbering through all pieces
+  for (Segment &sg : out) {
+    sg.chunk0 = chunks;
+    chunks += (sg.len + kSegChunkElems - 1) / kSegChunkElems;
+  }
   return out;
 }
 
@@ -533,10 +538,10 @@ int upload_segments(cocoComm *c, const std::vector<Segment> &segs, cudaStream_t 
   return cocoSuccess;
 }
 
-// Scattered LAMB: room for one partial-sum pair per (segment, CTA) of this rank.
+// Scattered LAMB: room for one partial-sum pair per chunk of this rank's pieces.
 // Nothing is cleared: a step reads only the entries it wrote.
-int ensure_seg_part(cocoComm *c, size_t nseg, int ctas, cudaStream_t stream, double **dev) {
-  const size_t need = nseg * (size_t)ctas * 2;
+int ensure_seg_part(cocoComm *c, size_t nchunk, cudaStream_t stream, double **dev) {
+  const size_t need = std::max<size_t>(1, nchunk) * 2;
   if (need > c->seg_part_cap) {
     CUDA_TRY(cudaStreamSynchronize(stream));
     if (c->seg_part) CUDA_TRY(cudaFree(c->seg_part));
@@ -571,6 +576,7 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
                                                      pc.v, dtype_size(pc.g_type));
     COCO_TRY(upload_segments(c, segs, pc.stream, &ra.segs));
     ra.nseg = (int)segs.size();
+    ra.nchunk = segs.empty() ? 0 : (int)(segs.back().chunk0 + (segs.back().len + kSegChunkElems - 1) / kSegChunkElems);
     sa.flags |= kFlagScattered;
     mc_g = mc_out = nullptr;
   }
@@ -591,7 +597,7 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
   COCO_TRY(pick_launch(c, pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, pc.sa.count,
                        c->world, 1, &sa, &cfg));
   if (pc.opt == kLAMB && ra.nseg > 0)
-    COCO_TRY(ensure_seg_part(c, (size_t)ra.nseg, cfg.ctas, pc.stream, &ra.seg_part));
+    COCO_TRY(ensure_seg_part(c, (size_t)ra.nchunk, pc.stream, &ra.seg_part));
   CUDA_TRY(launch_fused_step(pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, sa, ra, nullptr,
                              cfg, pc.stream));
   c->launches++;
@@ -686,6 +692,7 @@ int flush_group(LocalGroup *grp) {
                                                          dtype_size(pc0.g_type));
         int rc2 = upload_segments(ck, segs, pc0.stream, &host[k].segs);
         host[k].nseg = (int)segs.size();
+        host[k].nchunk = segs.empty() ? 0 : (int)(segs.back().chunk0 + (segs.back().len + kSegChunkElems - 1) / kSegChunkElems);
         if (rc2 != cocoSuccess) {
           result = rc2;
           failed = true;
@@ -706,8 +713,8 @@ int flush_group(LocalGroup *grp) {
       bool failed = false;
       for (size_t k = 0; k < ranks.size() && !failed; ++k)
         if (host[k].nseg > 0) {
-          int rc2 = ensure_seg_part(grp->comms[ranks[k]], (size_t)host[k].nseg, cfg.ctas,
-                                    pc0.stream, &host[k].seg_part);
+          int rc2 = ensure_seg_part(grp->comms[ranks[k]], (size_t)host[k].nchunk, pc0.stream,
+                                    &host[k].seg_part);
           if (rc2 != cocoSuccess) result = rc2, failed = true;
         }
       if (failed) break;

@@ -64,7 +64,9 @@ struct Segment {
   int tensor;
   unsigned long long tensor_len;  // elements of the whole tensor
   int first_rank, last_rank;      // ranks whose slices hold a part of the tensor
+  unsigned long long chunk0;      // number of kSegChunkElems-element chunks in the pieces before this one
 };
+constexpr int kSegChunkElems = 1024;  // what one warp takes at a time from a list of tensors
 
 // Per-rank pointers of one fused call.  Indexed tables hold the view THIS
 // rank has of every peer's buffer (entry [rank] is the rank's own buffer).
@@ -81,8 +83,8 @@ struct RankArgs {
   int aligned16;              // non-zero: slice start and all pointers are 16-byte aligned
   const Segment *segs;        // scattered calls: this rank's segments (device memory)
   int nseg;
-  int pad;
-  double *seg_part;           // scattered LAMB: [segment][CTA][2] partial sums of this rank
+  int nchunk;                 // chunks of all segments together
+  double *seg_part;           // scattered LAMB: [chunk][2] partial sums of this rank's pieces
 };
 
 // Internal StepArgs::flags bit (public flags use the low byte).
