@@ -1288,8 +1288,15 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
                         : PATH == kPathSegments + 2 ? 4 : 8;
     __shared__ int s_last;
     __shared__ RankArgs s_wra[16];  // one per warp (<= 512 threads per CTA)
+    // the pieces' first-chunk numbers, for the bisection (dependent loads from
+    // global memory cost more there than the chunk's arithmetic)
+    constexpr int kChunk0InSmem = 1536;
+    __shared__ unsigned long long s_chunk0[kChunk0InSmem];
     const Segment *segs = ra.segs;
     const int nseg = ra.nseg;
+    for (int k = threadIdx.x; k < nseg && k < kChunk0InSmem; k += blockDim.x) s_chunk0[k] = segs[k].chunk0;
+    __syncthreads();
+    const bool chunk0_in_smem = nseg <= kChunk0InSmem;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int nwarp = (blockDim.x + 31) >> 5;
     const size_t gw = (size_t)blockIdx.x * nwarp + wid, GW = (size_t)gridDim.x * nwarp;
@@ -1305,7 +1312,7 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
       int a = 0, b = nseg - 1;  // the last piece whose first chunk is <= q
       while (a < b) {
         const int mid = (a + b + 1) >> 1;
-        if (segs[mid].chunk0 <= q) a = mid;
+        if ((chunk0_in_smem ? s_chunk0[mid] : segs[mid].chunk0) <= q) a = mid;
         else b = mid - 1;
       }
       if (a != cached) {
