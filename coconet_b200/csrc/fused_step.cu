@@ -1268,15 +1268,18 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
   if constexpr (PATH >= kPathSegments) {
     // Scattered call: the slice is a sequence of pieces of different tensors.
     // The pieces are cut into chunks of kSegChunkElems elements, numbered
-    // through all pieces (Segment::chunk0 = a piece's first chunk).  Every warp
-    // takes chunks q = its number, + number of warps, ...: it finds the piece
-    // by bisection over chunk0, keeps a private copy of that piece's pointers
-    // in shared memory, and runs the ordinary peer-to-peer loop on the chunk
-    // with its 32 lanes.  No CTA barrier in the walk, and the work is balanced
-    // to within one chunk per warp whatever the tensors' sizes (walking the
-    // pieces one after the other with the whole grid left every piece's last
-    // pass partly empty: +17 % over the flat call for Adam, +43 % for LAMB, on
-    // a BERT-large-shaped list).
+    // through all pieces (Segment::chunk0 = a piece's first chunk).  Every CTA
+    // takes chunks q = its number, + number of CTAs, ...: it finds the piece by
+    // bisection over a shared-memory copy of the first-chunk numbers, swaps
+    // that piece's pointers into the shared RankArgs when the piece changes,
+    // and runs the ordinary peer-to-peer loop on the chunk with all its
+    // threads (adjacent warps on adjacent memory, like the flat call).  The
+    // work is balanced to within one chunk per CTA whatever the tensors'
+    // sizes; walking the pieces one after the other with the whole grid made
+    // every piece end in a partly filled pass and a grid-wide drain (+17 %
+    // over the flat call for Adam, +43 % for LAMB, on a BERT-large-shaped list
+    // of 398 tensors), and a walk warp by warp lost the locality between the
+    // warps of a CTA.
     // SGD and Adam: one walk.  LAMB: a walk for the moments that leaves every
     // chunk's partial norms in a table, the per-tensor sums and their exchange
     // between the ranks, and a walk that applies each tensor's own trust ratio.
@@ -1287,9 +1290,7 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
     constexpr int SRB = PATH == kPathSegments ? 1 : PATH == kPathSegments + 1 ? 2
                         : PATH == kPathSegments + 2 ? 4 : 8;
     __shared__ int s_last;
-    __shared__ RankArgs s_wra[16];  // one per warp (<= 512 threads per CTA)
-    // the pieces' first-chunk numbers, for the bisection (dependent loads from
-    // global memory cost more there than the chunk's arithmetic)
+    __shared__ float s_piece_scale;
     constexpr int kChunk0InSmem = 1536;
     __shared__ unsigned long long s_chunk0[kChunk0InSmem];
     const Segment *segs = ra.segs;
@@ -1299,15 +1300,10 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
     const bool chunk0_in_smem = nseg <= kChunk0InSmem;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int nwarp = (blockDim.x + 31) >> 5;
-    const size_t gw = (size_t)blockIdx.x * nwarp + wid, GW = (size_t)gridDim.x * nwarp;
     const size_t nchunk = (size_t)ra.nchunk;
-    RankArgs &wra = s_wra[wid];
-    for (int q = lane; q < (int)(sizeof(RankArgs) / sizeof(int)); q += 32)
-      reinterpret_cast<int *>(&wra)[q] = reinterpret_cast<const int *>(&ra)[q];
-    __syncwarp();
-    int cached = -1;  // the piece whose pointers wra holds
+    int cached = -1;  // the piece whose pointers the shared RankArgs holds (the same in every thread)
 
-    // piece of chunk q, with its pointers in wra
+    // piece of chunk q (q is uniform over the CTA), with its pointers in `ra`
     auto piece_of = [&](size_t q) -> int {
       int a = 0, b = nseg - 1;  // the last piece whose first chunk is <= q
       while (a < b) {
@@ -1316,15 +1312,17 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
         else b = mid - 1;
       }
       if (a != cached) {
-        __syncwarp();  // every lane is done with the previous piece's pointers
-        if (lane < kMaxRanks) {
-          wra.g[lane] = segs[a].g[lane];
-          wra.out[lane] = segs[a].out[lane];
-        } else if (lane == kMaxRanks) {
-          wra.w = segs[a].w, wra.m = segs[a].m, wra.v = segs[a].v;
+        __syncthreads();  // everyone is done with the previous piece's pointers
+        if (threadIdx.x < kMaxRanks) {
+          ra.g[threadIdx.x] = segs[a].g[threadIdx.x];
+          ra.out[threadIdx.x] = segs[a].out[threadIdx.x];
+        }
+        if (threadIdx.x == 32) {
+          ra.w = segs[a].w, ra.m = segs[a].m, ra.v = segs[a].v;
+          ra.aligned16 = segs[a].aligned16;
         }
         cached = a;
-        __syncwarp();
+        __syncthreads();
       }
       return a;
     };
@@ -1332,24 +1330,31 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
     // ---- first walk: SGD / Adam step, or LAMB moments + the chunk's partial norms ----
     if (ok) {
 #pragma unroll 1
-      for (size_t q = gw; q < nchunk; q += GW) {
+      for (size_t q = blockIdx.x; q < nchunk; q += gridDim.x) {
         const int a = piece_of(q);
         const size_t seg_lo = segs[a].begin, seg_len = segs[a].len;
         const size_t c_lo = (q - segs[a].chunk0) * (size_t)kSegChunkElems;
         const size_t c_len = seg_len - c_lo < (size_t)kSegChunkElems ? seg_len - c_lo
                                                                      : (size_t)kSegChunkElems;
-        const size_t nv = segs[a].aligned16 ? c_len / VEC : 0;
+        const size_t nv = ra.aligned16 ? c_len / VEC : 0;
         Hyper hs = h;
         if constexpr (OPT == kLAMB) hs.quirk_n = (float)segs[a].tensor_len;
         double p_w2 = 0.0, p_r2 = 0.0;
-        direct_step<OPT, GT, LPT, SRB>(wra, sa, hs, seg_lo, seg_lo + c_lo, nv * VEC, (size_t)lane, 32,
-                                       p_w2, p_r2);
-        for (size_t j = nv * VEC + lane; j < c_len; j += 32)
-          step_unit<OPT, GT, LPT, 1, 0>(wra, sa, hs, seg_lo, seg_lo + c_lo + j, p_w2, p_r2);
-        if constexpr (OPT == kLAMB) {  // lane order, then a fixed shuffle tree: reproducible
+        direct_step<OPT, GT, LPT, SRB>(ra, sa, hs, seg_lo, seg_lo + c_lo, nv * VEC, (size_t)threadIdx.x,
+                                       (size_t)blockDim.x, p_w2, p_r2);
+        for (size_t j = nv * VEC + threadIdx.x; j < c_len; j += blockDim.x)
+          step_unit<OPT, GT, LPT, 1, 0>(ra, sa, hs, seg_lo, seg_lo + c_lo + j, p_w2, p_r2);
+        if constexpr (OPT == kLAMB) {  // thread -> warp -> CTA, fixed order: reproducible
           p_w2 = warp_sum(p_w2);
           p_r2 = warp_sum(p_r2);
-          if (lane == 0) ra.seg_part[2 * q] = p_w2, ra.seg_part[2 * q + 1] = p_r2;
+          __syncthreads();  // the previous chunk's sums have been read
+          if (lane == 0) s_red[0][wid] = p_w2, s_red[1][wid] = p_r2;
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            double x = 0.0, y = 0.0;
+            for (int k = 0; k < nwarp; ++k) x += s_red[0][k], y += s_red[1][k];
+            ra.seg_part[2 * q] = x, ra.seg_part[2 * q + 1] = y;
+          }
         }
       }
     }
@@ -1367,23 +1372,23 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
       if (s_last) {
         __threadfence();
         for (int sidx = wid; sidx < nseg; sidx += nwarp) {  // one warp per piece
-          double a = 0.0, b = 0.0;
+          double x = 0.0, y = 0.0;
           if (started_ok) {  // a rank that never started publishes zeros
             const size_t c0 = segs[sidx].chunk0;
             const size_t nc = (segs[sidx].len + kSegChunkElems - 1) / kSegChunkElems;
             for (size_t c = lane; c < nc; c += 32) {
-              a += ld_volatile_f64(ra.seg_part + 2 * (c0 + c));
-              b += ld_volatile_f64(ra.seg_part + 2 * (c0 + c) + 1);
+              x += ld_volatile_f64(ra.seg_part + 2 * (c0 + c));
+              y += ld_volatile_f64(ra.seg_part + 2 * (c0 + c) + 1);
             }
           }
-          a = warp_sum(a);
-          b = warp_sum(b);
+          x = warp_sum(x);
+          y = warp_sum(y);
           if (lane == 0) {
             const int t = segs[sidx].tensor;
             for (int p = 0; p < R; ++p) {
               volatile double *dst = tensor_norms_of(ra.flags[p])->part[rank][t];
-              dst[0] = a;
-              dst[1] = b;
+              dst[0] = x;
+              dst[1] = y;
             }
             __threadfence_system();
           }
@@ -1407,13 +1412,13 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
 
       // ---- second walk: every tensor's own trust ratio ------------------------------
       if (ok) {
-        int scaled = -1;  // the piece lr_scale belongs to
-        float lr_scale = 0.f;
+        int scaled = -1;  // the piece s_piece_scale belongs to
 #pragma unroll 1
-        for (size_t q = gw; q < nchunk; q += GW) {
+        for (size_t q = blockIdx.x; q < nchunk; q += gridDim.x) {
           const int a = piece_of(q);
           if (a != scaled) {
-            if (lane == 0) {
+            __syncthreads();  // the previous piece's scale has been read
+            if (threadIdx.x == 0) {
               // this tensor's norms: the partials of the ranks that hold a part of
               // it, in rank order, so that every replica computes the same ratio
               TensorNorms *tn = tensor_norms_of(me);
@@ -1433,19 +1438,21 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
                 wn = sqrt(w2);
                 sc = (wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0;
               }
-              lr_scale = __fmul_rn(sa.lr, (float)sc);
+              s_piece_scale = __fmul_rn(sa.lr, (float)sc);
             }
-            lr_scale = __shfl_sync(0xffffffffu, lr_scale, 0);
+            __syncthreads();
             scaled = a;
           }
+          const float lr_scale = s_piece_scale;
           const size_t seg_lo = segs[a].begin, seg_len = segs[a].len;
           const size_t c_lo = (q - segs[a].chunk0) * (size_t)kSegChunkElems;
           const size_t c_len = seg_len - c_lo < (size_t)kSegChunkElems ? seg_len - c_lo
                                                                        : (size_t)kSegChunkElems;
-          const size_t nv = segs[a].aligned16 ? c_len / VEC : 0;
-          direct_apply<GT, LPT, SRB>(wra, sa, h, seg_lo, seg_lo + c_lo, nv * VEC, (size_t)lane, 32, lr_scale);
-          for (size_t j = nv * VEC + lane; j < c_len; j += 32)
-            lamb_apply_unit<LPT, 1, 0>(wra, sa, h, seg_lo, seg_lo + c_lo + j, lr_scale);
+          const size_t nv = ra.aligned16 ? c_len / VEC : 0;
+          direct_apply<GT, LPT, SRB>(ra, sa, h, seg_lo, seg_lo + c_lo, nv * VEC, (size_t)threadIdx.x,
+                                     (size_t)blockDim.x, lr_scale);
+          for (size_t j = nv * VEC + threadIdx.x; j < c_len; j += blockDim.x)
+            lamb_apply_unit<LPT, 1, 0>(ra, sa, h, seg_lo, seg_lo + c_lo + j, lr_scale);
         }
       }
     }

@@ -66,7 +66,7 @@ struct Segment {
   int first_rank, last_rank;      // ranks whose slices hold a part of the tensor
   unsigned long long chunk0;      // number of kSegChunkElems-element chunks in the pieces before this one
 };
-constexpr int kSegChunkElems = 2048;  // what one warp takes at a time from a list of tensors
+constexpr int kSegChunkElems = 8192;  // what one CTA takes at a time from a list of tensors
 
 // Per-rank pointers of one fused call.  Indexed tables hold the view THIS
 // rank has of every peer's buffer (entry [rank] is the rank's own buffer).
