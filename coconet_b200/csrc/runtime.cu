@@ -361,11 +361,13 @@ int peer_views(cocoComm *c, const void *ptr, size_t bytes, char *views[kMaxRanks
 bool aligned16(const void *p) { return (((uintptr_t)p) & 15u) == 0; }
 
 // Which data path serves the peer-to-peer step when COCO_PIPELINE is unset:
-// the warp rings from four ranks on (measured 6 % faster than the
-// register-staged path at four GPUs, slower at two: 1.66 against 1.77 ms and
-// 1.30 against 1.17 ms for the 334 M-element mixed-precision step), the
-// register-staged path below that and for virtual ranks sharing a GPU.
-bool ring_by_default(int world, int nvirt) { return world >= 4 && nvirt <= 1; }
+// the warp rings from four ranks on for SGD and Adam (measured 6 % faster than
+// the register-staged path at four and at eight GPUs, slower at two: 1.66
+// against 1.77 ms, 1.97 against 2.09 ms and 1.30 against 1.17 ms for the
+// 334 M-element mixed-precision step), the register-staged path below that,
+// for LAMB (4.15 against 4.19 ms at eight GPUs: its second phase is the same
+// in both) and for virtual ranks sharing a GPU.
+bool ring_by_default(int opt, int world, int nvirt) { return world >= 4 && nvirt <= 1 && opt != kLAMB; }
 
 int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
                 cocoDataType_t lp_type, size_t count, int world, int nvirt, StepArgs *sa,
@@ -384,7 +386,7 @@ int pick_launch(const cocoComm *c, int opt, cocoDataType_t g_type, bool has_lp,
   const size_t stage_bytes = (size_t)world * kRingTileBytesPerRank * warps;
   const size_t tile_elems = 32 * (16 / dtype_size(g_type));
   int stages = 0;
-  const bool ring_wanted = c->pipeline > 0 || (c->pipeline < 0 && ring_by_default(world, nvirt));
+  const bool ring_wanted = c->pipeline > 0 || (c->pipeline < 0 && ring_by_default(opt, world, nvirt));
   if (ring_wanted && slice >= tile_elems && !(sa->flags & (kFlagScattered | kFlagNvls))) {
     const size_t budget_sm = (size_t)c->smem_budget_kb * 1024;
     // at large world sizes one stage of two CTAs may not fit: one CTA per SM then

@@ -323,6 +323,36 @@ def case_collectives(comm):
         print(f"ok collectives R={R}", flush=True)
 
 
+def case_probe(comm):
+    """Topology table and link yardstick across processes: every pair reachable,
+    every mode of the probe gives a positive rate and leaves no device status."""
+    R, rank = comm.world, comm.rank
+    topo = comm.topology()
+    assert topo["world"] == R
+    for a in range(R):
+        for b in range(R):
+            assert topo["access"][a][b] in (1, -1), topo      # 0 would have failed creation
+    assert topo["access"][rank][rank] == 1
+    buf = torch.zeros(1 << 24, dtype=torch.float32, device="cuda")   # 64 MiB
+    comm.register(buf)
+    rates = {m: comm.link_probe(buf, m, unroll=u, iters=2)
+             for m, u in (("copy", 1), ("pull", 1), ("push", 2), ("both", 4))}
+    assert all(v > 1.0 for v in rates.values()), rates
+    sym = comm.mem_alloc(1 << 24, torch.float32)
+    sym.zero_()
+    torch.cuda.synchronize()
+    if comm.has_multicast(sym):
+        for m in ("switch_reduce", "switch_store", "switch_both"):
+            assert comm.link_probe(sym, m, unroll=2, iters=2) > 1.0
+        assert comm.link_probe(sym, "hybrid", unroll=8, iters=2) > 0.0    # microseconds
+    assert comm.status()["code"] == 0
+    torch.cuda.synchronize()
+    comm.mem_free(sym)
+    comm.barrier()
+    if rank == 0:
+        print(f"ok probe R={R} uniform={topo['uniform']} {rates}", flush=True)
+
+
 def case_timeout(comm):
     """Rank 1 skips one fused call: the others' bounded start wait must give
     up with a status, leave the weights untouched and keep the context alive."""
@@ -359,7 +389,7 @@ if __name__ == "__main__":
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     comm = coco.Communicator.init_rank(world, rank)
     try:
-        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls, "symm": case_symm, "scattered": case_scattered, "collectives": case_collectives}[sys.argv[1]](comm)
+        {"parity": case_parity, "timeout": case_timeout, "nvls": case_nvls, "symm": case_symm, "scattered": case_scattered, "collectives": case_collectives, "probe": case_probe}[sys.argv[1]](comm)
     except Exception:  # keep this rank alive until its peers are done with its memory
         import traceback
         print("WORKER FAILURE rank %d\n%s" % (rank, traceback.format_exc()), flush=True)

@@ -528,7 +528,7 @@ def test_fused_equals_single_rank_update_on_summed_gradient_full_size():
     # precision would need ~6 GB per rank; two ranks of it fit easily): the
     # R-rank fused step equals the one-rank step on the pre-summed gradient,
     # bit for bit, because the reduction order is fixed.
-    R, n = 2, 334_000_000 // 8  # one BASELINE slice per rank
+    R, n = 2, 334_000_000 // 8  # one slice of the 334 M-element workload at eight ranks
     gen = torch.Generator(device="cuda").manual_seed(13)
     g = [(torch.randn(n, device="cuda", generator=gen) * 1e-3) for _ in range(R)]
     w0 = torch.randn(n, device="cuda", generator=gen) * 0.02

@@ -117,3 +117,10 @@ def test_stand_alone_collectives():
     r = _launch("collectives", min(_ngpu(), 8))
     assert r.returncode == 0, _why(r)
     assert "ok collectives" in r.stdout, r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs >= 2 GPUs")
+def test_topology_table_and_link_probe():
+    r = _launch("probe", min(_ngpu(), 8))
+    assert r.returncode == 0, _why(r)
+    assert "ok probe" in r.stdout, r.stdout
