@@ -456,9 +456,32 @@ def run_sweep(args, rank, world, local_rank):
         if at <= max_n:
             Ssc = coco.scattered_slice_elems(shapes, R)
             msc, vsc = torch.zeros(Ssc, device=dev), torch.zeros(Ssc, device=dev)
+            tlist = coco.TensorList(gl, wl)   # the pointer arrays, made once like a C caller's
+
+            def time_queued_ms(fn, steps):
+                # `steps` calls enqueued behind 0.7 ms of memsets, one event pair around them:
+                # the device never waits for the host, whose work per call (a few hundred
+                # tensors' pieces) would otherwise be timed too.  Every call streams 5 GB,
+                # far more than L2 holds.
+                fn(0)
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                for _ in range(8):
+                    flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(steps):
+                    fn(1 + i)
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                return float(t.item())
 
             def scattered(i):
-                comm.fused_adam_scattered(gl, wl, msc, vsc, HYPER["lr"], HYPER["beta1"],
+                comm.fused_adam_scattered(tlist, None, msc, vsc, HYPER["lr"], HYPER["beta1"],
                                           HYPER["beta2"], HYPER["eps"], i)
 
             tot_f = tot // (8 * R) * (8 * R)   # keeps every rank's flat slice 16-byte aligned
@@ -467,16 +490,16 @@ def run_sweep(args, rank, world, local_rank):
                 comm.fused_adam(g32[:tot_f], w32[:tot_f], m[:tot_f // R], v[:tot_f // R],
                                 HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"], i)
 
-            ms_sc, ms_fl = time_ms(scattered, 5, 3), time_ms(flat, 5, 3)
+            ms_sc, ms_fl = time_queued_ms(scattered, 10), time_queued_ms(flat, 10)
             out.append({"opt": "adam", "grad": "f32", "count": tot, "world": R, "tensors": len(shapes),
-                        "scattered_ms": ms_sc, "flat_ms": ms_fl})
+                        "scattered_ms": ms_sc, "flat_ms": ms_fl, "timing": "10 calls queued back to back"})
             if rank == 0:
                 print(f"# adam  f32 scattered over {len(shapes)} BERT-large-shaped tensors, {tot} elements: "
                       f"{ms_sc:.4f} ms  (flat call on as many elements: {ms_fl:.4f} ms)", flush=True)
 
             # LAMB with one trust ratio per tensor, next to the flat call (one ratio overall)
             def scattered_lamb(i):
-                comm.fused_lamb_scattered(gl, wl, msc, vsc, HYPER["lr"], HYPER["beta1"],
+                comm.fused_lamb_scattered(tlist, None, msc, vsc, HYPER["lr"], HYPER["beta1"],
                                           HYPER["beta2"], HYPER["eps"], 0.01, i)
 
             def flat_lamb(i):
@@ -484,9 +507,9 @@ def run_sweep(args, rank, world, local_rank):
                                 HYPER["lr"], HYPER["beta1"], HYPER["beta2"], HYPER["eps"],
                                 0.01, i)
 
-            ms_sc, ms_fl = time_ms(scattered_lamb, 5, 3), time_ms(flat_lamb, 5, 3)
+            ms_sc, ms_fl = time_queued_ms(scattered_lamb, 10), time_queued_ms(flat_lamb, 10)
             out.append({"opt": "lamb", "grad": "f32", "count": tot, "world": R, "tensors": len(shapes),
-                        "scattered_ms": ms_sc, "flat_ms": ms_fl})
+                        "scattered_ms": ms_sc, "flat_ms": ms_fl, "timing": "10 calls queued back to back"})
             if rank == 0:
                 print(f"# lamb  f32 scattered (per-tensor trust ratios) over {len(shapes)} tensors: "
                       f"{ms_sc:.4f} ms  (flat call on as many elements: {ms_fl:.4f} ms)", flush=True)

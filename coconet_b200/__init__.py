@@ -11,6 +11,7 @@ from .runtime import (  # noqa: F401
     CocoError,
     Communicator,
     HostBootstrap,
+    TensorList,
     VARIANT_DSL,
     VARIANT_NCCL,
     VARIANT_OVERLAP,
@@ -26,7 +27,7 @@ from .runtime import (  # noqa: F401
 )
 
 __all__ = [
-    "CocoError", "Communicator", "HostBootstrap", "VARIANT_DSL", "VARIANT_NCCL", "VARIANT_OVERLAP",
+    "CocoError", "Communicator", "HostBootstrap", "TensorList", "VARIANT_DSL", "VARIANT_NCCL", "VARIANT_OVERLAP",
     "LAMB_REF_QUIRK", "group", "lib", "library_path", "rendezvous_address", "scattered_slice_elems", "scattered_tensor_place",
     "slice_bounds", "topology_check",
 ]

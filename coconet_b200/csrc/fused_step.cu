@@ -53,6 +53,10 @@
 #ifndef COCO_LOCAL32_THREADS
 #define COCO_LOCAL32_THREADS 512
 #endif
+// Threads per CTA the kernels for lists of tensors are compiled for.
+#ifndef COCO_SEG_THREADS
+#define COCO_SEG_THREADS 512
+#endif
 // The same for the multi-rank paths (register-staged, switch, warp rings) with
 // 16-bit gradients.
 #ifndef COCO_MULTI16_THREADS
@@ -1202,7 +1206,8 @@ enum : int { kPathDirect = 0, kPathNvls = 1, kPathRing = 2, kPathLocal = 3, kPat
 template <int PATH, typename GT> struct BlockThreads {
   static constexpr int value =
       PATH == kPathLocal ? (GradTraits<GT>::kIs16 ? COCO_LOCAL16_THREADS : COCO_LOCAL32_THREADS)
-      : (PATH < kPathSegments && GradTraits<GT>::kIs16) ? COCO_MULTI16_THREADS : 512;
+      : PATH >= kPathSegments ? COCO_SEG_THREADS
+      : GradTraits<GT>::kIs16 ? COCO_MULTI16_THREADS : 512;
 };
 
 template <int OPT, typename GT, typename LPT, int PATH>
@@ -1267,100 +1272,172 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
   bool seg_norm_ok = true;  // scattered LAMB: the norm exchange completed
   if constexpr (PATH >= kPathSegments) {
     // Scattered call: the slice is a sequence of pieces of different tensors.
-    // The pieces are cut into chunks of kSegChunkElems elements, numbered
+    // The pieces are cut into chunks of 2^chunk_shift elements, numbered
     // through all pieces (Segment::chunk0 = a piece's first chunk).  Every CTA
-    // takes chunks q = its number, + number of CTAs, ...: it finds the piece by
-    // bisection over a shared-memory copy of the first-chunk numbers, swaps
-    // that piece's pointers into the shared RankArgs when the piece changes,
-    // and runs the ordinary peer-to-peer loop on the chunk with all its
-    // threads (adjacent warps on adjacent memory, like the flat call).  The
-    // work is balanced to within one chunk per CTA whatever the tensors'
-    // sizes; walking the pieces one after the other with the whole grid made
-    // every piece end in a partly filled pass and a grid-wide drain (+17 %
-    // over the flat call for Adam, +43 % for LAMB, on a BERT-large-shaped list
-    // of 398 tensors), and a walk warp by warp lost the locality between the
-    // warps of a CTA.
+    // takes chunks q = its number, + number of CTAs, ..., and runs the
+    // ordinary peer-to-peer loop on a chunk with all its threads (adjacent
+    // warps on adjacent memory, like the flat call).  The bookkeeping is per
+    // warp, so the walk has no CTA barrier: every warp finds a chunk's piece
+    // by bisection over a shared-memory copy of the first-chunk numbers and
+    // keeps the piece's pointers in its own RankArgs in shared memory.  The
+    // NEXT chunk's piece is looked up before the current chunk's data loop and,
+    // when it is another piece, its descriptor is fetched then (one 8-byte word
+    // per lane, held in a register across the loop), so that the dependent
+    // loads of the lookup overlap the data loop instead of standing between
+    // two chunks.  The work is balanced to within one chunk per CTA whatever
+    // the tensors' sizes.  (Walking the pieces one after the other with the
+    // whole grid made every piece end in a partly filled pass and a grid-wide
+    // drain: +17 % over the flat call for Adam, +43 % for LAMB, on a
+    // BERT-large-shaped list of 398 tensors; a walk with the lookup between the
+    // chunks: +17 to +26 % and +32 %.)
     // SGD and Adam: one walk.  LAMB: a walk for the moments that leaves every
-    // chunk's partial norms in a table, the per-tensor sums and their exchange
-    // between the ranks, and a walk that applies each tensor's own trust ratio.
+    // chunk's partial norms (one pair per warp) in a table, the per-tensor sums
+    // and their exchange between the ranks, and a walk that applies each
+    // tensor's own trust ratio.
     //
     // SRB: the world-size bucket this kernel was built for (1, 2, <= 4, <= 8).
     // A kernel per bucket, because one kernel holding the loops of all four
     // spilled 400-550 bytes per thread against 16 and ran 8 % slower.
     constexpr int SRB = PATH == kPathSegments ? 1 : PATH == kPathSegments + 1 ? 2
                         : PATH == kPathSegments + 2 ? 4 : 8;
+    // a piece as a warp holds it: the pointers inside a RankArgs (what the unit
+    // functions take), the rest of the Segment's words behind it
+    struct WarpPiece {
+      RankArgs ra;
+      unsigned long long meta[kSegWords - kSegPointerWords];
+    };
+    enum { kMBegin = 0, kMLen, kMAlignedTensor, kMTensorLen, kMRanks, kMChunk0 };
+    static_assert(offsetof(Segment, len) == (kSegPointerWords + kMLen) * 8 &&
+                      offsetof(Segment, aligned16) == (kSegPointerWords + kMAlignedTensor) * 8 &&
+                      offsetof(Segment, tensor_len) == (kSegPointerWords + kMTensorLen) * 8 &&
+                      offsetof(Segment, first_rank) == (kSegPointerWords + kMRanks) * 8 &&
+                      offsetof(Segment, chunk0) == (kSegPointerWords + kMChunk0) * 8,
+                  "WarpPiece::meta follows the Segment's words");
     __shared__ int s_last;
-    __shared__ float s_piece_scale;
+    __shared__ WarpPiece s_wp[kSegPartPerChunk][2];  // per warp, two so that the next piece can be installed early
     constexpr int kChunk0InSmem = 1536;
     __shared__ unsigned long long s_chunk0[kChunk0InSmem];
+    __shared__ float s_scale[OPT == kLAMB ? kChunk0InSmem : 1];  // lr x trust ratio per piece
     const Segment *segs = ra.segs;
     const int nseg = ra.nseg;
     for (int k = threadIdx.x; k < nseg && k < kChunk0InSmem; k += blockDim.x) s_chunk0[k] = segs[k].chunk0;
-    __syncthreads();
     const bool chunk0_in_smem = nseg <= kChunk0InSmem;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int nwarp = (blockDim.x + 31) >> 5;
     const size_t nchunk = (size_t)ra.nchunk;
-    int cached = -1;  // the piece whose pointers the shared RankArgs holds (the same in every thread)
+    const int chunk_shift = ra.chunk_shift;
+    const size_t chunk_elems = (size_t)1 << chunk_shift;
+    // scattered LAMB: seg_part holds a pair of partial sums per chunk, and behind them a pair
+    // per chunk and warp
+    double *const warp_part = ra.seg_part + 2 * nchunk;
+    for (int k = lane; k < (int)(sizeof(RankArgs) / sizeof(int)); k += 32) {
+      const int x = reinterpret_cast<const int *>(&ra)[k];
+      reinterpret_cast<int *>(&s_wp[wid][0].ra)[k] = x;
+      reinterpret_cast<int *>(&s_wp[wid][1].ra)[k] = x;
+    }
+    __syncthreads();
 
-    // piece of chunk q (q is uniform over the CTA), with its pointers in `ra`
-    auto piece_of = [&](size_t q) -> int {
-      int a = 0, b = nseg - 1;  // the last piece whose first chunk is <= q
+    // the last piece whose first chunk is <= q
+    auto find_piece = [&](size_t q) -> int {
+      int a = 0, b = nseg - 1;
       while (a < b) {
         const int mid = (a + b + 1) >> 1;
         if ((chunk0_in_smem ? s_chunk0[mid] : segs[mid].chunk0) <= q) a = mid;
         else b = mid - 1;
       }
-      if (a != cached) {
-        __syncthreads();  // everyone is done with the previous piece's pointers
-        if (threadIdx.x < kMaxRanks) {
-          ra.g[threadIdx.x] = segs[a].g[threadIdx.x];
-          ra.out[threadIdx.x] = segs[a].out[threadIdx.x];
-        }
-        if (threadIdx.x == 32) {
-          ra.w = segs[a].w, ra.m = segs[a].m, ra.v = segs[a].v;
-          ra.aligned16 = segs[a].aligned16;
-        }
-        cached = a;
-        __syncthreads();
-      }
       return a;
+    };
+    // this lane's word of piece a's descriptor (the descriptors do not change during the kernel)
+    auto fetch_word = [&](int a) -> unsigned long long {
+      unsigned long long x = 0;
+      if (lane < kSegWords) {
+        const unsigned long long *src = reinterpret_cast<const unsigned long long *>(segs + a) + lane;
+        asm volatile("ld.global.nc.u64 %0, [%1];" : "=l"(x) : "l"(src));
+      }
+      return x;
+    };
+    auto install = [&](WarpPiece &wp, unsigned long long word) {
+      if (lane < kSegPointerWords) {
+        reinterpret_cast<unsigned long long *>(&wp.ra)[lane] = word;
+      } else if (lane < kSegWords) {
+        wp.meta[lane - kSegPointerWords] = word;
+        if (lane == kSegPointerWords + kMAlignedTensor) wp.ra.aligned16 = (int)(unsigned)word;
+      }
+      __syncwarp();
+    };
+    // body(piece as this warp holds it, chunk, piece number) for every chunk of this CTA
+    auto walk = [&](auto &&body) {
+      size_t q = blockIdx.x;
+      if (q >= nchunk) return;
+      int slot = 0;
+      int a = find_piece(q);
+      install(s_wp[wid][0], fetch_word(a));
+#pragma unroll 1
+      for (; q < nchunk; q += gridDim.x) {
+        const size_t qn = q + gridDim.x;
+        int an = a;
+        unsigned long long next_word = 0;
+        if (qn < nchunk) {
+          an = find_piece(qn);
+          if (an != a) next_word = fetch_word(an);
+        }
+        body(s_wp[wid][slot], q, a);
+        if (an != a) {
+          __syncwarp();  // every lane is done with what the other slot held
+          slot ^= 1;
+          install(s_wp[wid][slot], next_word);
+          a = an;
+        }
+      }
+    };
+    // a chunk's place in its piece
+    auto chunk_span = [&](const WarpPiece &wp, size_t q, size_t &seg_lo, size_t &c_lo, size_t &c_len) {
+      seg_lo = (size_t)wp.meta[kMBegin];
+      c_lo = (q - (size_t)wp.meta[kMChunk0]) << chunk_shift;
+      const size_t rest = (size_t)wp.meta[kMLen] - c_lo;
+      c_len = rest < chunk_elems ? rest : chunk_elems;
     };
 
     // ---- first walk: SGD / Adam step, or LAMB moments + the chunk's partial norms ----
     if (ok) {
-#pragma unroll 1
-      for (size_t q = blockIdx.x; q < nchunk; q += gridDim.x) {
-        const int a = piece_of(q);
-        const size_t seg_lo = segs[a].begin, seg_len = segs[a].len;
-        const size_t c_lo = (q - segs[a].chunk0) * (size_t)kSegChunkElems;
-        const size_t c_len = seg_len - c_lo < (size_t)kSegChunkElems ? seg_len - c_lo
-                                                                     : (size_t)kSegChunkElems;
-        const size_t nv = ra.aligned16 ? c_len / VEC : 0;
+      walk([&](WarpPiece &wp, size_t q, int) {
+        size_t seg_lo, c_lo, c_len;
+        chunk_span(wp, q, seg_lo, c_lo, c_len);
+        const size_t nv = wp.ra.aligned16 ? c_len / VEC : 0;
         Hyper hs = h;
-        if constexpr (OPT == kLAMB) hs.quirk_n = (float)segs[a].tensor_len;
+        if constexpr (OPT == kLAMB) hs.quirk_n = (float)wp.meta[kMTensorLen];
         double p_w2 = 0.0, p_r2 = 0.0;
-        direct_step<OPT, GT, LPT, SRB>(ra, sa, hs, seg_lo, seg_lo + c_lo, nv * VEC, (size_t)threadIdx.x,
-                                       (size_t)blockDim.x, p_w2, p_r2);
+        direct_step<OPT, GT, LPT, SRB>(wp.ra, sa, hs, seg_lo, seg_lo + c_lo, nv * VEC,
+                                       (size_t)threadIdx.x, (size_t)blockDim.x, p_w2, p_r2);
         for (size_t j = nv * VEC + threadIdx.x; j < c_len; j += blockDim.x)
-          step_unit<OPT, GT, LPT, 1, 0>(ra, sa, hs, seg_lo, seg_lo + c_lo + j, p_w2, p_r2);
-        if constexpr (OPT == kLAMB) {  // thread -> warp -> CTA, fixed order: reproducible
+          step_unit<OPT, GT, LPT, 1, 0>(wp.ra, sa, hs, seg_lo, seg_lo + c_lo + j, p_w2, p_r2);
+        if constexpr (OPT == kLAMB) {  // lane order, then a fixed shuffle tree: reproducible
           p_w2 = warp_sum(p_w2);
           p_r2 = warp_sum(p_r2);
-          __syncthreads();  // the previous chunk's sums have been read
-          if (lane == 0) s_red[0][wid] = p_w2, s_red[1][wid] = p_r2;
-          __syncthreads();
-          if (threadIdx.x == 0) {
-            double x = 0.0, y = 0.0;
-            for (int k = 0; k < nwarp; ++k) x += s_red[0][k], y += s_red[1][k];
-            ra.seg_part[2 * q] = x, ra.seg_part[2 * q + 1] = y;
+          if (lane == 0) {
+            double *dst = warp_part + 2 * (q * (size_t)nwarp + wid);
+            dst[0] = p_w2, dst[1] = p_r2;
           }
         }
-      }
+      });
     }
 
     if constexpr (OPT == kLAMB) {
-      // ---- per-tensor norms: chunk partials -> rank (last CTA, fixed order) -> peers
+      // ---- per-tensor norms: warp partials -> chunk (the CTA that walked it) -> rank
+      // (last CTA) -> peers, every sum in a fixed order
+      __syncthreads();
+      if (started_ok) {
+        for (size_t q = blockIdx.x + (size_t)threadIdx.x * gridDim.x; q < nchunk;
+             q += (size_t)blockDim.x * gridDim.x) {
+          const double2 *src = reinterpret_cast<const double2 *>(warp_part) + q * (size_t)nwarp;
+          double x = 0.0, y = 0.0;
+          for (int k = 0; k < nwarp; ++k) {
+            const double2 pr = __ldcg(src + k);
+            x += pr.x, y += pr.y;
+          }
+          reinterpret_cast<double2 *>(ra.seg_part)[q] = make_double2(x, y);
+        }
+      }
       __syncthreads();
       if (threadIdx.x == 0) {
         __threadfence();  // this CTA's partial sums before the count
@@ -1371,27 +1448,60 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
       __syncthreads();
       if (s_last) {
         __threadfence();
-        for (int sidx = wid; sidx < nseg; sidx += nwarp) {  // one warp per piece
+        // A piece's chunks are summed in chunk order by one thread when they are few
+        // (most tensors of a model are biases and norms of a chunk or two), by a warp
+        // otherwise: in both cases an order that depends on the piece alone.  The stores
+        // to the peers are ordered before the flag by the barrier and the one system
+        // fence of the releasing threads below (a fence per piece cost ~10 us each).
+        constexpr size_t kFewChunks = 32;
+        auto first_chunk = [&](int k) -> size_t {
+          if (k >= nseg) return nchunk;
+          return (size_t)(chunk0_in_smem ? s_chunk0[k] : segs[k].chunk0);
+        };
+        auto publish = [&](int sidx, double x, double y) {
+          const int t = segs[sidx].tensor;
+          for (int p = 0; p < R; ++p) {
+            volatile double *dst = tensor_norms_of(ra.flags[p])->part[rank][t];
+            dst[0] = x;
+            dst[1] = y;
+          }
+        };
+        const double2 *part = reinterpret_cast<const double2 *>(ra.seg_part);
+        for (int sidx = threadIdx.x; sidx < nseg; sidx += blockDim.x) {  // a thread per small piece
+          const size_t c0 = first_chunk(sidx), nc = first_chunk(sidx + 1) - c0;
+          if (nc > kFewChunks) continue;
           double x = 0.0, y = 0.0;
           if (started_ok) {  // a rank that never started publishes zeros
-            const size_t c0 = segs[sidx].chunk0;
-            const size_t nc = (segs[sidx].len + kSegChunkElems - 1) / kSegChunkElems;
-            for (size_t c = lane; c < nc; c += 32) {
-              x += ld_volatile_f64(ra.seg_part + 2 * (c0 + c));
-              y += ld_volatile_f64(ra.seg_part + 2 * (c0 + c) + 1);
+            for (size_t c = 0; c < nc; ++c) {
+              const double2 pr = __ldcg(part + c0 + c);
+              x += pr.x, y += pr.y;
+            }
+          }
+          publish(sidx, x, y);
+        }
+        for (int sidx = wid; sidx < nseg; sidx += nwarp) {  // a warp per large piece
+          const size_t c0 = first_chunk(sidx), nc = first_chunk(sidx + 1) - c0;
+          if (nc <= kFewChunks) continue;
+          double x = 0.0, y = 0.0;
+          if (started_ok) {
+            const double2 *src = part + c0;
+            size_t c = lane;
+            for (; c + 96 < nc; c += 128) {  // four loads in flight per lane
+              const double2 p0 = __ldcg(src + c), p1 = __ldcg(src + c + 32), p2 = __ldcg(src + c + 64),
+                            p3 = __ldcg(src + c + 96);
+              x += p0.x, y += p0.y;
+              x += p1.x, y += p1.y;
+              x += p2.x, y += p2.y;
+              x += p3.x, y += p3.y;
+            }
+            for (; c < nc; c += 32) {
+              const double2 pr = __ldcg(src + c);
+              x += pr.x, y += pr.y;
             }
           }
           x = warp_sum(x);
           y = warp_sum(y);
-          if (lane == 0) {
-            const int t = segs[sidx].tensor;
-            for (int p = 0; p < R; ++p) {
-              volatile double *dst = tensor_norms_of(ra.flags[p])->part[rank][t];
-              dst[0] = x;
-              dst[1] = y;
-            }
-            __threadfence_system();
-          }
+          if (lane == 0) publish(sidx, x, y);
         }
         __syncthreads();
         if ((int)threadIdx.x < R) {
@@ -1412,48 +1522,52 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
 
       // ---- second walk: every tensor's own trust ratio ------------------------------
       if (ok) {
-        int scaled = -1;  // the piece s_piece_scale belongs to
-#pragma unroll 1
-        for (size_t q = blockIdx.x; q < nchunk; q += gridDim.x) {
-          const int a = piece_of(q);
+        // lr x trust ratio of piece a's tensor: the partials of the ranks that hold a
+        // part of it, in rank order, so that every replica computes the same ratio
+        auto piece_scale = [&](int a) -> float {
+          TensorNorms *tn = tensor_norms_of(me);
+          const int t = segs[a].tensor;
+          double w2 = 0.0, r2 = 0.0;
+          for (int p = segs[a].first_rank; p <= segs[a].last_rank; ++p) {
+            w2 += ld_volatile_f64(&tn->part[p][t][0]);
+            r2 += ld_volatile_f64(&tn->part[p][t][1]);
+          }
+          double wn, rn, sc;
+          if (sa.flags & COCO_LAMB_REF_QUIRK) {  // sample :424-433, per buffer
+            rn = sqrt(r2);
+            wn = sqrt(w2 / (double)segs[a].tensor_len);
+            sc = ((wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0) / rn;
+          } else {
+            rn = sqrt(r2);
+            wn = sqrt(w2);
+            sc = (wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0;
+          }
+          return __fmul_rn(sa.lr, (float)sc);
+        };
+        // all pieces' scales at once, a thread per piece (a stride of the walk is longer
+        // than most tensors, so nearly every chunk enters another piece)
+        for (int k = threadIdx.x; k < nseg && k < kChunk0InSmem; k += blockDim.x) s_scale[k] = piece_scale(k);
+        __syncthreads();
+        int scaled = -1;  // the piece lr_scale belongs to
+        float lr_scale = 0.f;
+        walk([&](WarpPiece &wp, size_t q, int a) {
           if (a != scaled) {
-            __syncthreads();  // the previous piece's scale has been read
-            if (threadIdx.x == 0) {
-              // this tensor's norms: the partials of the ranks that hold a part of
-              // it, in rank order, so that every replica computes the same ratio
-              TensorNorms *tn = tensor_norms_of(me);
-              const int t = segs[a].tensor;
-              double w2 = 0.0, r2 = 0.0;
-              for (int p = segs[a].first_rank; p <= segs[a].last_rank; ++p) {
-                w2 += ld_volatile_f64(&tn->part[p][t][0]);
-                r2 += ld_volatile_f64(&tn->part[p][t][1]);
-              }
-              double wn, rn, sc;
-              if (sa.flags & COCO_LAMB_REF_QUIRK) {  // sample :424-433, per buffer
-                rn = sqrt(r2);
-                wn = sqrt(w2 / (double)segs[a].tensor_len);
-                sc = ((wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0) / rn;
-              } else {
-                rn = sqrt(r2);
-                wn = sqrt(w2);
-                sc = (wn > 0) ? (rn > 0 ? wn / rn : 1.0) : 1.0;
-              }
-              s_piece_scale = __fmul_rn(sa.lr, (float)sc);
+            if (a < kChunk0InSmem) {
+              lr_scale = s_scale[a];
+            } else {
+              if (lane == 0) lr_scale = piece_scale(a);
+              lr_scale = __shfl_sync(0xffffffffu, lr_scale, 0);
             }
-            __syncthreads();
             scaled = a;
           }
-          const float lr_scale = s_piece_scale;
-          const size_t seg_lo = segs[a].begin, seg_len = segs[a].len;
-          const size_t c_lo = (q - segs[a].chunk0) * (size_t)kSegChunkElems;
-          const size_t c_len = seg_len - c_lo < (size_t)kSegChunkElems ? seg_len - c_lo
-                                                                       : (size_t)kSegChunkElems;
-          const size_t nv = ra.aligned16 ? c_len / VEC : 0;
-          direct_apply<GT, LPT, SRB>(ra, sa, h, seg_lo, seg_lo + c_lo, nv * VEC, (size_t)threadIdx.x,
+          size_t seg_lo, c_lo, c_len;
+          chunk_span(wp, q, seg_lo, c_lo, c_len);
+          const size_t nv = wp.ra.aligned16 ? c_len / VEC : 0;
+          direct_apply<GT, LPT, SRB>(wp.ra, sa, h, seg_lo, seg_lo + c_lo, nv * VEC, (size_t)threadIdx.x,
                                      (size_t)blockDim.x, lr_scale);
           for (size_t j = nv * VEC + threadIdx.x; j < c_len; j += blockDim.x)
-            lamb_apply_unit<LPT, 1, 0>(ra, sa, h, seg_lo, seg_lo + c_lo + j, lr_scale);
-        }
+            lamb_apply_unit<LPT, 1, 0>(wp.ra, sa, h, seg_lo, seg_lo + c_lo + j, lr_scale);
+        });
       }
     }
     seg_norm_ok = ok;
@@ -1730,7 +1844,8 @@ int fused_step_path(const StepArgs &sa) {
 int fused_step_block_threads(int path, cocoDataType_t g_type) {
   const bool is16 = g_type != cocoFloat32;
   if (path == kPathLocal) return is16 ? COCO_LOCAL16_THREADS : COCO_LOCAL32_THREADS;
-  return (path < kPathSegments && is16) ? COCO_MULTI16_THREADS : 512;
+  if (path >= kPathSegments) return COCO_SEG_THREADS;
+  return is16 ? COCO_MULTI16_THREADS : 512;
 }
 
 namespace {

@@ -195,6 +195,7 @@ struct cocoComm {
   int smem_budget_kb = 200;  // shared memory the warp rings may use per SM
   int pipeline = -1;         // COCO_PIPELINE: 1 warp rings (bulk copies), 0 register-staged, unset: by world size
   int ring_stages = 0;       // COCO_RING_STAGES: cap on the stages of a ring, 0 = as many as fit
+  int seg_chunk_shift = 0;   // COCO_SEG_CHUNK_SHIFT: log2 of the chunk of a list walk, 0 = by size
   int algo = 2;              // 0 p2p, 1 nvls, 2 auto (COCO_ALGO=p2p|nvls|auto)
   cocoTopology_t topo = {};  // peer access / performance between the ranks' GPUs
 };
@@ -232,6 +233,7 @@ int init_common(cocoComm *c) {
   if (c->threads < 32 || c->threads > 512 || (c->threads % 32) != 0) c->threads = 512;
   c->pipeline = env_int("COCO_PIPELINE", -1);
   c->ring_stages = env_int("COCO_RING_STAGES", 0);
+  c->seg_chunk_shift = env_int("COCO_SEG_CHUNK_SHIFT", 0);
   {
     const char *algo = getenv("COCO_ALGO");
     c->algo = !algo ? 2 : !strcmp(algo, "nvls") ? 1 : !strcmp(algo, "p2p") ? 0 : 2;
@@ -468,13 +470,29 @@ void fill_rank_args(RankArgs *ra, int rank, int world, char *const g_views[], ch
   ra->aligned16 = (ok16 && (lo % vec) == 0) ? 1 : 0;
 }
 
+// log2 of the chunk size for a walk over `slice_elems` elements by `ctas` CTAs.
+int seg_chunk_shift(const cocoComm *c, size_t slice_elems, long ctas) {
+  if (c->seg_chunk_shift > 0)
+    return std::min(kSegChunkShiftMax, std::max(kSegChunkShiftMin, c->seg_chunk_shift));
+  int shift = kSegChunkShiftMax;
+  while (shift > kSegChunkShiftMin &&
+         (slice_elems >> shift) < (size_t)std::max(1L, ctas) * kSegChunksPerCta)
+    --shift;
+  return shift;
+}
+
+int seg_chunk_count(const std::vector<Segment> &segs, int chunk_shift) {
+  if (segs.empty()) return 0;
+  return (int)(segs.back().chunk0 + ((segs.back().len + ((1ull << chunk_shift) - 1)) >> chunk_shift));
+}
+
 // This rank's pieces of a list of tensors.  views_g[b][p] / views_w[b][p]: rank
 // p's copy of tensor b as this rank addresses it.
 std::vector<Segment> build_segments(int rank, int world, const FlatLayout &L,
                                     const std::vector<size_t> &counts,
                                     const std::vector<std::vector<char *>> &views_g,
                                     const std::vector<std::vector<char *>> &views_w, float *m,
-                                    float *v, size_t gsize) {
+                                    float *v, size_t gsize, int chunk_shift) {
   std::vector<Segment> out;
   const size_t lo = std::min(L.total, (size_t)rank * L.slice);
   const size_t hi = std::min(L.total, lo + L.slice);
@@ -508,7 +526,7 @@ std::vector<Segment> build_segments(int rank, int world, const FlatLayout &L,
   unsigned long long chunks = 0;  // chunk numbering through all pieces
   for (Segment &sg : out) {
     sg.chunk0 = chunks;
-    chunks += (sg.len + kSegChunkElems - 1) / kSegChunkElems;
+    chunks += (sg.len + ((1ull << chunk_shift) - 1)) >> chunk_shift;
   }
   return out;
 }
@@ -540,10 +558,10 @@ int upload_segments(cocoComm *c, const std::vector<Segment> &segs, cudaStream_t 
   return cocoSuccess;
 }
 
-// Scattered LAMB: room for one partial-sum pair per chunk of this rank's pieces.
-// Nothing is cleared: a step reads only the entries it wrote.
+// Scattered LAMB: room for one partial-sum pair per chunk of this rank's pieces,
+// and behind them one per chunk and warp of a CTA.  Nothing is cleared: a step reads only the entries it wrote.
 int ensure_seg_part(cocoComm *c, size_t nchunk, cudaStream_t stream, double **dev) {
-  const size_t need = std::max<size_t>(1, nchunk) * 2;
+  const size_t need = std::max<size_t>(1, nchunk) * (1 + kSegPartPerChunk) * 2;
   if (need > c->seg_part_cap) {
     CUDA_TRY(cudaStreamSynchronize(stream));
     if (c->seg_part) CUDA_TRY(cudaFree(c->seg_part));
@@ -574,11 +592,12 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
       COCO_TRY(peer_views(c, pc.sg[b], pc.scounts[b] * dtype_size(pc.g_type), vg[b].data(), &mc));
       COCO_TRY(peer_views(c, pc.sw[b], pc.scounts[b] * sizeof(float), vw[b].data(), &mc));
     }
+    ra.chunk_shift = seg_chunk_shift(c, L.slice, 2L * c->sm_count);
     const std::vector<Segment> segs = build_segments(c->rank, c->world, L, pc.scounts, vg, vw, pc.m,
-                                                     pc.v, dtype_size(pc.g_type));
+                                                     pc.v, dtype_size(pc.g_type), ra.chunk_shift);
     COCO_TRY(upload_segments(c, segs, pc.stream, &ra.segs));
     ra.nseg = (int)segs.size();
-    ra.nchunk = segs.empty() ? 0 : (int)(segs.back().chunk0 + (segs.back().len + kSegChunkElems - 1) / kSegChunkElems);
+    ra.nchunk = seg_chunk_count(segs, ra.chunk_shift);
     sa.flags |= kFlagScattered;
     mc_g = mc_out = nullptr;
   }
@@ -689,12 +708,14 @@ int flush_group(LocalGroup *grp) {
       bool failed = false;
       for (size_t k = 0; k < ranks.size() && !failed; ++k) {
         cocoComm *ck = grp->comms[ranks[k]];
+        // virtual ranks share the device's CTAs
+        host[k].chunk_shift = seg_chunk_shift(ck, L.slice, 2L * ck->sm_count / (long)ranks.size());
         const std::vector<Segment> segs = build_segments(ranks[k], R, L, pc0.scounts, vg, vw,
                                                          ck->pending.m, ck->pending.v,
-                                                         dtype_size(pc0.g_type));
+                                                         dtype_size(pc0.g_type), host[k].chunk_shift);
         int rc2 = upload_segments(ck, segs, pc0.stream, &host[k].segs);
         host[k].nseg = (int)segs.size();
-        host[k].nchunk = segs.empty() ? 0 : (int)(segs.back().chunk0 + (segs.back().len + kSegChunkElems - 1) / kSegChunkElems);
+        host[k].nchunk = seg_chunk_count(segs, host[k].chunk_shift);
         if (rc2 != cocoSuccess) {
           result = rc2;
           failed = true;

@@ -243,6 +243,27 @@ class HostBootstrap:
             self._h = None
 
 
+class TensorList:
+    """The pointer and size arrays of a list of (gradient, weight) tensors, made
+    once: what a C caller of the `...Scattered` entry points builds before its
+    training loop.  Pass it as `gs` (with `ws=None`) to the `fused_*_scattered`
+    methods; converting a few hundred tensors on every call costs more host
+    time than the step takes on the device."""
+
+    def __init__(self, gs, ws):
+        assert len(gs) == len(ws) and len(gs) > 0
+        self.tensors = (list(gs), list(ws))   # keeps the memory alive
+        self.n = len(gs)
+        self.g = (C.c_void_p * self.n)(*[t.data_ptr() for t in gs])
+        self.w = (C.c_void_p * self.n)(*[t.data_ptr() for t in ws])
+        self.counts = (C.c_size_t * self.n)(*[t.numel() for t in ws])
+        self.dtype = _dtype_code(gs[0])
+
+
+def _list_dtype(gs):
+    return gs.dtype if isinstance(gs, TensorList) else _dtype_code(gs[0])
+
+
 class Communicator:
     """One rank of a fused-step communicator (wraps cocoComm_t)."""
 
@@ -377,6 +398,8 @@ class Communicator:
     # ---- lists of tensors ----
     @staticmethod
     def _lists(gs, ws):
+        if isinstance(gs, TensorList):
+            return gs.n, gs.g, gs.w, gs.counts
         n = len(gs)
         ga = (C.c_void_p * n)(*[t.data_ptr() for t in gs])
         wa = (C.c_void_p * n)(*[t.data_ptr() for t in ws])
@@ -385,13 +408,13 @@ class Communicator:
 
     def fused_sgd_scattered(self, gs, ws, lr, grad_scale=1.0, stream=None):
         n, ga, wa, ca = self._lists(gs, ws)
-        _check(lib().cocoFusedSGDScattered(self._h, n, ga, _dtype_code(gs[0]), wa, ca, lr,
+        _check(lib().cocoFusedSGDScattered(self._h, n, ga, _list_dtype(gs), wa, ca, lr,
                                            grad_scale, _stream(stream)), "cocoFusedSGDScattered")
 
     def fused_adam_scattered(self, gs, ws, m, v, lr, beta1, beta2, eps, step, grad_scale=1.0,
                              variant=VARIANT_OVERLAP, stream=None):
         n, ga, wa, ca = self._lists(gs, ws)
-        _check(lib().cocoFusedAdamScattered(self._h, n, ga, _dtype_code(gs[0]), wa, ca, _ptr(m),
+        _check(lib().cocoFusedAdamScattered(self._h, n, ga, _list_dtype(gs), wa, ca, _ptr(m),
                                             _ptr(v), lr, beta1, beta2, eps, step, grad_scale,
                                             variant, _stream(stream)), "cocoFusedAdamScattered")
 
@@ -399,7 +422,7 @@ class Communicator:
                              grad_scale=1.0, variant=VARIANT_OVERLAP, flags=0, stream=None):
         """LAMB over a list of tensors with one trust ratio PER TENSOR."""
         n, ga, wa, ca = self._lists(gs, ws)
-        _check(lib().cocoFusedLAMBScattered(self._h, n, ga, _dtype_code(gs[0]), wa, ca, _ptr(m),
+        _check(lib().cocoFusedLAMBScattered(self._h, n, ga, _list_dtype(gs), wa, ca, _ptr(m),
                                             _ptr(v), lr, beta1, beta2, eps, weight_decay, step,
                                             grad_scale, variant, flags, _stream(stream)),
                "cocoFusedLAMBScattered")

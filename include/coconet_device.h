@@ -5,6 +5,7 @@
 #define COCONET_DEVICE_H_
 
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 #include "coconet_rt.h"
@@ -64,19 +65,30 @@ struct Segment {
   int tensor;
   unsigned long long tensor_len;  // elements of the whole tensor
   int first_rank, last_rank;      // ranks whose slices hold a part of the tensor
-  unsigned long long chunk0;      // number of kSegChunkElems-element chunks in the pieces before this one
+  unsigned long long chunk0;      // number of chunks in the pieces before this one
 };
-constexpr int kSegChunkElems = 8192;  // what one CTA takes at a time from a list of tensors
+// A list of tensors is walked in chunks of 2^RankArgs::chunk_shift elements, one CTA per
+// chunk at a time.  The host picks the size per call: large enough that the lookup between
+// two chunks is rare (64 Ki elements: 32 passes of a 512-thread CTA), small enough that
+// every CTA gets at least kSegChunksPerCta of them, so that the last, partly filled round
+// of the walk stays a few percent of the step.
+constexpr int kSegChunkShiftMin = 13, kSegChunkShiftMax = 16;
+constexpr int kSegChunksPerCta = 16;
+constexpr int kSegWords = 25;         // a Segment is this many 8-byte words
+constexpr int kSegPointerWords = 2 * kMaxRanks + 3;  // g, out, w, m, v: the words a RankArgs starts with too
+constexpr int kSegPartPerChunk = 16;  // scattered LAMB: partial sums kept per chunk (one per warp of a CTA)
 
 // Per-rank pointers of one fused call.  Indexed tables hold the view THIS
 // rank has of every peer's buffer (entry [rank] is the rank's own buffer).
+// The first kSegPointerWords words are laid out like a Segment's, so that a
+// piece of a list of tensors is entered by copying those words.
 struct RankArgs {
   const void *g[kMaxRanks];   // gradients of each peer, element 0
   void *out[kMaxRanks];       // gathered output of each peer (fp32 w, or w_lp), element 0
-  FlagPage *flags[kMaxRanks]; // flag page of each peer
   float *w;                   // own fp32 weights, element 0 (N elements)
   float *m;                   // own first moment, slice-local (S elements)
   float *v;                   // own second moment, slice-local
+  FlagPage *flags[kMaxRanks]; // flag page of each peer
   const void *mc_g;           // NVLS multicast address of the gradient buffers, or null
   void *mc_out;               // NVLS multicast address of the gathered output, or null
   int rank;
@@ -84,8 +96,16 @@ struct RankArgs {
   const Segment *segs;        // scattered calls: this rank's segments (device memory)
   int nseg;
   int nchunk;                 // chunks of all segments together
-  double *seg_part;           // scattered LAMB: [chunk][2] partial sums of this rank's pieces
+  int chunk_shift;            // log2 of the elements per chunk
+  int pad_;
+  double *seg_part;           // scattered LAMB: [chunk][2] partial sums of this rank's pieces, then [chunk][warp][2]
 };
+static_assert(sizeof(Segment) == kSegWords * 8, "Segment is walked as 8-byte words");
+static_assert(offsetof(Segment, g) == offsetof(RankArgs, g) && offsetof(Segment, out) == offsetof(RankArgs, out) &&
+                  offsetof(Segment, w) == offsetof(RankArgs, w) && offsetof(Segment, m) == offsetof(RankArgs, m) &&
+                  offsetof(Segment, v) == offsetof(RankArgs, v) &&
+                  offsetof(Segment, begin) == kSegPointerWords * 8,
+              "a Segment's pointers and a RankArgs' pointers share one layout");
 
 // Internal StepArgs::flags bit (public flags use the low byte).
 constexpr unsigned kFlagNvls = 0x100u;  // reduce / gather through NVSwitch multicast

@@ -26,9 +26,15 @@ def _layout(counts, R):
     return off, at, S
 
 
-@pytest.mark.parametrize("R", [1, 2, 3, 8])
+@pytest.mark.parametrize("R,chunk_shift,as_list", [(1, 0, False), (2, 0, True), (3, 0, False), (8, 0, False),
+                                                  (1, 16, True), (3, 14, False)])
 @pytest.mark.parametrize("opt", ["sgd", "adam"])
-def test_scattered_matches_per_tensor_oracle(R, opt):
+def test_scattered_matches_per_tensor_oracle(R, opt, chunk_shift, as_list, monkeypatch):
+    # chunk_shift: the walk's chunk size (0 = chosen by size: 8 Ki elements here, so the
+    # half-million-element tensor is 65 chunks spread over the CTAs); as_list: the
+    # pointer arrays made once (TensorList) instead of on every call
+    if chunk_shift:
+        monkeypatch.setenv("COCO_SEG_CHUNK_SHIFT", str(chunk_shift))
     counts = SIZES
     off, total, S = _layout(counts, R)
     assert coco.scattered_slice_elems(counts, R) == S
@@ -45,13 +51,20 @@ def test_scattered_matches_per_tensor_oracle(R, opt):
         for step in range(3):
             grads = [[K.make_grads(R, c, 600 + b, step)[r] for b, c in enumerate(counts)]
                      for r in range(R)]
-            g = [[torch.from_numpy(x).cuda() for x in grads[r]] for r in range(R)]
+            if step == 0 or not as_list:
+                g = [[torch.from_numpy(x).cuda() for x in grads[r]] for r in range(R)]
+                lists = [coco.TensorList(g[r], w[r]) for r in range(R)] if as_list else None
+            else:       # the list holds the gradient tensors' addresses: refill them in place
+                for r in range(R):
+                    for b in range(len(counts)):
+                        g[r][b].copy_(torch.from_numpy(grads[r][b]))
             with coco.group():
                 for r, c in enumerate(comms):
+                    gs, ws = (lists[r], None) if as_list else (g[r], w[r])
                     if opt == "sgd":
-                        c.fused_sgd_scattered(g[r], w[r], 0.01)
+                        c.fused_sgd_scattered(gs, ws, 0.01)
                     else:
-                        c.fused_adam_scattered(g[r], w[r], m[r], v[r], h["lr"], h["beta1"],
+                        c.fused_adam_scattered(gs, ws, m[r], v[r], h["lr"], h["beta1"],
                                                h["beta2"], h["eps"], step)
             torch.cuda.synchronize()
             for c in comms:
@@ -75,14 +88,17 @@ def test_scattered_matches_per_tensor_oracle(R, opt):
             c.destroy()
 
 
-@pytest.mark.parametrize("R", [1, 2, 3, 8])
+@pytest.mark.parametrize("R,chunk_shift", [(1, 0), (2, 0), (3, 0), (8, 0), (2, 15)])
 @pytest.mark.parametrize("quirk", [False, True])
-def test_scattered_lamb_has_one_trust_ratio_per_tensor(R, quirk):
+def test_scattered_lamb_has_one_trust_ratio_per_tensor(R, quirk, chunk_shift, monkeypatch):
     """Every tensor of the list against the oracle's LAMB run on that tensor
     alone (its own ||w||, ||r||): moments bit for bit, weights to 1e-5 (the
     norms are summed in another order), replicas bit-identical.  With the
     quirk flag the step is also replayed through the reference sample's own
-    host checker, tensor by tensor."""
+    host checker, tensor by tensor.  With the default chunk size the largest
+    tensor's norms are summed by a warp, the others' by a thread each."""
+    if chunk_shift:
+        monkeypatch.setenv("COCO_SEG_CHUNK_SHIFT", str(chunk_shift))
     counts = SIZES
     off, total, S = _layout(counts, R)
     comms = coco.Communicator.init_all(R, [0] * R)
