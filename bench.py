@@ -900,6 +900,9 @@ def main():
         ms = (timed_flushed if small else timed)(lambda i: fused_step(g[i % nbuf]), args.steps, args.warmup)
         launches = comm.launch_count() - l0 - args.warmup
         clocks = sampler.stop() if sampler else None
+        # the last timed step as CTA 0 of rank 0 saw it (GPU timer): first data phase, norm
+        # exchange, last data phase (everything but LAMB has only the last)
+        phases_us = [round(x, 1) for x in comm.last_phase_times()]
         st = comm.status()
         if st["code"] != 0:
             raise RuntimeError(f"device-side failure during the benchmark: {st}")
@@ -1170,7 +1173,10 @@ def main():
                              "every step under its own event pair"),
                     "algo": "nvls" if use_nvls else "p2p",
                     "bus_gbs": b_nv / t / 1e9, "roofline": roof, "clocks": clocks,
-                    "gpu_launches": int(launches), "e2e": e2e, "parity": parity}
+                    "gpu_launches": int(launches), "e2e": e2e, "parity": parity,
+                    "phases_us": {"first_data_phase": phases_us[0], "norm_exchange": phases_us[1],
+                                  "last_data_phase": phases_us[2],
+                                  "what": "the last timed step inside the kernel, CTA 0 of rank 0, GPU timer"}}
             if probe:
                 line["link_probe"] = probe
             if nccl:

@@ -1620,6 +1620,15 @@ int cocoLastLambNorms(cocoComm_t comm, double out[2]) {
   return cocoSuccess;
 }
 
+int cocoLastPhaseTimes(cocoComm_t comm, unsigned long long out_ns[3]) {
+  if (!comm || !out_ns) return cocoInvalidArgument;
+  DeviceGuard guard(comm->device);
+  unsigned long long t[4];
+  CUDA_TRY(cudaMemcpy(t, comm->flags->phase_ns, sizeof(t), cudaMemcpyDeviceToHost));
+  for (int k = 0; k < 3; ++k) out_ns[k] = t[k + 1] >= t[k] ? t[k + 1] - t[k] : 0;
+  return cocoSuccess;
+}
+
 int cocoGetStatus(cocoComm_t comm, cocoStatus_t *status) {
   if (!comm || !status) return cocoInvalidArgument;
   DeviceGuard guard(comm->device);

@@ -104,6 +104,7 @@ _SIGNATURES = {
     "cocoLinkProbe": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int,
                                 C.POINTER(C.c_double), C.c_void_p]),
     "cocoLastLambNorms": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
+    "cocoLastPhaseTimes": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "cocoGetStatus": (C.c_int, [C.c_void_p, C.POINTER(_Status)]),
     "cocoSliceBounds": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_size_t),
                                   C.POINTER(C.c_size_t)]),
@@ -464,6 +465,13 @@ class Communicator:
         out = (C.c_double * 2)()
         _check(lib().cocoLastLambNorms(self._h, out), "cocoLastLambNorms")
         return out[0], out[1]
+
+    def last_phase_times(self):
+        """(first data phase, norm exchange, last data phase) of the last fused call
+        in microseconds, as CTA 0 of this rank saw them.  Synchronise first."""
+        out = (C.c_uint64 * 3)()
+        _check(lib().cocoLastPhaseTimes(self._h, out), "cocoLastPhaseTimes")
+        return tuple(x / 1e3 for x in out)
 
     def launch_count(self):
         n = C.c_uint64()

@@ -35,6 +35,10 @@ struct FlagPage {
   unsigned int norm_count;  // CTAs of this rank that posted their partial norms
   int status[8];            // cocoStatus_t image: code, rank, phase, peer, seq lo/hi
   double last_norms[2];     // {||w||, ||r||} of the last LAMB step
+  // GPU timer (ns) at which this rank's CTA 0 passed, in the last fused call: the start
+  // barrier, the end of its first data phase (LAMB), the arrival of all ranks' norms (LAMB),
+  // the end of its data; entries a call does not pass are set to the previous one
+  unsigned long long phase_ns[4];
   double cta_part[kMaxCtasPerRank][2];
 };
 

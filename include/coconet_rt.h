@@ -383,6 +383,16 @@ int cocoLinkProbe(cocoComm_t comm, void *buf, size_t bytes, int mode, int unroll
  * out[1] = ||r|| as used for the trust ratio.  Synchronise the stream first. */
 int cocoLastLambNorms(cocoComm_t comm, double out[2]);
 
+/* Where the last fused call on this communicator spent its time, as seen by
+ * CTA 0 of this rank, in nanoseconds of the GPU's timer: out[0] = from the
+ * start barrier to the end of the first data phase (LAMB: reduce + moments +
+ * norms; otherwise 0), out[1] = the exchange of the norms (LAMB; otherwise
+ * 0), out[2] = the last data phase (LAMB: scale + gather; otherwise the
+ * whole reduce + update + gather).  Synchronise the stream first.  The
+ * reference has no counterpart; its programs time whole stages with events
+ * (src/codegen.cpp:4330-4380). */
+int cocoLastPhaseTimes(cocoComm_t comm, unsigned long long out_ns[3]);
+
 /* First device-side failure since the last call (then cleared); the
  * counterpart of ncclCommGetAsyncError (nccl/src/init.cc:996-1021). */
 int cocoGetStatus(cocoComm_t comm, cocoStatus_t *status);
