@@ -653,3 +653,30 @@ def test_more_than_2_to_the_31_elements():
     finally:
         for c in comms + [one]:
             c.destroy()
+
+
+def test_phase_times_of_the_last_call():
+    # cocoLastPhaseTimes: LAMB has two data phases with the exchange of the norms between
+    # them, everything else one; the three add up to less than the call's event time
+    comm = coco.Communicator.init_all(1, [0])[0]
+    try:
+        n = 1 << 24
+        g = torch.full((n,), 1e-3, device="cuda")
+        w = torch.full((n,), 0.5, device="cuda")
+        m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+        for step, lamb in ((0, True), (1, True), (2, False)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if lamb:
+                comm.fused_lamb(g, w, m, v, 1e-3, 0.9, 0.999, 1e-6, 0.01, step)
+            else:
+                comm.fused_adam(g, w, m, v, 1e-3, 0.9, 0.999, 1e-6, step)
+            e1.record()
+            torch.cuda.synchronize()
+            first, exchange, last = comm.last_phase_times()
+            assert last > 0
+            assert (first > 0 and exchange > 0) if lamb else (first == 0 and exchange == 0)
+            assert first + exchange + last <= e0.elapsed_time(e1) * 1e3 + 1.0
+        assert comm.status()["code"] == 0
+    finally:
+        comm.destroy()
