@@ -227,3 +227,51 @@ def test_scattered_rejects_what_is_not_built():
             c.fused_lamb_scattered(many, many, w[0], w[0], 1e-3, 0.9, 0.999, 1e-6, 0.01, 0)
     finally:
         c.destroy()
+
+
+@pytest.mark.parametrize("opt", ["adam", "lamb"])
+def test_scattered_more_pieces_than_the_shared_tables_hold(opt):
+    """2000 small tensors on one rank: more pieces than the kernel keeps first-chunk
+    numbers and trust ratios for in shared memory (1536), so the walk's lookups and
+    the per-tensor ratios of the pieces beyond come from device memory.  Every
+    tensor against the oracle's run on that tensor alone."""
+    rng = np.random.default_rng(11)
+    counts = [int(c) for c in rng.integers(1, 40, size=2000)]
+    counts[1700] = 20000                     # one piece of several chunks among the late ones
+    off, total, S = _layout(counts, 1)
+    comm = coco.Communicator.init_all(1, [0])[0]
+    h = K.HYPER
+    try:
+        w0 = [K.make_weights(c, 900 + b) for b, c in enumerate(counts)]
+        grads = [K.make_grads(1, c, 950 + b, 0)[0] for b, c in enumerate(counts)]
+        # all tensors inside two big buffers, every one at a multiple of 8 elements
+        gbuf, wbuf = torch.zeros(total, device="cuda"), torch.zeros(total, device="cuda")
+        g = [gbuf[o:o + c] for o, c in zip(off, counts)]
+        w = [wbuf[o:o + c] for o, c in zip(off, counts)]
+        gbuf.copy_(torch.from_numpy(np.concatenate(
+            [np.pad(x, (0, (len(x) + 7) // 8 * 8 - len(x))) for x in grads])))
+        wbuf.copy_(torch.from_numpy(np.concatenate(
+            [np.pad(x, (0, (len(x) + 7) // 8 * 8 - len(x))) for x in w0])))
+        m, v = torch.zeros(S, device="cuda"), torch.zeros(S, device="cuda")
+        tl = coco.TensorList(g, w)
+        if opt == "adam":
+            comm.fused_adam_scattered(tl, None, m, v, h["lr"], h["beta1"], h["beta2"], h["eps"], 0)
+        else:
+            comm.fused_lamb_scattered(tl, None, m, v, h["lr"], h["beta1"], h["beta2"], h["eps"],
+                                      h["weight_decay"], 0)
+        torch.cuda.synchronize()
+        assert comm.status()["code"] == 0
+        got_w, got_m, got_v = wbuf.cpu().numpy(), m.cpu().numpy(), v.cpu().numpy()
+        for b, c in enumerate(counts):
+            ow, om, ov = w0[b].copy(), np.zeros(c, np.float32), np.zeros(c, np.float32)
+            if opt == "adam":
+                O.adam(ow, om, ov, grads[b], h["lr"], h["beta1"], h["beta2"], h["eps"], 0)
+                assert np.array_equal(got_w[off[b]:off[b] + c], ow), b
+            else:
+                O.lamb(ow, om, ov, grads[b], h["lr"], h["beta1"], h["beta2"], h["eps"],
+                       h["weight_decay"], 0)
+                K.assert_close(got_w[off[b]:off[b] + c], ow, 1e-5, f"w of tensor {b}")
+            assert np.array_equal(got_m[off[b]:off[b] + c], om), b
+            assert np.array_equal(got_v[off[b]:off[b] + c], ov), b
+    finally:
+        comm.destroy()
