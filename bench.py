@@ -903,6 +903,9 @@ def main():
         # the last timed step as CTA 0 of rank 0 saw it (GPU timer): first data phase, norm
         # exchange, last data phase (everything but LAMB has only the last)
         phases_us = [round(x, 1) for x in comm.last_phase_times()]
+        # ... and how evenly its work was spread: first, median and last CTA of rank 0
+        spread_us = [round(x, 1) for x in comm.last_cta_spread()] \
+            if hasattr(coco.lib(), "cocoLastCtaSpread") else None
         st = comm.status()
         if st["code"] != 0:
             raise RuntimeError(f"device-side failure during the benchmark: {st}")
@@ -1176,6 +1179,7 @@ def main():
                     "gpu_launches": int(launches), "e2e": e2e, "parity": parity,
                     "phases_us": {"first_data_phase": phases_us[0], "norm_exchange": phases_us[1],
                                   "last_data_phase": phases_us[2],
+                                  "cta_end_first_median_last": spread_us,
                                   "what": "the last timed step inside the kernel, CTA 0 of rank 0, GPU timer"}}
             if probe:
                 line["link_probe"] = probe

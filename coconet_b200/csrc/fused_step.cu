@@ -868,12 +868,103 @@ __device__ __forceinline__ void nvls_gather(const RankArgs &ra, int R, size_t i,
 #endif
 constexpr int kNvlsDepth = COCO_NVLS_DEPTH;
 
+// Measured (mixed-precision Adam, 334 M elements; 0 = equal shares by grid stride): at two
+// GPUs 1.166 -> 1.141 ms peer to peer and 1.758 -> 1.692 ms through the switch, fp32 Adam on
+// 2^26 elements 0.452 -> 0.440 ms, the CTAs' finishing times 6-9 % apart before and 2-3 %
+// after; at four GPUs, where the links are the bound whoever uses them, 1.632 -> 1.613 ms.
+#ifndef COCO_MULTI_DYNAMIC
+#define COCO_MULTI_DYNAMIC 1
+#endif
+#ifndef COCO_DYNAMIC_PASSES
+#define COCO_DYNAMIC_PASSES 8
+#endif
+// Hands the units [0, nunits) out warp by warp from a counter in chunks of up to
+// COCO_DYNAMIC_PASSES passes of a warp (32 units each), instead of by grid stride: the
+// CTAs of a rank do not move their shares over the links at the same rate, and under
+// equal shares the step ends with the slowest.  A chunk is at most a quarter of a warp's
+// even share, down to one pass, so that a small message still spreads over all warps
+// (with 8-pass chunks a 1 Mi-element step at two GPUs kept 512 warps busy for 8 passes
+// each: 65 us against 43).  Lane 0 asks for the chunk after next when the warp enters a
+// chunk, so the atomic's round trip is over long before its result is needed.  next()
+// gives the warp's next unit (this lane's), or nunits when there is none.
+struct WarpWork {
+  unsigned *counter;
+  size_t nunits, nchunks;
+  size_t base;        // first unit of the current chunk
+  unsigned pending;   // lane 0: number of the chunk after the current one
+  int pass, passes, lane;
+  bool done;          // no chunk is left (the same in every lane)
+  __device__ __forceinline__ void start(unsigned *c, size_t n) {
+    counter = c, nunits = n;
+    const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+    const size_t quarter_share = n / (warps * 32 * 4);  // in passes
+    passes = quarter_share >= COCO_DYNAMIC_PASSES ? COCO_DYNAMIC_PASSES
+             : quarter_share >= 1 ? (int)quarter_share : 1;
+    nchunks = (n + (size_t)(32 * passes) - 1) / (size_t)(32 * passes);
+    lane = threadIdx.x & 31;
+    pending = 0;
+    if (lane == 0) pending = atomicAdd(counter, 1u);
+    pass = passes;  // the first next() enters the first chunk
+    base = 0;
+    done = false;
+  }
+  __device__ __forceinline__ size_t next() {
+    if (pass == passes) {
+      const size_t c = __shfl_sync(0xffffffffu, pending, 0);
+      if (c >= nchunks) {
+        done = true;  // and stays so: pass is not reset
+        return nunits;
+      }
+      if (lane == 0) pending = atomicAdd(counter, 1u);
+      base = c * (size_t)(32 * passes);
+      pass = 0;
+    }
+    const size_t u = base + (size_t)pass * 32 + lane;
+    ++pass;
+    return u < nunits ? u : nunits;
+  }
+};
+
 // PHASE 0: SGD / Adam step or LAMB moments; PHASE 1: LAMB apply.
 template <int OPT, typename GT, typename LPT, int PHASE>
 __device__ __forceinline__ void nvls_phase(const RankArgs &ra, const StepArgs &sa, const Hyper &h,
                                            size_t lo, size_t nunits, size_t tid, size_t nth,
                                            double &sum_w2, double &sum_r2, float lr_scale) {
   constexpr int V = Multimem<GT>::kN;
+#if COCO_MULTI_DYNAMIC
+  if constexpr (PHASE == 0 && OPT != kLAMB) {  // LAMB's norms are summed in the order of a fixed assignment
+    const GT *src = (const GT *)ra.mc_g + lo;
+    WarpWork ww;
+    ww.start(&ra.flags[ra.rank]->work_next, nunits);
+    uint4 raw[kNvlsDepth];
+    size_t ids[kNvlsDepth];
+#pragma unroll
+    for (int k = 0; k < kNvlsDepth; ++k) {
+      ids[k] = ww.next();
+      if (ids[k] < nunits) raw[k] = Multimem<GT>::ld_reduce(src + ids[k] * V);
+    }
+    for (;;) {
+      const uint4 cur = raw[0];
+      const size_t u = ids[0];
+#pragma unroll
+      for (int k = 0; k + 1 < kNvlsDepth; ++k) raw[k] = raw[k + 1], ids[k] = ids[k + 1];
+      const size_t un = ww.next();
+      ids[kNvlsDepth - 1] = un;
+      if (un < nunits) raw[kNvlsDepth - 1] = Multimem<GT>::ld_reduce(src + un * V);
+      if (u < nunits) {
+        float g[V];
+        Multimem<GT>::unpack(cur, g);
+#pragma unroll
+        for (int e = 0; e < V; ++e) g[e] = __fmul_rn(g[e], sa.grad_scale);
+        apply_unit<OPT, LPT, V, 0, 4, true>(ra, sa, h, lo, lo + u * V, g, sum_w2, sum_r2);
+      }
+      // units come in rising order, so nothing valid follows once the queue is empty
+      // and this warp's current units are past the end
+      if (ww.done && __all_sync(0xffffffffu, u >= nunits)) break;
+    }
+    return;
+  }
+#endif
   if constexpr (PHASE == 0) {
     const GT *src = (const GT *)ra.mc_g + lo;
     uint4 raw[kNvlsDepth];
@@ -968,6 +1059,32 @@ __device__ __forceinline__ void direct_step(const RankArgs &ra, const StepArgs &
       step_unit<OPT, GT, LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, sum_w2, sum_r2);
   }
 }
+#if COCO_MULTI_DYNAMIC
+// The flat slice of a multi-rank SGD / Adam step with the units handed out warp by warp.
+template <int OPT, typename GT, typename LPT, int RB>
+__device__ __forceinline__ void direct_step_dynamic(const RankArgs &ra, const StepArgs &sa,
+                                                    const Hyper &h, size_t lo, size_t first,
+                                                    size_t nelems, size_t tid, size_t nth,
+                                                    double &sum_w2, double &sum_r2) {
+  constexpr int VEC = DirectVec<OPT, GT, RB>::kVec;
+  if constexpr (VEC == 4 && OPT != kLAMB) {
+    const size_t nunits = nelems / VEC;
+    WarpWork ww;
+    ww.start(&ra.flags[ra.rank]->work_next, nunits);
+    for (;;) {
+      const size_t u = ww.next();
+      if (ww.done) break;
+      if (u < nunits) step_unit<OPT, GT, LPT, VEC, RB>(ra, sa, h, lo, first + u * VEC, sum_w2, sum_r2);
+    }
+  } else {
+    direct_step<OPT, GT, LPT, RB>(ra, sa, h, lo, first, nelems, tid, nth, sum_w2, sum_r2);
+  }
+}
+#define COCO_DIRECT_STEP direct_step_dynamic
+#else
+#define COCO_DIRECT_STEP direct_step
+#endif
+
 template <typename GT, typename LPT, int RB>
 __device__ __forceinline__ void direct_apply(const RankArgs &ra, const StepArgs &sa,
                                              const Hyper &h, size_t lo, size_t first,
@@ -1637,11 +1754,11 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
       // scalar loop below takes what the path left over
       (void)first;
     } else if (R == 2)
-      direct_step<OPT, GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
+      COCO_DIRECT_STEP<OPT, GT, LPT, 2>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     else if (R <= 4)
-      direct_step<OPT, GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
+      COCO_DIRECT_STEP<OPT, GT, LPT, 4>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     else
-      direct_step<OPT, GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
+      COCO_DIRECT_STEP<OPT, GT, LPT, 8>(ra, sa, h, lo, first, nvec_rest * VEC, tid, nth, sum_w2, sum_r2);
     const size_t done_elems = PATH == kPathNvls ? nvls_units * NV
                               : PATH == kPathRing ? piped : piped + nvec_rest * VEC;
     for (size_t j = done_elems + tid; j < L; j += nth)
@@ -1765,7 +1882,11 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
 
   if (seg_done) ok = started_ok && seg_norm_ok;
   __syncthreads();
-  if (stamps) me->phase_ns[3] = globaltimer_ns();
+  if (threadIdx.x == 0) {
+    const unsigned long long t = globaltimer_ns();
+    if (blockIdx.x < kMaxCtasPerRank) me->cta_end_ns[blockIdx.x] = t;  // cocoLastCtaSpread
+    if (stamps) me->phase_ns[3] = t;
+  }
 
   // ---- end barrier ----------------------------------------------------------
   if (R > 1) {
@@ -1776,7 +1897,10 @@ __global__ void __launch_bounds__((BlockThreads<PATH, GT>::value), 2)
       if (threadIdx.x == 0) {
         __threadfence_system();
         prev = atomicAdd(&me->done_count, 1u);
-        if (prev == gridDim.x - 1) me->done_count = 0;
+        if (prev == gridDim.x - 1) {
+          me->done_count = 0;
+          me->work_next = 0;  // every CTA of the rank has stopped taking chunks
+        }
         __threadfence_system();
       }
       __syncwarp();

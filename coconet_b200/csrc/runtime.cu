@@ -196,6 +196,7 @@ struct cocoComm {
   int pipeline = -1;         // COCO_PIPELINE: 1 warp rings (bulk copies), 0 register-staged, unset: by world size
   int ring_stages = 0;       // COCO_RING_STAGES: cap on the stages of a ring, 0 = as many as fit
   int seg_chunk_shift = 0;   // COCO_SEG_CHUNK_SHIFT: log2 of the chunk of a list walk, 0 = by size
+  int last_ctas = 0;         // CTAs of this rank in the last fused launch
   int algo = 2;              // 0 p2p, 1 nvls, 2 auto (COCO_ALGO=p2p|nvls|auto)
   cocoTopology_t topo = {};  // peer access / performance between the ranks' GPUs
 };
@@ -622,6 +623,7 @@ int launch_single(cocoComm *c, const PendingCall &pc, char *const g_views[],
   CUDA_TRY(launch_fused_step(pc.opt, pc.g_type, pc.w_lp != nullptr, pc.lp_type, sa, ra, nullptr,
                              cfg, pc.stream));
   c->launches++;
+  c->last_ctas = cfg.ctas;
   return cocoSuccess;
 }
 
@@ -1626,6 +1628,24 @@ int cocoLastPhaseTimes(cocoComm_t comm, unsigned long long out_ns[3]) {
   unsigned long long t[4];
   CUDA_TRY(cudaMemcpy(t, comm->flags->phase_ns, sizeof(t), cudaMemcpyDeviceToHost));
   for (int k = 0; k < 3; ++k) out_ns[k] = t[k + 1] >= t[k] ? t[k + 1] - t[k] : 0;
+  return cocoSuccess;
+}
+
+int cocoLastCtaSpread(cocoComm_t comm, unsigned long long out_ns[3]) {
+  if (!comm || !out_ns) return cocoInvalidArgument;
+  DeviceGuard guard(comm->device);
+  const int n = comm->last_ctas;
+  out_ns[0] = out_ns[1] = out_ns[2] = 0;
+  if (n <= 0) return cocoSuccess;
+  unsigned long long t0 = 0;
+  std::vector<unsigned long long> end((size_t)n);
+  CUDA_TRY(cudaMemcpy(&t0, &comm->flags->phase_ns[0], sizeof(t0), cudaMemcpyDeviceToHost));
+  CUDA_TRY(cudaMemcpy(end.data(), comm->flags->cta_end_ns, sizeof(unsigned long long) * n,
+                      cudaMemcpyDeviceToHost));
+  std::sort(end.begin(), end.end());
+  out_ns[0] = end.front() >= t0 ? end.front() - t0 : 0;
+  out_ns[1] = end[n / 2] >= t0 ? end[n / 2] - t0 : 0;
+  out_ns[2] = end.back() >= t0 ? end.back() - t0 : 0;
   return cocoSuccess;
 }
 

@@ -105,6 +105,7 @@ _SIGNATURES = {
                                 C.POINTER(C.c_double), C.c_void_p]),
     "cocoLastLambNorms": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "cocoLastPhaseTimes": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
+    "cocoLastCtaSpread": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "cocoGetStatus": (C.c_int, [C.c_void_p, C.POINTER(_Status)]),
     "cocoSliceBounds": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_size_t),
                                   C.POINTER(C.c_size_t)]),
@@ -471,6 +472,13 @@ class Communicator:
         in microseconds, as CTA 0 of this rank saw them.  Synchronise first."""
         out = (C.c_uint64 * 3)()
         _check(lib().cocoLastPhaseTimes(self._h, out), "cocoLastPhaseTimes")
+        return tuple(x / 1e3 for x in out)
+
+    def last_cta_spread(self):
+        """Microseconds from the start barrier to the end of the data of the first,
+        the median and the last CTA of this rank in the last fused call."""
+        out = (C.c_uint64 * 3)()
+        _check(lib().cocoLastCtaSpread(self._h, out), "cocoLastCtaSpread")
         return tuple(x / 1e3 for x in out)
 
     def launch_count(self):

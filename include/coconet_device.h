@@ -40,6 +40,12 @@ struct FlagPage {
   // the end of its data; entries a call does not pass are set to the previous one
   unsigned long long phase_ns[4];
   double cta_part[kMaxCtasPerRank][2];
+  // GPU timer (ns) at which every CTA of this rank finished its data in the last fused call
+  unsigned long long cta_end_ns[kMaxCtasPerRank];
+  // multi-rank kernels that hand their work out warp by warp: the next chunk to take (set
+  // back to zero by the rank's last CTA at the end barrier)
+  unsigned int work_next;
+  unsigned int pad_;
 };
 
 // Per-tensor norm partials of a scattered LAMB call.  A communicator allocates

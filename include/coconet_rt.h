@@ -393,6 +393,13 @@ int cocoLastLambNorms(cocoComm_t comm, double out[2]);
  * (src/codegen.cpp:4330-4380). */
 int cocoLastPhaseTimes(cocoComm_t comm, unsigned long long out_ns[3]);
 
+/* How evenly the last fused call's work was spread over this rank's CTAs:
+ * the time from the start barrier to the end of a CTA's data, in nanoseconds
+ * of the GPU's timer, for the CTA that finished first (out[0]), the median
+ * CTA (out[1]) and the last (out[2]).  The step ends with the last.
+ * Synchronise the stream first.  No reference counterpart. */
+int cocoLastCtaSpread(cocoComm_t comm, unsigned long long out_ns[3]);
+
 /* First device-side failure since the last call (then cleared); the
  * counterpart of ncclCommGetAsyncError (nccl/src/init.cc:996-1021). */
 int cocoGetStatus(cocoComm_t comm, cocoStatus_t *status);

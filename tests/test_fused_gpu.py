@@ -677,6 +677,9 @@ def test_phase_times_of_the_last_call():
             assert last > 0
             assert (first > 0 and exchange > 0) if lamb else (first == 0 and exchange == 0)
             assert first + exchange + last <= e0.elapsed_time(e1) * 1e3 + 1.0
+            # cocoLastCtaSpread: the first, the median and the last CTA to finish its data
+            lo_us, mid_us, hi_us = comm.last_cta_spread()
+            assert 0 < lo_us <= mid_us <= hi_us <= e0.elapsed_time(e1) * 1e3 + 1.0
         assert comm.status()["code"] == 0
     finally:
         comm.destroy()
