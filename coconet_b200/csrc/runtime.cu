@@ -768,6 +768,7 @@ int flush_group(LocalGroup *grp) {
       break;
     }
     lead->launches++;
+    for (int r : ranks) grp->comms[r]->last_ctas = cfg.ctas;
   }
   for (cocoComm *c : grp->comms) c->has_pending = false;
   return result;
